@@ -1,0 +1,152 @@
+/*
+ * tmw.h — C ABI of libtmw: sliding-window attention with persistent prefix keys
+ * for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces the attention core of TitanMAC's WindowedAttention module
+ * (reference project path: titans_core/attn/windowed_attention.py).  All
+ * pointers are device pointers unless stated otherwise; sizes and strides are in
+ * ELEMENTS; the innermost (head_dim) stride of every tensor is 1.  Every entry
+ * point enqueues work on the CUDA stream it is given (a cudaStream_t passed as
+ * void*, NULL = the default stream) and returns without synchronising.  Return
+ * value: TMW_OK (0) or a negative tmw_status.  Nothing here throws, allocates
+ * caller-visible memory or falls back to the CPU.
+ *
+ * Positions.  The reference treats the first n_persistent rows of its input as
+ * "persistent" rows and the rest as sequence rows; positions in this header
+ * count over that whole length L = n_persistent + T.  A query at position p
+ * attends to
+ *     every key position g <  n_persistent                       and, if
+ *     p >= n_persistent, to the keys max(n_persistent, p - window) <= g <= p.
+ * (windowed_attention.py:113-118 and :134-150; a query therefore sees window+1
+ * sequence keys including itself.)
+ */
+#ifndef TMW_H_
+#define TMW_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TMW_VERSION 100
+
+#if defined(__GNUC__)
+#define TMW_API __attribute__((visibility("default")))
+#else
+#define TMW_API
+#endif
+
+typedef enum tmw_status {
+    TMW_OK = 0,
+    TMW_ERR_INVALID_ARGUMENT = -1, /* NULL pointer, negative size, stride/alignment rule broken        */
+    TMW_ERR_UNSUPPORTED = -2,      /* dtype / head_dim / algorithm combination that has no kernel       */
+    TMW_ERR_PERSISTENT_GE_LEN = -3,/* n_persistent >= length (the reference raises ValueError, :97-100) */
+    TMW_ERR_NEGATIVE_WINDOW = -4,  /* window < 0 (the reference raises ValueError, :102-103)            */
+    TMW_ERR_KEY_RANGE = -5,        /* a query needs a key position the K/V buffers do not hold          */
+    TMW_ERR_CUDA = -6,             /* a CUDA runtime or driver call failed; see tmw_last_cuda_error()   */
+    TMW_ERR_DEVICE_TIMEOUT = -7,   /* a bounded device-side wait gave up (read back by tmw_poll_status) */
+    TMW_ERR_TOO_LARGE = -8         /* a fixed capacity of the called entry point is exceeded            */
+} tmw_status;
+
+typedef enum tmw_dtype { TMW_F32 = 0, TMW_BF16 = 1, TMW_F16 = 2 } tmw_dtype;
+
+typedef enum tmw_algo {
+    TMW_ALGO_AUTO = 0,   /* tcgen05 kernel when it applies, otherwise the CUDA-core kernel       */
+    TMW_ALGO_SIMT = 1,   /* CUDA-core kernel (every dtype, head_dim 8/16/32/64/96/128/256)       */
+    TMW_ALGO_TCGEN05 = 2 /* tensor-core kernel (bf16/f16, head_dim 64 or 128)                    */
+} tmw_algo;
+
+/*
+ * Prefill: o = softmax(q kᵀ · scale + mask) v for a block of query rows.
+ * Replaces the bool→additive mask conversion and the scaled-dot-product call of
+ * WindowedAttention.forward (windowed_attention.py:307-323) together with the
+ * dense mask of build_band_mask (:61-152), which is never materialised.
+ *
+ * q, o : [batch, heads, q_rows, head_dim]   addressed through *_stride[3] =
+ * k, v : [batch, heads, k_rows, head_dim]   {batch, head, row} element strides.
+ *
+ * Query row r sits at position q_pos0 + r.  Key rows [0, n_persistent) are the
+ * persistent keys; key row n_persistent + i sits at position k_pos0 + i.  The
+ * unsharded call has q_pos0 = 0, k_pos0 = n_persistent and q_rows = k_rows = L.
+ * A sequence-sharded rank passes its own rows as q and a K/V buffer laid out as
+ * [persistent | halo from the left neighbour | own rows] with k_pos0 = position
+ * of the first halo row.
+ */
+typedef struct tmw_prefill_desc {
+    int32_t dtype;        /* tmw_dtype of q, k, v and o                                   */
+    int32_t algo;         /* tmw_algo                                                     */
+    int32_t batch, heads, head_dim;
+    int32_t q_rows, k_rows;
+    int32_t window;       /* w: a sequence query sees itself and the w previous keys      */
+    int32_t n_persistent; /* Np                                                           */
+    int32_t q_pos0;       /* position of query row 0                                      */
+    int32_t k_pos0;       /* position of key row n_persistent (>= n_persistent)           */
+    float scale;          /* 0 selects 1/sqrt(head_dim), the reference's default (:318)   */
+    int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3];
+} tmw_prefill_desc;
+
+TMW_API int tmw_prefill(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v, void* o,
+                void* stream);
+
+/*
+ * Decode: one new token per sequence against a ring cache of the last window+1
+ * keys.  The reference has no incremental decode (its generation helper re-runs
+ * the full forward per token, examples/train_math.py:146-161); this entry point
+ * returns what the last row of that forward returns.
+ *
+ * k_ring, v_ring : [batch, heads, slots, head_dim] contiguous, slots = window+1.
+ * k_pers, v_pers : [heads, n_persistent, head_dim] contiguous, shared by the batch
+ *                  (may be NULL when n_persistent == 0).
+ * Token t of a sequence (t = 0 for its first sequence token) lives in slot
+ * t % slots.
+ */
+typedef struct tmw_cache_desc {
+    int32_t dtype;
+    int32_t batch, heads, head_dim;
+    int32_t window, n_persistent;
+    void* k_ring;
+    void* v_ring;
+    const void* k_pers;
+    const void* v_pers;
+    float scale; /* 0 selects 1/sqrt(head_dim) */
+} tmw_cache_desc;
+
+/* Bytes of ONE ring (k or v) for the given geometry; 0 on bad arguments. */
+TMW_API size_t tmw_cache_ring_bytes(int32_t dtype, int32_t batch, int32_t heads, int32_t head_dim, int32_t window);
+
+/*
+ * Copy K/V rows produced by a prefill into the ring.  k, v: [batch, heads, rows,
+ * head_dim] through {batch, head, row} strides, row i being sequence token
+ * t0 + i.  Only the last min(rows, window+1) rows are kept.
+ */
+TMW_API int tmw_cache_fill(const tmw_cache_desc* cache, const void* k, const void* v, const int64_t k_stride[3],
+                   const int64_t v_stride[3], int32_t rows, int32_t t0, void* stream);
+
+/*
+ * One decode step.  q, k_new, v_new, o: [batch, heads, head_dim] through
+ * {batch, head} strides.  pos: device array [batch] of int32, the sequence index
+ * t of the new token.  The call stores k_new/v_new into slot t % (window+1) and
+ * attends over the persistent keys and the min(t+1, window+1) newest slots.
+ */
+TMW_API int tmw_decode(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new, void* o,
+               const int64_t q_stride[2], const int64_t kv_new_stride[2], const int64_t o_stride[2],
+               const int32_t* pos, void* stream);
+
+/* Library facts. */
+TMW_API int tmw_version(void);
+TMW_API const char* tmw_strerror(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+TMW_API const char* tmw_last_cuda_error(void);
+/*
+ * Device-side status word of the current device: 0, or TMW_ERR_DEVICE_TIMEOUT if a
+ * kernel's bounded wait expired since the last poll.  Synchronises the given
+ * stream, then clears the word.
+ */
+TMW_API int tmw_poll_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TMW_H_ */

@@ -1,0 +1,92 @@
+"""Parity of the ring-cache decode path (through the C ABI) with the reference's decode semantics:
+the output for a new token equals the last row of a full forward over everything seen so far."""
+
+import pytest
+import torch
+
+from oracle import windowed_oracle as wo
+from titanmac_b200 import _native
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_decode(q, k, v, w, Np, prefill_tokens, dtype):
+    """q,k,v: [B,H,L,dh] CPU.  Prefill the ring with the first tokens, then decode the rest one by one."""
+    B, H, L, dh = q.shape
+    cache = _native.RingCache(B, H, dh, w, Np, dtype, DEV)
+    qd, kd, vd = (t.to(dtype).to(DEV) for t in (q, k, v))
+    cache.set_persistent(kd[0, :, :Np], vd[0, :, :Np])
+    if prefill_tokens > 0:
+        cache.fill(kd[:, :, Np:Np + prefill_tokens], vd[:, :, Np:Np + prefill_tokens], t0=0)
+    outs = []
+    for t in range(prefill_tokens, L - Np):
+        pos = torch.full((B,), t, dtype=torch.int32, device=DEV)
+        outs.append(cache.decode(qd[:, :, Np + t], kd[:, :, Np + t], vd[:, :, Np + t], pos).clone())
+    return torch.stack(outs, dim=2)  # [B,H,steps,dh]
+
+
+def test_decode_fp32_equals_last_row_of_reference_forward(golden):
+    case = "dh64_multi_tile"   # L=300, w=64, Np=16: the ring wraps several times
+    m = golden.meta(case)
+    q, k, v, o = (golden[case, f"core_{n}"] for n in "qkvo")
+    for pre in (0, 10, 100):
+        got = run_decode(q, k, v, m["w"], m["Np"], pre, torch.float32).cpu()
+        want = o[:, :, m["Np"] + pre:]
+        assert (got - want).abs().max().item() <= 1e-5, pre
+
+
+@pytest.mark.parametrize("dh,w,Np,B,H,L,pre", [
+    (64, 512, 16, 3, 10, 16 + 700, 600),   # default model geometry, ring wraps
+    (128, 100, 16, 2, 2, 16 + 230, 0),
+    (32, 7, 0, 2, 3, 60, 3),               # no persistent keys
+    (16, 0, 2, 1, 2, 2 + 20, 1),           # self-only window
+    (256, 20, 4, 1, 1, 4 + 50, 25),
+    (8, 5, 1, 2, 1, 1 + 30, 0),
+])
+def test_decode_bf16_matches_fp32_oracle(dh, w, Np, B, H, L, pre):
+    q, k, v = wo.qkv_inputs(B, H, L, dh, seed=dh + w)
+    q, k, v = (t.to(torch.bfloat16) for t in (q, k, v))
+    k[1:, :, :Np] = k[:1, :, :Np]  # persistent rows are shared by the batch
+    v[1:, :, :Np] = v[:1, :, :Np]
+    got = run_decode(q, k, v, w, Np, pre, torch.bfloat16).float().cpu()
+    want = wo.attention_core_rows(q[:, :, Np + pre:], k, v, Np + pre, w, Np)
+    assert (got - want).abs().max().item() <= 2e-2
+
+
+def test_decode_ragged_positions_and_strided_inputs():
+    """Sequences at different positions in one call; q/k/v taken as strided views of one [B, 3D] buffer."""
+    dh, w, Np, B, H = 64, 50, 4, 4, 3
+    L = Np + 200
+    q, k, v = (t.to(torch.bfloat16) for t in wo.qkv_inputs(B, H, L, dh, seed=9))
+    k[1:, :, :Np] = k[:1, :, :Np]
+    v[1:, :, :Np] = v[:1, :, :Np]
+    ts = [0, 49, 50, 137]
+    cache = _native.RingCache(B, H, dh, w, Np, torch.bfloat16, DEV)
+    cache.set_persistent(k[0, :, :Np].to(DEV), v[0, :, :Np].to(DEV))
+    for b, t in enumerate(ts):  # history of sequence b: tokens 0..t-1
+        if t > 0:
+            cb = _native.RingCache(1, H, dh, w, Np, torch.bfloat16, DEV)
+            cb.fill(k[b:b + 1, :, Np:Np + t].to(DEV), v[b:b + 1, :, Np:Np + t].to(DEV))
+            cache.k_ring[b].copy_(cb.k_ring[0])
+            cache.v_ring[b].copy_(cb.v_ring[0])
+    qkv = torch.empty(B, 3, H, dh, dtype=torch.bfloat16, device=DEV)
+    for b, t in enumerate(ts):
+        qkv[b, 0], qkv[b, 1], qkv[b, 2] = q[b, :, Np + t].to(DEV), k[b, :, Np + t].to(DEV), v[b, :, Np + t].to(DEV)
+    pos = torch.tensor(ts, dtype=torch.int32, device=DEV)
+    got = cache.decode(qkv[:, 0], qkv[:, 1], qkv[:, 2], pos).float().cpu()
+    for b, t in enumerate(ts):
+        want = wo.attention_core_rows(q[b:b + 1, :, Np + t:Np + t + 1], k[b:b + 1], v[b:b + 1], Np + t, w, Np)
+        assert (got[b] - want[0, :, 0]).abs().max().item() <= 2e-2, (b, t)
+        assert torch.equal(cache.k_ring[b, :, t % (w + 1)].cpu(), k[b, :, Np + t])
+
+
+def test_cache_fill_keeps_only_the_window():
+    dh, w, B, H = 16, 4, 1, 1
+    k = torch.arange(12, dtype=torch.float32).view(1, 1, 12, 1).expand(B, H, 12, dh).contiguous().to(DEV)
+    cache = _native.RingCache(B, H, dh, w, 0, torch.float32, DEV)
+    cache.fill(k, k, t0=3)  # tokens 3..14; the ring of 5 slots keeps tokens 10..14
+    ring = cache.k_ring[0, 0, :, 0].cpu().tolist()
+    assert sorted(ring) == [7.0, 8.0, 9.0, 10.0, 11.0]       # row i holds value i = token 3+i
+    for tok in range(10, 15):
+        assert ring[tok % 5] == float(tok - 3)

@@ -1,0 +1,185 @@
+// C-ABI entry points of libtmw: argument validation, kernel selection, error text.
+// Everything that can be rejected is rejected here, on the host, before a launch.
+#include <cstdio>
+#include <cstring>
+
+#include "tmw_common.cuh"
+
+namespace tmw {
+
+static thread_local char g_error_text[256] = "";
+
+void set_error_text(const char* text) {
+    std::snprintf(g_error_text, sizeof(g_error_text), "%s", text);
+}
+
+void set_cuda_error(cudaError_t e, const char* where) {
+    std::snprintf(g_error_text, sizeof(g_error_text), "%s: %s (%s)", cudaGetErrorName(e), cudaGetErrorString(e),
+                  where);
+}
+
+// One status word per device: a __device__ variable is instantiated in every
+// context that loads this module.
+__device__ int g_device_status = 0;
+
+int* device_status_word() {
+    constexpr int kMaxDevices = 64;
+    static int* cache[kMaxDevices] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (cache[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
+        cache[dev] = static_cast<int*>(ptr);
+    }
+    return cache[dev];
+}
+
+namespace {
+
+bool dtype_ok(int dtype) { return dtype == TMW_F32 || dtype == TMW_BF16 || dtype == TMW_F16; }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool strides_ok(const int64_t* s, int n, int dtype) {
+    const int64_t unit = 16 / (int64_t)dtype_size(dtype);  // elements per 16 bytes
+    for (int i = 0; i < n; ++i)
+        if (s[i] < 0 || s[i] % unit != 0) return false;
+    return true;
+}
+
+int validate_prefill(const tmw_prefill_desc* d, const void* q, const void* k, const void* v, const void* o) {
+    if (d == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (!dtype_ok(d->dtype)) return TMW_ERR_UNSUPPORTED;
+    if (d->algo < TMW_ALGO_AUTO || d->algo > TMW_ALGO_TCGEN05) return TMW_ERR_INVALID_ARGUMENT;
+    if (d->batch < 0 || d->heads < 0 || d->head_dim <= 0 || d->q_rows < 0 || d->k_rows < 0 ||
+        d->n_persistent < 0 || d->q_pos0 < 0)
+        return TMW_ERR_INVALID_ARGUMENT;
+    if (d->window < 0) return TMW_ERR_NEGATIVE_WINDOW;
+    if (d->k_rows <= d->n_persistent) return TMW_ERR_PERSISTENT_GE_LEN;
+    if (d->k_pos0 < d->n_persistent) return TMW_ERR_INVALID_ARGUMENT;
+    if (!(d->scale >= 0.f)) return TMW_ERR_INVALID_ARGUMENT;
+    if (d->batch == 0 || d->heads == 0 || d->q_rows == 0) return TMW_OK;
+    if (q == nullptr || k == nullptr || v == nullptr || o == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return TMW_ERR_INVALID_ARGUMENT;
+    if (!strides_ok(d->q_stride, 3, d->dtype) || !strides_ok(d->k_stride, 3, d->dtype) ||
+        !strides_ok(d->v_stride, 3, d->dtype) || !strides_ok(d->o_stride, 3, d->dtype))
+        return TMW_ERR_INVALID_ARGUMENT;
+    // every sequence query must find its window inside the K/V buffers
+    const int64_t np = d->n_persistent;
+    const int64_t p_last = (int64_t)d->q_pos0 + d->q_rows - 1;
+    if (p_last >= np) {
+        const int64_t p_first = d->q_pos0 > np ? d->q_pos0 : np;
+        const int64_t g_lo = p_first - d->window > np ? p_first - d->window : np;
+        const int64_t k_last = (int64_t)d->k_pos0 + (d->k_rows - np) - 1;
+        if (g_lo < d->k_pos0 || p_last > k_last) return TMW_ERR_KEY_RANGE;
+    }
+    return TMW_OK;
+}
+
+int validate_cache(const tmw_cache_desc* c) {
+    if (c == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (!dtype_ok(c->dtype)) return TMW_ERR_UNSUPPORTED;
+    if (c->batch < 0 || c->heads < 0 || c->head_dim <= 0 || c->n_persistent < 0) return TMW_ERR_INVALID_ARGUMENT;
+    if (c->window < 0) return TMW_ERR_NEGATIVE_WINDOW;
+    const int dh = c->head_dim;
+    if (!(dh == 8 || dh == 16 || dh == 32 || dh == 64 || dh == 128 || dh == 256)) return TMW_ERR_UNSUPPORTED;
+    if (!(c->scale >= 0.f)) return TMW_ERR_INVALID_ARGUMENT;
+    if (c->batch == 0 || c->heads == 0) return TMW_OK;
+    if (c->k_ring == nullptr || c->v_ring == nullptr || !aligned16(c->k_ring) || !aligned16(c->v_ring))
+        return TMW_ERR_INVALID_ARGUMENT;
+    if (c->n_persistent > 0 &&
+        (c->k_pers == nullptr || c->v_pers == nullptr || !aligned16(c->k_pers) || !aligned16(c->v_pers)))
+        return TMW_ERR_INVALID_ARGUMENT;
+    return TMW_OK;
+}
+
+}  // namespace
+}  // namespace tmw
+
+extern "C" {
+
+int tmw_version(void) { return TMW_VERSION; }
+
+const char* tmw_strerror(int status) {
+    switch (status) {
+        case TMW_OK: return "ok";
+        case TMW_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, negative size, stride or alignment)";
+        case TMW_ERR_UNSUPPORTED: return "unsupported dtype / head_dim / algorithm";
+        case TMW_ERR_PERSISTENT_GE_LEN: return "n_persistent must be < length";
+        case TMW_ERR_NEGATIVE_WINDOW: return "window must be non-negative";
+        case TMW_ERR_KEY_RANGE: return "a query's window reaches outside the key/value buffers";
+        case TMW_ERR_CUDA: return "CUDA call failed";
+        case TMW_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+        case TMW_ERR_TOO_LARGE: return "size exceeds a fixed capacity of this entry point";
+        default: return "unknown status";
+    }
+}
+
+const char* tmw_last_cuda_error(void) { return tmw::g_error_text; }
+
+int tmw_prefill(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v, void* o,
+                void* stream) {
+    const int rc = tmw::validate_prefill(desc, q, k, v, o);
+    if (rc != TMW_OK) return rc;
+    if (desc->batch == 0 || desc->heads == 0 || desc->q_rows == 0) return TMW_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool tc_ok = tmw::prefill_tc_supports(*desc, q, k, v, o);
+    if (desc->algo == TMW_ALGO_TCGEN05) {
+        if (!tc_ok) return TMW_ERR_UNSUPPORTED;
+        return tmw::launch_prefill_tc(*desc, q, k, v, o, s);
+    }
+    if (desc->algo == TMW_ALGO_AUTO && tc_ok) return tmw::launch_prefill_tc(*desc, q, k, v, o, s);
+    return tmw::launch_prefill_simt(*desc, q, k, v, o, s);
+}
+
+size_t tmw_cache_ring_bytes(int32_t dtype, int32_t batch, int32_t heads, int32_t head_dim, int32_t window) {
+    if (!tmw::dtype_ok(dtype) || batch < 0 || heads < 0 || head_dim <= 0 || window < 0) return 0;
+    return (size_t)batch * (size_t)heads * ((size_t)window + 1) * (size_t)head_dim * tmw::dtype_size(dtype);
+}
+
+int tmw_cache_fill(const tmw_cache_desc* cache, const void* k, const void* v, const int64_t k_stride[3],
+                   const int64_t v_stride[3], int32_t rows, int32_t t0, void* stream) {
+    const int rc = tmw::validate_cache(cache);
+    if (rc != TMW_OK) return rc;
+    if (rows < 0 || t0 < 0 || k_stride == nullptr || v_stride == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (cache->batch == 0 || cache->heads == 0 || rows == 0) return TMW_OK;
+    if (k == nullptr || v == nullptr || !tmw::aligned16(k) || !tmw::aligned16(v)) return TMW_ERR_INVALID_ARGUMENT;
+    if (!tmw::strides_ok(k_stride, 3, cache->dtype) || !tmw::strides_ok(v_stride, 3, cache->dtype))
+        return TMW_ERR_INVALID_ARGUMENT;
+    return tmw::launch_cache_fill(*cache, k, v, k_stride, v_stride, rows, t0, static_cast<cudaStream_t>(stream));
+}
+
+int tmw_decode(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new, void* o,
+               const int64_t q_stride[2], const int64_t kv_new_stride[2], const int64_t o_stride[2],
+               const int32_t* pos, void* stream) {
+    const int rc = tmw::validate_cache(cache);
+    if (rc != TMW_OK) return rc;
+    if (q_stride == nullptr || kv_new_stride == nullptr || o_stride == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (cache->batch == 0 || cache->heads == 0) return TMW_OK;
+    if (q == nullptr || k_new == nullptr || v_new == nullptr || o == nullptr || pos == nullptr)
+        return TMW_ERR_INVALID_ARGUMENT;
+    if (!tmw::aligned16(q) || !tmw::aligned16(k_new) || !tmw::aligned16(v_new) || !tmw::aligned16(o))
+        return TMW_ERR_INVALID_ARGUMENT;
+    if (!tmw::strides_ok(q_stride, 2, cache->dtype) || !tmw::strides_ok(kv_new_stride, 2, cache->dtype) ||
+        !tmw::strides_ok(o_stride, 2, cache->dtype))
+        return TMW_ERR_INVALID_ARGUMENT;
+    return tmw::launch_decode(*cache, q, k_new, v_new, o, q_stride, kv_new_stride, o_stride, pos,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int tmw_poll_status(void* stream) {
+    TMW_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    int* word = tmw::device_status_word();
+    if (word == nullptr) return TMW_ERR_CUDA;
+    int value = 0;
+    TMW_CUDA_TRY(cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (value != 0) {
+        const int zero = 0;
+        TMW_CUDA_TRY(cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice));
+        return TMW_ERR_DEVICE_TIMEOUT;
+    }
+    return TMW_OK;
+}
+
+}  // extern "C"

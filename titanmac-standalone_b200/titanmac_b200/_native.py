@@ -1,0 +1,273 @@
+"""ctypes binding of ``libtmw.so`` (C ABI declared in ``include/tmw.h``).
+
+There is no other implementation behind these functions: if the shared library is
+missing or a call fails, an exception is raised — nothing falls back to PyTorch
+or to the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import Optional, Sequence
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtmw.so")
+
+TMW_OK = 0
+TMW_ERR_INVALID_ARGUMENT = -1
+TMW_ERR_UNSUPPORTED = -2
+TMW_ERR_PERSISTENT_GE_LEN = -3
+TMW_ERR_NEGATIVE_WINDOW = -4
+TMW_ERR_KEY_RANGE = -5
+TMW_ERR_CUDA = -6
+TMW_ERR_DEVICE_TIMEOUT = -7
+TMW_ERR_TOO_LARGE = -8
+
+TMW_F32, TMW_BF16, TMW_F16 = 0, 1, 2
+ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05 = 0, 1, 2
+
+_DTYPES = {torch.float32: TMW_F32, torch.bfloat16: TMW_BF16, torch.float16: TMW_F16}
+
+
+class TmwError(RuntimeError):
+    """A libtmw call returned a status that has no more specific Python exception."""
+
+    def __init__(self, status: int, text: str):
+        super().__init__(f"libtmw: {text} (status {status})")
+        self.status = status
+
+
+class PrefillDesc(ctypes.Structure):
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("algo", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("q_rows", ctypes.c_int32),
+        ("k_rows", ctypes.c_int32),
+        ("window", ctypes.c_int32),
+        ("n_persistent", ctypes.c_int32),
+        ("q_pos0", ctypes.c_int32),
+        ("k_pos0", ctypes.c_int32),
+        ("scale", ctypes.c_float),
+        ("q_stride", ctypes.c_int64 * 3),
+        ("k_stride", ctypes.c_int64 * 3),
+        ("v_stride", ctypes.c_int64 * 3),
+        ("o_stride", ctypes.c_int64 * 3),
+    ]
+
+
+class CacheDesc(ctypes.Structure):
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("batch", ctypes.c_int32),
+        ("heads", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32),
+        ("window", ctypes.c_int32),
+        ("n_persistent", ctypes.c_int32),
+        ("k_ring", ctypes.c_void_p),
+        ("v_ring", ctypes.c_void_p),
+        ("k_pers", ctypes.c_void_p),
+        ("v_pers", ctypes.c_void_p),
+        ("scale", ctypes.c_float),
+    ]
+
+
+# name -> (restype, argtypes); the CPU test-suite checks that every symbol here is
+# declared in include/tmw.h and exported by the library, and vice versa.
+SIGNATURES = {
+    "tmw_version": (ctypes.c_int, []),
+    "tmw_strerror": (ctypes.c_char_p, [ctypes.c_int]),
+    "tmw_last_cuda_error": (ctypes.c_char_p, []),
+    "tmw_poll_status": (ctypes.c_int, [ctypes.c_void_p]),
+    "tmw_prefill": (
+        ctypes.c_int,
+        [ctypes.POINTER(PrefillDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+         ctypes.c_void_p],
+    ),
+    "tmw_cache_ring_bytes": (ctypes.c_size_t, [ctypes.c_int32] * 5),
+    "tmw_cache_fill": (
+        ctypes.c_int,
+        [ctypes.POINTER(CacheDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64),
+         ctypes.POINTER(ctypes.c_int64), ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p],
+    ),
+    "tmw_decode": (
+        ctypes.c_int,
+        [ctypes.POINTER(CacheDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+         ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
+         ctypes.c_void_p, ctypes.c_void_p],
+    ),
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load ``libtmw.so`` from the package directory (once)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `make -C titanmac-standalone_b200/csrc -j` "
+                "(nvcc, sm_100a).  There is no fallback implementation."
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def check(status: int) -> None:
+    """Map a libtmw status to the exception the reference raises in the same situation."""
+    if status == TMW_OK:
+        return
+    text = lib().tmw_strerror(status).decode()
+    if status in (TMW_ERR_PERSISTENT_GE_LEN, TMW_ERR_NEGATIVE_WINDOW):
+        raise ValueError(text)  # build_band_mask raises ValueError for both
+    if status == TMW_ERR_CUDA:
+        text += ": " + lib().tmw_last_cuda_error().decode()
+    raise TmwError(status, text)
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("libtmw works on CUDA tensors only; there is no CPU path")
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _bhrd_strides(t: torch.Tensor) -> Sequence[int]:
+    if t.stride(3) != 1:
+        raise ValueError("the head_dim axis must be contiguous")
+    return (t.stride(0), t.stride(1), t.stride(2))
+
+
+def prefill(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    window: int,
+    n_persistent: int,
+    out: Optional[torch.Tensor] = None,
+    q_pos0: int = 0,
+    k_pos0: Optional[int] = None,
+    scale: float = 0.0,
+    algo: int = ALGO_AUTO,
+) -> torch.Tensor:
+    """``tmw_prefill`` on ``[B, H, rows, dh]`` tensors (any strides with a contiguous last axis)."""
+    _require_cuda(q, k, v)
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise TypeError("q, k, v must share one dtype out of float32, bfloat16, float16")
+    B, H, rq, dh = q.shape
+    rk = k.shape[2]
+    if out is None:
+        out = torch.empty((B, rq, H, dh), dtype=q.dtype, device=q.device).permute(0, 2, 1, 3)
+    d = PrefillDesc()
+    d.dtype = _DTYPES[q.dtype]
+    d.algo = algo
+    d.batch, d.heads, d.head_dim = B, H, dh
+    d.q_rows, d.k_rows = rq, rk
+    d.window, d.n_persistent = window, n_persistent
+    d.q_pos0 = q_pos0
+    d.k_pos0 = n_persistent if k_pos0 is None else k_pos0
+    d.scale = scale
+    d.q_stride[:] = _bhrd_strides(q)
+    d.k_stride[:] = _bhrd_strides(k)
+    d.v_stride[:] = _bhrd_strides(v)
+    d.o_stride[:] = _bhrd_strides(out)
+    with torch.cuda.device(q.device):
+        check(lib().tmw_prefill(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                _stream_ptr(q.device)))
+    return out
+
+
+class RingCache:
+    """K/V ring of ``window + 1`` slots per (sequence, head) plus the batch-shared persistent K/V."""
+
+    def __init__(self, batch: int, heads: int, head_dim: int, window: int, n_persistent: int,
+                 dtype: torch.dtype, device: torch.device, scale: float = 0.0):
+        if dtype not in _DTYPES:
+            raise TypeError("dtype must be float32, bfloat16 or float16")
+        if window < 0:
+            raise ValueError(f"window_size must be non-negative, got {window}")
+        self.batch, self.heads, self.head_dim = batch, heads, head_dim
+        self.window, self.n_persistent = window, n_persistent
+        self.slots = window + 1
+        self.dtype, self.device, self.scale = dtype, torch.device(device), scale
+        nbytes = lib().tmw_cache_ring_bytes(_DTYPES[dtype], batch, heads, head_dim, window)
+        elems = nbytes // torch.empty((), dtype=dtype).element_size()
+        assert elems == batch * heads * self.slots * head_dim
+        self.k_ring = torch.zeros((batch, heads, self.slots, head_dim), dtype=dtype, device=device)
+        self.v_ring = torch.zeros_like(self.k_ring)
+        self.k_pers = torch.zeros((heads, n_persistent, head_dim), dtype=dtype, device=device)
+        self.v_pers = torch.zeros_like(self.k_pers)
+
+    def desc(self) -> CacheDesc:
+        c = CacheDesc()
+        c.dtype = _DTYPES[self.dtype]
+        c.batch, c.heads, c.head_dim = self.batch, self.heads, self.head_dim
+        c.window, c.n_persistent = self.window, self.n_persistent
+        c.k_ring, c.v_ring = self.k_ring.data_ptr(), self.v_ring.data_ptr()
+        c.k_pers = self.k_pers.data_ptr() if self.n_persistent > 0 else None
+        c.v_pers = self.v_pers.data_ptr() if self.n_persistent > 0 else None
+        c.scale = self.scale
+        return c
+
+    def set_persistent(self, k_pers: torch.Tensor, v_pers: torch.Tensor) -> None:
+        """``[heads, Np, dh]`` keys/values of the persistent rows (identical for every sequence)."""
+        self.k_pers.copy_(k_pers)
+        self.v_pers.copy_(v_pers)
+
+    def fill(self, k: torch.Tensor, v: torch.Tensor, t0: int = 0) -> None:
+        """Load sequence K/V rows ``[B, H, rows, dh]`` (row i = token ``t0 + i``) into the ring."""
+        _require_cuda(k, v)
+        c = self.desc()
+        ks = (ctypes.c_int64 * 3)(*_bhrd_strides(k))
+        vs = (ctypes.c_int64 * 3)(*_bhrd_strides(v))
+        with torch.cuda.device(self.device):
+            check(lib().tmw_cache_fill(ctypes.byref(c), k.data_ptr(), v.data_ptr(), ks, vs, k.shape[2], t0,
+                                       _stream_ptr(self.device)))
+
+    def decode(self, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, pos: torch.Tensor,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One step: ``q, k_new, v_new [B, H, dh]``, ``pos [B] int32`` (token index of the new token)."""
+        _require_cuda(q, k_new, v_new, pos)
+        if pos.dtype != torch.int32:
+            raise TypeError("pos must be int32")
+        for t in (q, k_new, v_new):
+            if t.stride(2) != 1:
+                raise ValueError("the head_dim axis must be contiguous")
+        if k_new.stride()[:2] != v_new.stride()[:2]:
+            raise ValueError("k_new and v_new must share their strides")
+        if out is None:
+            out = torch.empty((self.batch, self.heads, self.head_dim), dtype=self.dtype, device=self.device)
+        c = self.desc()
+        qs = (ctypes.c_int64 * 2)(q.stride(0), q.stride(1))
+        ns = (ctypes.c_int64 * 2)(k_new.stride(0), k_new.stride(1))
+        os_ = (ctypes.c_int64 * 2)(out.stride(0), out.stride(1))
+        with torch.cuda.device(self.device):
+            check(lib().tmw_decode(ctypes.byref(c), q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+                                   out.data_ptr(), qs, ns, os_, pos.data_ptr(), _stream_ptr(self.device)))
+        return out
+
+
+def poll_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise the current stream and raise if a kernel reported an expired bounded wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        check(lib().tmw_poll_status(_stream_ptr(dev)))
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)
