@@ -1,8 +1,785 @@
-// placeholder until the tensor-core kernel lands
+// Tensor-core prefill kernel for B200: sliding-window attention with persistent prefix
+// keys on tcgen05 (5th-generation tensor cores) with accumulators in tensor memory.
+//
+// One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row query
+// tiles.  Its 12 warps have fixed roles:
+//   warps 0-3   softmax group of query tile 0      (one thread per query row)
+//   warps 4-7   softmax group of query tile 1
+//   warp  8     TMA producer: Q tiles, then the K tiles of the window
+//   warp  9     TMA producer: persistent K/V tile, then the V tiles of the window
+//   warp  10    issues every tcgen05.mma (one elected thread)
+//   warp  11    allocates / frees tensor memory
+// Key positions are cut into 128-key tiles anchored at (first query position - w), so
+// the second query tile always needs the same tiles shifted by one: both tiles share
+// every K/V tile that is loaded, and tiles that lie outside a query tile's window are
+// never multiplied.  The persistent keys are one extra, always-first tile kept in its
+// own shared-memory buffer.
+//
+// Per (query tile, key tile):  S = Q Kᵀ (fp32, tensor memory)  ->  the softmax group
+// reads its row of S, updates the running maximum lazily (the output accumulator in
+// tensor memory is only rescaled when the maximum grew by more than 2^8), writes
+// P = exp2(S·c - m) as 16-bit values back into tensor memory over S  ->  O += P V with P
+// read from tensor memory.  The two query tiles alternate on the tensor pipe, so one
+// tile's softmax overlaps the other tile's matrix products.
+//
+// Every wait on an mbarrier is bounded: on expiry the kernel records
+// TMW_ERR_DEVICE_TIMEOUT in the device status word, stops waiting anywhere and runs
+// to completion (with meaningless output) so that tensor memory is freed and the
+// context stays usable.
+#include <cuda.h>
+
+#include <cstdio>
+#include <mutex>
+
 #include "tmw_common.cuh"
+
 namespace tmw {
-bool prefill_tc_supports(const tmw_prefill_desc&, const void*, const void*, const void*, const void*) { return false; }
-int launch_prefill_tc(const tmw_prefill_desc&, const void*, const void*, const void*, void*, cudaStream_t) {
-    return TMW_ERR_UNSUPPORTED;
+namespace {
+
+constexpr int kThreadsTc = 384;
+constexpr int BM = 128;  // query rows per tile
+constexpr int BN = 128;  // keys per tile
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+
+// tensor-memory columns (32-bit each, 128 lanes): S0 | S1 | O0 | O1; P aliases S
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+
+struct TcParams {
+    int q_rows, k_rows, window, np, np_pad, q_pos0, k_pos0;
+    int dim_order;  // bit i set: tensor i (0=q,1=k,2=v,3=o) has its head axis before its row axis in the map
+    float scale_log2;
+    int* status;
+};
+
+// ---------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait.  `abort_flag` lives in shared memory; once it is set nobody waits any more.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try_wait(bar, parity)) return;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 63u) == 0u) {
+            if (*abort_flag) return;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = 1;
+                atomicExch(status, (int)TMW_ERR_DEVICE_TIMEOUT);
+                return;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait() {
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+#define TMW_R8(a, o)                                                                                        \
+    "=r"(a[o + 0]), "=r"(a[o + 1]), "=r"(a[o + 2]), "=r"(a[o + 3]), "=r"(a[o + 4]), "=r"(a[o + 5]),        \
+        "=r"(a[o + 6]), "=r"(a[o + 7])
+#define TMW_I8(a, o)                                                                                        \
+    "r"(a[o + 0]), "r"(a[o + 1]), "r"(a[o + 2]), "r"(a[o + 3]), "r"(a[o + 4]), "r"(a[o + 5]), "r"(a[o + 6]), \
+        "r"(a[o + 7])
+
+// 32 lanes x 32 consecutive columns: thread t of the warp gets lane (base lane + t)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : TMW_R8(r, 0), TMW_R8(r, 8), TMW_R8(r, 16), TMW_R8(r, 24)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), TMW_I8(r, 0), TMW_I8(r, 8)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), TMW_I8(r, 0), TMW_I8(r, 8), TMW_I8(r, 16), TMW_I8(r, 24)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+//   bits [0,14)  start address >> 4       bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4  bits [46,48) version = 1    bits [61,64) layout = 2 (SWIZZLE_128B)
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulate, A K-major; B K-major or MN-major.
+//   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
+//   [15] A major  [16] B major (1 = MN)  [17,23) N >> 3  [24,29) M >> 4
+__device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, uint32_t b_mn_major, uint32_t n) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (b_mn_major << 16) | ((n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------------
+// Schedule of one CTA, computed identically by every role
+// ---------------------------------------------------------------------------------
+struct QtPlan {
+    int p_lo;      // position of the tile's first query row
+    int rows;      // valid query rows (0: tile absent)
+    int has_pers;  // 1 if the persistent tile is item 0
+    int a;         // first window tile index
+    int n_win;     // number of window tiles
+    int n_items;   // has_pers + n_win
+};
+
+struct CtaPlan {
+    int anchor;  // position of key 0 of window tile 0
+    QtPlan qt[2];
+    int x_begin, x_end;  // window tiles [x_begin, x_end) are loaded
+};
+
+__device__ __forceinline__ int floor_div(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
+
+__device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block) {
+    CtaPlan c;
+    const int r0 = block * 2 * BM;
+    c.anchor = p.q_pos0 + r0 - p.window;
+    c.x_begin = 1 << 30;
+    c.x_end = 0;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        QtPlan& q = c.qt[t];
+        q.p_lo = p.q_pos0 + r0 + t * BM;
+        q.rows = max(0, min(BM, p.q_rows - (r0 + t * BM)));
+        q.has_pers = (q.rows > 0 && p.np > 0) ? 1 : 0;
+        const int p_hi = q.p_lo + q.rows - 1;
+        if (q.rows > 0 && p_hi >= p.np) {
+            const int g_lo = max(p.np, q.p_lo - p.window);
+            q.a = floor_div(g_lo - c.anchor, BN);
+            q.n_win = floor_div(p_hi - c.anchor, BN) - q.a + 1;
+            c.x_begin = min(c.x_begin, q.a);
+            c.x_end = max(c.x_end, q.a + q.n_win);
+        } else {
+            q.a = 0;
+            q.n_win = 0;
+        }
+        q.n_items = q.has_pers + q.n_win;
+    }
+    if (c.x_end == 0) c.x_begin = 0;
+    return c;
+}
+
+// Does query tile `t` multiply window tile x?  And in which turn?  Item index of window tile x is
+// x - a + has_pers; QK of item i is issued in turn (i - 1, t), PV of item i in turn (i, t); turns
+// are ordered by 2 * turn + t.
+__device__ __forceinline__ bool uses_tile(const QtPlan& q, int x) { return x >= q.a && x < q.a + q.n_win; }
+__device__ __forceinline__ int qk_order(const QtPlan& q, int t, int x) { return 2 * (x - q.a + q.has_pers - 1) + t; }
+__device__ __forceinline__ int pv_order(const QtPlan& q, int t, int x) { return 2 * (x - q.a + q.has_pers) + t; }
+
+// ---------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------
+template <int DH, int KS, int VS>
+struct TcSmem {
+    static constexpr int kTileBytes = BN * DH * 2;       // one K or V or Q tile
+    static constexpr int kSubTileBytes = BN * 128;       // 128 rows x 64 columns of 16-bit
+    static constexpr int kQ = 0;                         // 2 tiles
+    static constexpr int kK = kQ + 2 * kTileBytes;       // KS tiles
+    static constexpr int kV = kK + KS * kTileBytes;      // VS tiles
+    static constexpr int kP = kV + VS * kTileBytes;      // persistent K then V: np_pad x DH x 2 bytes each
+    static int total_bytes(int np_pad) { return kP + 2 * np_pad * DH * 2 + 1024 /*barriers*/ + 1024 /*alignment*/; }
+};
+
+// barrier slots inside the barrier area
+enum BarSlot {
+    BAR_Q_FULL = 0,        // [2]
+    BAR_KP_FULL = 2,       // persistent K and V
+    BAR_S_FULL = 3,        // [2]
+    BAR_P_READY = 5,       // [2]
+    BAR_O_DONE = 7,        // [2]
+    BAR_K_FULL = 9,        // [KS <= 4]
+    BAR_K_EMPTY = 13,      // [KS]
+    BAR_V_FULL = 17,       // [VS <= 4]
+    BAR_V_EMPTY = 21,      // [VS]
+    BAR_COUNT = 25
+};
+
+template <int DH, int KS, int VS, bool BF16>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                  const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                  const __grid_constant__ CUtensorMap map_kp, const __grid_constant__ CUtensorMap map_vp,
+                  const TcParams p) {
+    using L = TcSmem<DH, KS, VS>;
+    constexpr int NSUB = DH / 64;  // 64-column sub-tiles per tile
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t pers_bytes = (uint32_t)p.np_pad * DH * 2;
+    const uint32_t bar_base = smem_base + L::kP + 2 * pers_bytes;
+    uint8_t* bar_area = smem + L::kP + 2 * pers_bytes;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_area + BAR_COUNT * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_area + BAR_COUNT * 8 + 8);
+    auto bar = [&](int slot) -> uint32_t { return bar_base + slot * 8; };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int head = blockIdx.y, batch = blockIdx.z;
+    const CtaPlan plan = make_plan(p, blockIdx.x);
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar(BAR_Q_FULL + 0), 1);
+        mbar_init(bar(BAR_Q_FULL + 1), 1);
+        mbar_init(bar(BAR_KP_FULL), 1);
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(bar(BAR_S_FULL + t), 1);
+            mbar_init(bar(BAR_P_READY + t), BM);
+            mbar_init(bar(BAR_O_DONE + t), 1);
+        }
+        for (int s = 0; s < KS; ++s) {
+            mbar_init(bar(BAR_K_FULL + s), 1);
+            mbar_init(bar(BAR_K_EMPTY + s), 1);
+        }
+        for (int s = 0; s < VS; ++s) {
+            mbar_init(bar(BAR_V_FULL + s), 1);
+            mbar_init(bar(BAR_V_EMPTY + s), 1);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 11) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // coordinate order of each tensor map: (dh, rows, heads, batch) or (dh, heads, rows, batch)
+    auto coords = [&](int which, int row, int& c1, int& c2) {
+        if ((p.dim_order >> which) & 1) { c1 = head; c2 = row; } else { c1 = row; c2 = head; }
+    };
+
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory");
+        if (warp == 8 && lane == 0) {
+            // ---------------- producer: Q tiles, then K tiles ----------------
+            for (int t = 0; t < 2; ++t) {
+                if (plan.qt[t].rows == 0) continue;
+                mbar_expect_tx(bar(BAR_Q_FULL + t), L::kTileBytes);
+                int c1, c2;
+                coords(0, blockIdx.x * 2 * BM + t * BM, c1, c2);
+                for (int s = 0; s < NSUB; ++s)
+                    tma_load_4d(smem_base + L::kQ + t * L::kTileBytes + s * L::kSubTileBytes, &map_q,
+                                bar(BAR_Q_FULL + t), s * 64, c1, c2, batch);
+            }
+            int n = 0;
+            for (int x = plan.x_begin; x < plan.x_end; ++x, ++n) {
+                const int s = n % KS;
+                mbar_wait(bar(BAR_K_EMPTY + s), ((n / KS) & 1) ^ 1, abort_flag, p.status);
+                mbar_expect_tx(bar(BAR_K_FULL + s), L::kTileBytes);
+                int c1, c2;
+                coords(1, p.np + plan.anchor + x * BN - p.k_pos0, c1, c2);
+                for (int u = 0; u < NSUB; ++u)
+                    tma_load_4d(smem_base + L::kK + s * L::kTileBytes + u * L::kSubTileBytes, &map_k,
+                                bar(BAR_K_FULL + s), u * 64, c1, c2, batch);
+            }
+        } else if (warp == 9 && lane == 0) {
+            // ---------------- producer: persistent K/V, then V tiles ----------------
+            if (p.np > 0) {
+                mbar_expect_tx(bar(BAR_KP_FULL), 2 * pers_bytes);
+                int c1, c2;
+                coords(1, 0, c1, c2);
+                for (int u = 0; u < NSUB; ++u)
+                    tma_load_4d(smem_base + L::kP + u * p.np_pad * 128, &map_kp, bar(BAR_KP_FULL), u * 64, c1, c2, batch);
+                coords(2, 0, c1, c2);
+                for (int u = 0; u < NSUB; ++u)
+                    tma_load_4d(smem_base + L::kP + pers_bytes + u * p.np_pad * 128, &map_vp, bar(BAR_KP_FULL), u * 64,
+                                c1, c2, batch);
+            }
+            int n = 0;
+            for (int x = plan.x_begin; x < plan.x_end; ++x, ++n) {
+                const int s = n % VS;
+                mbar_wait(bar(BAR_V_EMPTY + s), ((n / VS) & 1) ^ 1, abort_flag, p.status);
+                mbar_expect_tx(bar(BAR_V_FULL + s), L::kTileBytes);
+                int c1, c2;
+                coords(2, p.np + plan.anchor + x * BN - p.k_pos0, c1, c2);
+                for (int u = 0; u < NSUB; ++u)
+                    tma_load_4d(smem_base + L::kV + s * L::kTileBytes + u * L::kSubTileBytes, &map_v,
+                                bar(BAR_V_FULL + s), u * 64, c1, c2, batch);
+            }
+        } else if (warp == 10 && lane == 0) {
+            // ---------------- tensor-core issue ----------------
+            const uint32_t fmt = BF16 ? 1u : 0u;
+            const uint32_t idesc_qk_win = make_idesc(fmt, 0, BN);
+            const uint32_t idesc_qk_pers = make_idesc(fmt, 0, (uint32_t)max(p.np_pad, 16));
+            const uint32_t idesc_pv = make_idesc(fmt, 1, DH);
+            const uint32_t col_s[2] = {kColS0, kColS1};
+            const uint32_t col_o[2] = {kColO0, kColO1};
+            int k_confirmed = plan.x_begin;  // window tiles < k_confirmed are known to be in shared memory
+            int v_confirmed = plan.x_begin;
+            bool pers_confirmed = false;
+
+            auto issue_qk = [&](int t, int item) {
+                const QtPlan& q = plan.qt[t];
+                const uint32_t q_addr = smem_base + L::kQ + t * L::kTileBytes;
+                uint32_t b_addr, b_sub, idesc;
+                int x = -1;
+                if (item < q.has_pers) {
+                    if (!pers_confirmed) {
+                        mbar_wait(bar(BAR_KP_FULL), 0, abort_flag, p.status);
+                        pers_confirmed = true;
+                    }
+                    b_addr = smem_base + L::kP;
+                    b_sub = (uint32_t)p.np_pad * 128;
+                    idesc = idesc_qk_pers;
+                } else {
+                    x = q.a + item - q.has_pers;
+                    while (k_confirmed <= x) {
+                        const int n = k_confirmed - plan.x_begin;
+                        mbar_wait(bar(BAR_K_FULL + n % KS), (n / KS) & 1, abort_flag, p.status);
+                        ++k_confirmed;
+                    }
+                    b_addr = smem_base + L::kK + ((x - plan.x_begin) % KS) * L::kTileBytes;
+                    b_sub = L::kSubTileBytes;
+                    idesc = idesc_qk_win;
+                }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < DH / 16; ++kk) {
+                    const uint64_t a_desc = make_desc(q_addr + (kk / 4) * L::kSubTileBytes + (kk % 4) * 32, 16, 1024);
+                    const uint64_t b_desc = make_desc(b_addr + (kk / 4) * b_sub + (kk % 4) * 32, 16, 1024);
+                    mma_ss(tmem_base + col_s[t], a_desc, b_desc, idesc, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(bar(BAR_S_FULL + t));
+                if (x >= 0) {
+                    const QtPlan& o = plan.qt[t ^ 1];
+                    const bool other_later = uses_tile(o, x) && qk_order(o, t ^ 1, x) > qk_order(q, t, x);
+                    if (!other_later) tc_commit(bar(BAR_K_EMPTY + (x - plan.x_begin) % KS));
+                }
+            };
+
+            auto issue_pv = [&](int t, int item) {
+                const QtPlan& q = plan.qt[t];
+                uint32_t b_addr, lbo;
+                int ksteps, x = -1;
+                if (item < q.has_pers) {
+                    b_addr = smem_base + L::kP + pers_bytes;
+                    lbo = (uint32_t)p.np_pad * 128;
+                    ksteps = p.np_pad / 16;
+                } else {
+                    x = q.a + item - q.has_pers;
+                    while (v_confirmed <= x) {
+                        const int n = v_confirmed - plan.x_begin;
+                        mbar_wait(bar(BAR_V_FULL + n % VS), (n / VS) & 1, abort_flag, p.status);
+                        ++v_confirmed;
+                    }
+                    b_addr = smem_base + L::kV + ((x - plan.x_begin) % VS) * L::kTileBytes;
+                    lbo = L::kSubTileBytes;
+                    ksteps = BN / 16;
+                }
+                tc_fence_after();
+                for (int kk = 0; kk < ksteps; ++kk) {
+                    // B = V tile, MN-major: 16 keys = two 8-row groups of 1024 bytes per k-step
+                    const uint64_t b_desc = make_desc(b_addr + kk * 2048, lbo, 1024);
+                    mma_ts(tmem_base + col_o[t], tmem_base + col_s[t] + kk * 8, b_desc, idesc_pv,
+                           (item > 0 || kk > 0) ? 1u : 0u);
+                }
+                if (x >= 0) {
+                    const QtPlan& o = plan.qt[t ^ 1];
+                    const bool other_later = uses_tile(o, x) && pv_order(o, t ^ 1, x) > pv_order(q, t, x);
+                    if (!other_later) tc_commit(bar(BAR_V_EMPTY + (x - plan.x_begin) % VS));
+                }
+            };
+
+            for (int t = 0; t < 2; ++t) {
+                if (plan.qt[t].n_items == 0) continue;
+                mbar_wait(bar(BAR_Q_FULL + t), 0, abort_flag, p.status);
+                issue_qk(t, 0);
+            }
+            const int max_items = max(plan.qt[0].n_items, plan.qt[1].n_items);
+            for (int i = 0; i < max_items; ++i) {
+                for (int t = 0; t < 2; ++t) {
+                    if (i >= plan.qt[t].n_items) continue;
+                    mbar_wait(bar(BAR_P_READY + t), i & 1, abort_flag, p.status);
+                    issue_pv(t, i);
+                    if (i + 1 < plan.qt[t].n_items) issue_qk(t, i + 1);
+                    else tc_commit(bar(BAR_O_DONE + t));
+                }
+            }
+        }
+    } else {
+        // ---------------- softmax groups ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
+        const int t = warp >> 2;                       // query tile of this group
+        const int row = threadIdx.x & (BM - 1);        // row of the tile == tensor-memory lane
+        const QtPlan& q = plan.qt[t];
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        const uint32_t s_addr = tmem_base + lane_addr + (t == 0 ? kColS0 : kColS1);
+        const uint32_t o_addr = tmem_base + lane_addr + (t == 0 ? kColO0 : kColO1);
+        const int pos = q.p_lo + row;
+        float m_used = -INFINITY;  // maximum the stored P and O are relative to (log2 domain)
+        float l_sum = 0.f;
+
+        for (int item = 0; item < q.n_items; ++item) {
+            // visible columns of this row inside the tile: [j_lo, j_hi]
+            int j_lo, j_hi, ncols;
+            bool full;
+            if (item < q.has_pers) {
+                j_lo = 0;
+                j_hi = p.np - 1;
+                ncols = p.np_pad;
+                full = false;
+            } else {
+                const int g0 = plan.anchor + (q.a + item - q.has_pers) * BN;
+                if (pos >= p.np) {
+                    j_lo = max(p.np, pos - p.window) - g0;
+                    j_hi = pos - g0;
+                } else {
+                    j_lo = 1;
+                    j_hi = 0;
+                }
+                ncols = BN;
+                // every row of the tile sees every key of the tile (decided per tile, not per row)
+                full = q.p_lo >= p.np && g0 >= p.np && g0 + BN - 1 <= q.p_lo && q.p_lo + BM - 1 - g0 <= p.window;
+            }
+            const int nchunks = (ncols + 31) / 32;
+
+            mbar_wait(bar(BAR_S_FULL + t), item & 1, abort_flag, p.status);
+            tc_fence_after();
+
+            uint32_t s[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (c < nchunks) tmem_ld32(s_addr + c * 32, s[c]);
+            tc_wait_ld();
+
+            float tile_max = -INFINITY;
+            if (full) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(s[c][j]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (c < nchunks) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int col = c * 32 + j;
+                            const float val = (col >= j_lo && col <= j_hi) ? __uint_as_float(s[c][j]) : -INFINITY;
+                            s[c][j] = __float_as_uint(val);
+                            tile_max = fmaxf(tile_max, val);
+                        }
+                    }
+            }
+            tile_max *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
+
+            // lazy maximum: keep the old reference unless the new maximum is more than 2^8 above it
+            const bool grow = tile_max > m_used + 8.0f;
+            if (item == 0) {
+                m_used = tile_max;
+            } else if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = fmaxf(m_used, tile_max);
+                const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_used - m_new);
+                m_used = m_new;
+                l_sum *= alpha;
+#pragma unroll
+                for (int c = 0; c < DH / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_ld32(o_addr + c * 32, o);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                    tmem_st32(o_addr + c * 32, o);
+                }
+            }
+
+            // P = exp2(S * c - m), packed two 16-bit values per column, written over S
+            const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (c < nchunks) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float e0 = fast_exp2(fmaf(__uint_as_float(s[c][j]), p.scale_log2, neg_m));
+                        const float e1 = fast_exp2(fmaf(__uint_as_float(s[c][j + 1]), p.scale_log2, neg_m));
+                        l_sum += e0 + e1;
+                        if (BF16) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+                            packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h);
+                        } else {
+                            const __half2 h = __floats2half2_rn(e0, e1);
+                            packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                    }
+                    tmem_st16(s_addr + c * 16, packed);
+                }
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(BAR_P_READY + t));
+        }
+
+        if (q.n_items > 0) {
+            // ---------------- epilogue: O / l -> shared memory (swizzled) -> TMA store ----------------
+            mbar_wait(bar(BAR_O_DONE + t), 0, abort_flag, p.status);
+            tc_fence_after();
+            const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            uint8_t* stage = smem + L::kQ + t * L::kTileBytes;  // the Q tile is no longer needed
+#pragma unroll
+            for (int c = 0; c < DH / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(o_addr + c * 32, o);
+                tc_wait_ld();
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {  // 8 columns = one 16-byte chunk
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float a = __uint_as_float(o[g * 8 + 2 * e]) * inv;
+                        const float b = __uint_as_float(o[g * 8 + 2 * e + 1]) * inv;
+                        if (BF16) {
+                            const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        } else {
+                            const __half2 h = __floats2half2_rn(a, b);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&h);
+                        }
+                    }
+                    const int col = c * 32 + g * 8;          // first column of the chunk
+                    const int sub = col / 64;                // 64-column sub-tile
+                    const int chunk = (col % 64) / 8;        // 16-byte chunk inside the 128-byte row
+                    uint8_t* dst = stage + sub * L::kSubTileBytes + row * 128 + ((chunk ^ (row & 7)) * 16);
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(1 + t, BM);
+            if (row == 0) {
+                int c1, c2;
+                coords(3, blockIdx.x * 2 * BM + t * BM, c1, c2);
+                for (int u = 0; u < NSUB; ++u)
+                    tma_store_4d(&map_o, smem_u32(stage + u * L::kSubTileBytes), u * 64, c1, c2, batch);
+                tma_store_commit_and_wait();
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 11) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// Host side: tensor maps and launch
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// Map over a [batch, heads, rows, dh] tensor given by element strides {batch, head, row}; the two
+// middle axes are ordered by stride.  Returns false on failure; sets *heads_first.
+bool make_map(CUtensorMap* map, const void* base, int dtype, int batch, int heads, int rows, int dh,
+              const int64_t stride[3], int box_rows, bool* heads_first) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    // a stride of an extent-1 axis is never used for addressing; give it a harmless valid value
+    const int64_t row_stride = rows > 1 ? stride[2] : dh;
+    const int64_t head_stride = heads > 1 ? stride[1] : row_stride * rows;
+    const int64_t inner_span = head_stride * heads > row_stride * rows ? head_stride * heads : row_stride * rows;
+    const int64_t batch_stride = batch > 1 ? stride[0] : inner_span;
+    *heads_first = head_stride < row_stride;
+    cuuint64_t dims[4];
+    cuuint64_t strides[3];
+    cuuint32_t box[4];
+    dims[0] = (cuuint64_t)dh;
+    box[0] = 64;
+    if (*heads_first) {
+        dims[1] = (cuuint64_t)heads; strides[0] = (cuuint64_t)head_stride * 2; box[1] = 1;
+        dims[2] = (cuuint64_t)rows;  strides[1] = (cuuint64_t)row_stride * 2;  box[2] = (cuuint32_t)box_rows;
+    } else {
+        dims[1] = (cuuint64_t)rows;  strides[0] = (cuuint64_t)row_stride * 2;  box[1] = (cuuint32_t)box_rows;
+        dims[2] = (cuuint64_t)heads; strides[1] = (cuuint64_t)head_stride * 2; box[2] = 1;
+    }
+    dims[3] = (cuuint64_t)batch;
+    strides[2] = (cuuint64_t)batch_stride * 2;
+    box[3] = 1;
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType dt = dtype == TMW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, elem_strides,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char text[96];
+        snprintf(text, sizeof(text), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        set_error_text(text);
+        return false;
+    }
+    return true;
+}
+
+int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
+
+template <int DH, int KS, int VS>
+int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream) {
+    using L = TcSmem<DH, KS, VS>;
+    const int np_pad = np_pad_of(d.n_persistent);
+    CUtensorMap mq, mk, mv, mo, mkp, mvp;
+    bool hf[4] = {false, false, false, false}, hf_p[2];
+    if (!make_map(&mq, q, d.dtype, d.batch, d.heads, d.q_rows, DH, d.q_stride, BM, &hf[0]) ||
+        !make_map(&mk, k, d.dtype, d.batch, d.heads, d.k_rows, DH, d.k_stride, BN, &hf[1]) ||
+        !make_map(&mv, v, d.dtype, d.batch, d.heads, d.k_rows, DH, d.v_stride, BN, &hf[2]) ||
+        !make_map(&mo, o, d.dtype, d.batch, d.heads, d.q_rows, DH, d.o_stride, BM, &hf[3]) ||
+        !make_map(&mkp, k, d.dtype, d.batch, d.heads, d.k_rows, DH, d.k_stride, np_pad > 0 ? np_pad : 16, &hf_p[0]) ||
+        !make_map(&mvp, v, d.dtype, d.batch, d.heads, d.k_rows, DH, d.v_stride, np_pad > 0 ? np_pad : 16, &hf_p[1]))
+        return TMW_ERR_CUDA;
+    TcParams p;
+    p.q_rows = d.q_rows; p.k_rows = d.k_rows; p.window = d.window; p.np = d.n_persistent; p.np_pad = np_pad;
+    p.q_pos0 = d.q_pos0; p.k_pos0 = d.k_pos0;
+    p.dim_order = (hf[0] ? 1 : 0) | (hf[1] ? 2 : 0) | (hf[2] ? 4 : 0) | (hf[3] ? 8 : 0);
+    const float scale = d.scale != 0.f ? d.scale : 1.0f / sqrtf((float)DH);
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = device_status_word();
+    if (p.status == nullptr) return TMW_ERR_CUDA;
+    const int smem_bytes = L::total_bytes(np_pad);
+    dim3 grid((d.q_rows + 2 * BM - 1) / (2 * BM), d.heads, d.batch);
+    if (d.dtype == TMW_BF16) {
+        auto kern = prefill_tc_kernel<DH, KS, VS, true>;
+        TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        kern<<<grid, kThreadsTc, smem_bytes, stream>>>(mq, mk, mv, mo, mkp, mvp, p);
+    } else {
+        auto kern = prefill_tc_kernel<DH, KS, VS, false>;
+        TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        kern<<<grid, kThreadsTc, smem_bytes, stream>>>(mq, mk, mv, mo, mkp, mvp, p);
+    }
+    TMW_CUDA_TRY(cudaGetLastError());
+    return TMW_OK;
+}
+
+constexpr int kMaxDynamicSmem = 232448;  // 227 KB per CTA on sm_100
+
+}  // namespace
+
+bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, const void*, const void*) {
+    if (d.dtype != TMW_BF16 && d.dtype != TMW_F16) return false;
+    if (d.head_dim != 64 && d.head_dim != 128) return false;
+    if (d.batch > 65535 || d.heads > 65535) return false;
+    const int np_pad = np_pad_of(d.n_persistent);
+    if (np_pad > 128) return false;
+    const int need = d.head_dim == 64 ? TcSmem<64, 3, 3>::total_bytes(np_pad) : TcSmem<128, 2, 2>::total_bytes(np_pad);
+    if (need > kMaxDynamicSmem) return false;
+    // positions are combined in 32-bit arithmetic inside the kernel
+    if ((int64_t)d.q_pos0 + d.q_rows + d.window + 4 * BN >= (int64_t)1 << 30) return false;
+    return true;
+}
+
+int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
+                      cudaStream_t stream) {
+    if (d.head_dim == 64) return launch_tc<64, 3, 3>(d, q, k, v, o, stream);
+    return launch_tc<128, 2, 2>(d, q, k, v, o, stream);
+}
+
 }  // namespace tmw
