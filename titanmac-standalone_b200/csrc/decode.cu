@@ -5,7 +5,11 @@
 // one 16-byte load each, a warp covers 32/(head_dim/8) rows per load instruction and
 // keeps UNROLL such instructions in flight for K and for V before it touches the
 // softmax.  Dot products are finished with warp shuffles; each lane group keeps a
-// private online-softmax state that is merged across groups and warps at the end.
+// private online-softmax state that is merged across groups (and warps) at the end.
+//
+// Two launch shapes share the code: with many (sequence, head) pairs every pair gets
+// ONE warp (no block-level merge, all pairs resident at once, so no wave
+// quantisation); with few pairs a whole CTA of 8 warps shares one pair.
 #include <math_constants.h>
 
 #include "tmw_common.cuh"
@@ -13,9 +17,6 @@
 namespace tmw {
 namespace {
 
-constexpr int kDecodeThreads = 128;
-constexpr int kDecodeWarps = kDecodeThreads / 32;
-constexpr int UNROLL = 4;
 
 struct DecodeParams {
     void* k_ring;
@@ -28,20 +29,79 @@ struct DecodeParams {
     void* o;
     const int32_t* pos;
     long long qs[2], ns[2], os[2];
-    int heads, slots, np;
+    int batch, heads, slots, np;
     float scale_log2;
 };
 
-// LPK = lanes per key row = DH / 8
-template <typename T, int DH>
-__global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const DecodeParams p) {
-    constexpr int LPK = DH / 8;
-    constexpr int RPW = 32 / LPK;                 // key rows per warp per load instruction
-    constexpr int STEP = RPW * kDecodeWarps;      // key rows per CTA per load instruction
+// 8 consecutive elements as raw bits, loaded through the read-only path without keeping
+// the line in L1 (every ring byte is read exactly once per step).
+template <typename T>
+struct Raw8;
+template <>
+struct Raw8<float> {
+    uint4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p));
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(p + 4));
+    }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+        f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y); f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+    }
+};
+template <>
+struct Raw8<__nv_bfloat16> {
+    uint4 a;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p));
+    }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+template <>
+struct Raw8<__half> {
+    uint4 a;
+    __device__ __forceinline__ void load(const __half* p) {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(p));
+    }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        const __half2* h = reinterpret_cast<const __half2*>(&a);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 t = __half22float2(h[i]);
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        }
+    }
+};
+
+// WARPS = warps that share one (sequence, head) pair; a CTA holds 2 pairs when WARPS == 1, and nine
+// such CTAs fit on an SM (register bound), i.e. 2664 pairs are resident at once on 148 SMs.
+template <typename T, int DH, int WARPS>
+__global__ void __launch_bounds__(WARPS == 1 ? 64 : WARPS * 32, WARPS == 1 ? 9 : 1) decode_kernel(const DecodeParams p) {
+    // 16-byte loads in flight per lane for K, and again for V; fewer when one warp owns a pair, because
+    // then 18 warps per SM are resident and the register budget per thread is 112
+    constexpr int UNROLL = (WARPS == 1 ? 4 : 8) / (sizeof(T) == 4 ? 2 : 1);
+    constexpr int LPK = DH / 8;       // lanes per key row
+    constexpr int RPW = 32 / LPK;     // key rows per warp per load instruction
+    constexpr int STRIDE = RPW * WARPS;
     static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "head_dim must be 8 * 2^n, at most 256");
 
-    const int h = blockIdx.x, b = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pair = WARPS == 1 ? blockIdx.x * 2 + warp : blockIdx.x;
+    if (pair >= p.batch * p.heads) return;  // whole warps leave together; no block barrier when WARPS == 1
+    const int b = pair / p.heads, h = pair % p.heads;
+    const int wslot = WARPS == 1 ? 0 : warp;  // which share of the keys this warp scans
     const int sub = lane % LPK;  // which 8-element slice of the row
     const int grp = lane / LPK;  // which row of the warp's RPW rows
 
@@ -53,38 +113,42 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const DecodePara
     T* vr = static_cast<T*>(p.v_ring) + ring_bh;
     const T* kp = static_cast<const T*>(p.k_pers) + (long long)h * p.np * DH;
     const T* vp = static_cast<const T*>(p.v_pers) + (long long)h * p.np * DH;
+    const T* kn = static_cast<const T*>(p.k_new) + b * p.ns[0] + h * p.ns[1];
+    const T* vn = static_cast<const T*>(p.v_new) + b * p.ns[0] + h * p.ns[1];
 
-    // 1. the new token's key and value go into their slot first
-    if (tid < 2 * LPK) {
-        const int c = tid % LPK;
-        const bool is_v = tid >= LPK;
-        const T* src = static_cast<const T*>(is_v ? p.v_new : p.k_new) + b * p.ns[0] + h * p.ns[1] + c * 8;
-        T* dst = (is_v ? vr : kr) + (long long)slot_new * DH + c * 8;
-        float tmp[8];
-        load8<T>(src, tmp);
-        store8<T>(dst, tmp);
-    }
     float qreg[8];
     load8<T>(static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1] + sub * 8, qreg);
-    __syncthreads();  // the slot written above is read below by other threads of this CTA
 
+    // Virtual key index i: [0, np) persistent keys, np = the new token (read from k_new / v_new, so the
+    // ring slot written below is never read back), then the count-1 older ring slots in slot order.
+    const int n_keys = p.np + count;
     float m = -CUDART_INF_F, l = 0.f;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const int n_keys = p.np + count;
 
-    for (int i0 = 0; i0 < n_keys; i0 += STEP * UNROLL) {
-        float kf[UNROLL][8], vf[UNROLL][8];
+    for (int i0 = 0; i0 < n_keys; i0 += STRIDE * UNROLL) {
+        Raw8<T> kraw[UNROLL], vraw[UNROLL];
         bool ok[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int i = i0 + u * STEP + warp * RPW + grp;
+            const int i = i0 + u * STRIDE + wslot * RPW + grp;
             ok[u] = i < n_keys;
-            const int ii = ok[u] ? i : 0;
-            const T* ksrc = ii < p.np ? kp + (long long)ii * DH : kr + (long long)(ii - p.np) * DH;
-            const T* vsrc = ii < p.np ? vp + (long long)ii * DH : vr + (long long)(ii - p.np) * DH;
             if (ok[u]) {
-                load8<T>(ksrc + sub * 8, kf[u]);
-                load8<T>(vsrc + sub * 8, vf[u]);
+                const T* ksrc;
+                const T* vsrc;
+                if (i < p.np) {
+                    ksrc = kp + (long long)i * DH;
+                    vsrc = vp + (long long)i * DH;
+                } else if (i == p.np) {
+                    ksrc = kn;
+                    vsrc = vn;
+                } else {
+                    const int j = i - p.np - 1;
+                    const int slot = j < slot_new ? j : j + 1;
+                    ksrc = kr + (long long)slot * DH;
+                    vsrc = vr + (long long)slot * DH;
+                }
+                kraw[u].load(ksrc + sub * 8);
+                vraw[u].load(vsrc + sub * 8);
             }
         }
         float s[UNROLL];
@@ -93,8 +157,10 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const DecodePara
         for (int u = 0; u < UNROLL; ++u) {
             float part = 0.f;
             if (ok[u]) {
+                float kf[8];
+                kraw[u].unpack(kf);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) part = fmaf(qreg[e], kf[u][e], part);
+                for (int e = 0; e < 8; ++e) part = fmaf(qreg[e], kf[e], part);
             }
 #pragma unroll
             for (int off = 1; off < LPK; off <<= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
@@ -113,14 +179,25 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const DecodePara
                 if (ok[u]) {
                     const float pj = exp2f(s[u] - m);
                     l += pj;
+                    float vf[8];
+                    vraw[u].unpack(vf);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] = fmaf(pj, vf[u][e], acc[e]);
+                    for (int e = 0; e < 8; ++e) acc[e] = fmaf(pj, vf[e], acc[e]);
                 }
             }
         }
     }
 
-    // 2. merge the RPW lane groups of the warp (lanes that hold the same slice)
+    // the new token's key and value go into their ring slot for the following steps
+    if (wslot == 0 && grp == 0) {
+        float tmp[8];
+        load8<T>(kn + sub * 8, tmp);
+        store8<T>(kr + (long long)slot_new * DH + sub * 8, tmp);
+        load8<T>(vn + sub * 8, tmp);
+        store8<T>(vr + (long long)slot_new * DH + sub * 8, tmp);
+    }
+
+    // merge the RPW lane groups of the warp (lanes that hold the same slice)
 #pragma unroll
     for (int off = LPK; off < 32; off <<= 1) {
         const float m_o = __shfl_xor_sync(0xffffffffu, m, off);
@@ -137,35 +214,46 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const DecodePara
         m = m_new;
     }
 
-    // 3. merge the warps through shared memory
-    __shared__ float sm_m[kDecodeWarps], sm_l[kDecodeWarps];
-    __shared__ float sm_acc[kDecodeWarps][DH];
-    if (grp == 0) {
+    T* out = static_cast<T*>(p.o) + b * p.os[0] + h * p.os[1];
+    if (WARPS == 1) {
+        if (grp == 0) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float res[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) sm_acc[warp][sub * 8 + e] = acc[e];
-        if (sub == 0) {
-            sm_m[warp] = m;
-            sm_l[warp] = l;
+            for (int e = 0; e < 8; ++e) res[e] = acc[e] * inv;
+            store8<T>(out + sub * 8, res);
         }
-    }
-    __syncthreads();
-    if (tid < LPK) {
-        float m_all = -CUDART_INF_F;
+    } else {
+        // merge the warps through shared memory
+        __shared__ float sm_m[WARPS], sm_l[WARPS];
+        __shared__ float sm_acc[WARPS][DH];
+        if (grp == 0) {
 #pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) m_all = fmaxf(m_all, sm_m[w]);
-        float l_all = 0.f;
-        float out[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) {
-            const float a = sm_m[w] > -CUDART_INF_F ? exp2f(sm_m[w] - m_all) : 0.f;
-            l_all += sm_l[w] * a;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) out[e] += sm_acc[w][tid * 8 + e] * a;
+            for (int e = 0; e < 8; ++e) sm_acc[warp][sub * 8 + e] = acc[e];
+            if (sub == 0) {
+                sm_m[warp] = m;
+                sm_l[warp] = l;
+            }
         }
-        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        __syncthreads();
+        if (tid < LPK) {
+            float m_all = -CUDART_INF_F;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) out[e] *= inv;
-        store8<T>(static_cast<T*>(p.o) + b * p.os[0] + h * p.os[1] + tid * 8, out);
+            for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, sm_m[w]);
+            float l_all = 0.f;
+            float res[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const float a = sm_m[w] > -CUDART_INF_F ? exp2f(sm_m[w] - m_all) : 0.f;
+                l_all += sm_l[w] * a;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) res[e] += sm_acc[w][tid * 8 + e] * a;
+            }
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) res[e] *= inv;
+            store8<T>(out + tid * 8, res);
+        }
     }
 }
 
@@ -197,20 +285,32 @@ __global__ void cache_fill_kernel(const FillParams p) {
     }
 }
 
-template <typename T>
-int launch_decode_dh(const DecodeParams& p, int batch, int heads, int dh, cudaStream_t stream) {
-    dim3 grid(heads, batch);
-    switch (dh) {
-        case 8: decode_kernel<T, 8><<<grid, kDecodeThreads, 0, stream>>>(p); break;
-        case 16: decode_kernel<T, 16><<<grid, kDecodeThreads, 0, stream>>>(p); break;
-        case 32: decode_kernel<T, 32><<<grid, kDecodeThreads, 0, stream>>>(p); break;
-        case 64: decode_kernel<T, 64><<<grid, kDecodeThreads, 0, stream>>>(p); break;
-        case 128: decode_kernel<T, 128><<<grid, kDecodeThreads, 0, stream>>>(p); break;
-        case 256: decode_kernel<T, 256><<<grid, kDecodeThreads, 0, stream>>>(p); break;
-        default: return TMW_ERR_UNSUPPORTED;
+constexpr int kCtaWarps = 8;
+
+template <typename T, int DH>
+int launch_decode_shape(const DecodeParams& p, cudaStream_t stream) {
+    const int pairs = p.batch * p.heads;
+    // enough pairs to give every SM a dozen warps: one warp per pair; otherwise a CTA per pair
+    if (pairs >= 1536) {
+        decode_kernel<T, DH, 1><<<(pairs + 1) / 2, 64, 0, stream>>>(p);
+    } else {
+        decode_kernel<T, DH, kCtaWarps><<<pairs, kCtaWarps * 32, 0, stream>>>(p);
     }
     TMW_CUDA_TRY(cudaGetLastError());
     return TMW_OK;
+}
+
+template <typename T>
+int launch_decode_dh(const DecodeParams& p, int dh, cudaStream_t stream) {
+    switch (dh) {
+        case 8: return launch_decode_shape<T, 8>(p, stream);
+        case 16: return launch_decode_shape<T, 16>(p, stream);
+        case 32: return launch_decode_shape<T, 32>(p, stream);
+        case 64: return launch_decode_shape<T, 64>(p, stream);
+        case 128: return launch_decode_shape<T, 128>(p, stream);
+        case 256: return launch_decode_shape<T, 256>(p, stream);
+        default: return TMW_ERR_UNSUPPORTED;
+    }
 }
 
 }  // namespace
@@ -219,18 +319,18 @@ int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, con
                   const int64_t qs[2], const int64_t ns[2], const int64_t os[2], const int32_t* pos,
                   cudaStream_t stream) {
     if (c.batch == 0 || c.heads == 0) return TMW_OK;
-    if (c.batch > 65535) return TMW_ERR_TOO_LARGE;
+    if ((long long)c.batch * c.heads > (1LL << 30)) return TMW_ERR_TOO_LARGE;
     DecodeParams p;
     p.k_ring = c.k_ring; p.v_ring = c.v_ring; p.k_pers = c.k_pers; p.v_pers = c.v_pers;
     p.q = q; p.k_new = k_new; p.v_new = v_new; p.o = o; p.pos = pos;
     for (int i = 0; i < 2; ++i) { p.qs[i] = qs[i]; p.ns[i] = ns[i]; p.os[i] = os[i]; }
-    p.heads = c.heads; p.slots = c.window + 1; p.np = c.n_persistent;
+    p.batch = c.batch; p.heads = c.heads; p.slots = c.window + 1; p.np = c.n_persistent;
     const float scale = c.scale != 0.f ? c.scale : 1.0f / sqrtf((float)c.head_dim);
     p.scale_log2 = scale * 1.4426950408889634f;
     switch (c.dtype) {
-        case TMW_F32: return launch_decode_dh<float>(p, c.batch, c.heads, c.head_dim, stream);
-        case TMW_BF16: return launch_decode_dh<__nv_bfloat16>(p, c.batch, c.heads, c.head_dim, stream);
-        case TMW_F16: return launch_decode_dh<__half>(p, c.batch, c.heads, c.head_dim, stream);
+        case TMW_F32: return launch_decode_dh<float>(p, c.head_dim, stream);
+        case TMW_BF16: return launch_decode_dh<__nv_bfloat16>(p, c.head_dim, stream);
+        case TMW_F16: return launch_decode_dh<__half>(p, c.head_dim, stream);
         default: return TMW_ERR_UNSUPPORTED;
     }
 }

@@ -30,6 +30,7 @@
 
 #include <cstdio>
 #include <mutex>
+#include <type_traits>
 
 #include "tmw_common.cuh"
 
@@ -40,10 +41,19 @@ constexpr int kThreadsTc = 384;
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per tile
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+constexpr int kPolyOf4 = 2;  // of every 4 column pairs, how many take the polynomial exp2
 
 // tensor-memory columns (32-bit each, 128 lanes): S0 | S1 | O0 | O1; P aliases S
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+
+#ifdef TMW_TRACE
+// Build-time instrumentation (never part of the shipped library): clock stamps of one CTA.
+__device__ long long g_trace[4096];
+#define TRACE(slot) do { if (trace_on) g_trace[(slot)] = clock64(); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#endif
 
 struct TcParams {
     int q_rows, k_rows, window, np, np_pad, q_pos0, k_pos0;
@@ -122,6 +132,54 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// two fp32 values in one 64-bit register, for the packed f32x2 arithmetic of sm_100
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// exp2 of two values on the FMA pipe instead of the MUFU unit: round to the nearest integer j with
+// the 1.5 * 2^23 trick, evaluate a cubic for 2^f on f = x - j in [-0.5, 0.5] (relative error 7.5e-5,
+// far below the 16-bit rounding of P) and add j to the exponent field.  x is clamped at -126.
+__device__ __forceinline__ uint64_t poly_exp2_x2(uint64_t x) {
+    float x0, x1;
+    unpack2(x, x0, x1);
+    x = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+    const uint64_t magic = pack2(12582912.f, 12582912.f);
+    const uint64_t neg_magic = pack2(-12582912.f, -12582912.f);
+    const uint64_t fx = add2(x, magic);
+    const uint64_t j = add2(fx, neg_magic);
+    const uint64_t f = fma2(j, pack2(-1.f, -1.f), x);
+    uint64_t pl = fma2(pack2(0.0551716648042202f, 0.0551716648042202f), f, pack2(0.2426111251115799f, 0.2426111251115799f));
+    pl = fma2(pl, f, pack2(0.6932609677314758f, 0.6932609677314758f));
+    pl = fma2(pl, f, pack2(0.9999280571937561f, 0.9999280571937561f));
+    float p0, p1, f0, f1;
+    unpack2(pl, p0, p1);
+    unpack2(fx, f0, f1);
+    const float e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(f0) << 23));
+    const float e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(f1) << 23));
+    return pack2(e0, e1);
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -309,6 +367,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y, batch = blockIdx.z;
     const CtaPlan plan = make_plan(p, blockIdx.x);
+#ifdef TMW_TRACE
+    const bool trace_on = blockIdx.x == 8 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+    if (trace_on && threadIdx.x == 0) g_trace[0] = clock64();
+#endif
 
     if (threadIdx.x == 0) {
         mbar_init(bar(BAR_Q_FULL + 0), 1);
@@ -316,7 +378,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         mbar_init(bar(BAR_KP_FULL), 1);
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar(BAR_S_FULL + t), 1);
-            mbar_init(bar(BAR_P_READY + t), BM);
+            mbar_init(bar(BAR_P_READY + t), BM / 32);  // one arrival per softmax warp
             mbar_init(bar(BAR_O_DONE + t), 1);
         }
         for (int s = 0; s < KS; ++s) {
@@ -348,10 +410,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
     if (warp >= 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory");
-        if (warp == 8 && lane == 0) {
+        // Every role warp runs its loop with all 32 lanes (so the warp never splits into a running
+        // lane and 31 lanes parked at the final barrier); one lane issues the asynchronous operations.
+        const bool leader = lane == 0;
+        if (warp == 8) {
             // ---------------- producer: Q tiles, then K tiles ----------------
+#pragma unroll
             for (int t = 0; t < 2; ++t) {
-                if (plan.qt[t].rows == 0) continue;
+                if (plan.qt[t].rows == 0 || !leader) continue;
                 mbar_expect_tx(bar(BAR_Q_FULL + t), L::kTileBytes);
                 int c1, c2;
                 coords(0, blockIdx.x * 2 * BM + t * BM, c1, c2);
@@ -363,16 +429,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             for (int x = plan.x_begin; x < plan.x_end; ++x, ++n) {
                 const int s = n % KS;
                 mbar_wait(bar(BAR_K_EMPTY + s), ((n / KS) & 1) ^ 1, abort_flag, p.status);
-                mbar_expect_tx(bar(BAR_K_FULL + s), L::kTileBytes);
-                int c1, c2;
-                coords(1, p.np + plan.anchor + x * BN - p.k_pos0, c1, c2);
-                for (int u = 0; u < NSUB; ++u)
-                    tma_load_4d(smem_base + L::kK + s * L::kTileBytes + u * L::kSubTileBytes, &map_k,
-                                bar(BAR_K_FULL + s), u * 64, c1, c2, batch);
+                if (leader) {
+                    mbar_expect_tx(bar(BAR_K_FULL + s), L::kTileBytes);
+                    int c1, c2;
+                    coords(1, p.np + plan.anchor + x * BN - p.k_pos0, c1, c2);
+                    for (int u = 0; u < NSUB; ++u)
+                        tma_load_4d(smem_base + L::kK + s * L::kTileBytes + u * L::kSubTileBytes, &map_k,
+                                    bar(BAR_K_FULL + s), u * 64, c1, c2, batch);
+                }
+                __syncwarp();
             }
-        } else if (warp == 9 && lane == 0) {
+        } else if (warp == 9) {
             // ---------------- producer: persistent K/V, then V tiles ----------------
-            if (p.np > 0) {
+            if (p.np > 0 && leader) {
                 mbar_expect_tx(bar(BAR_KP_FULL), 2 * pers_bytes);
                 int c1, c2;
                 coords(1, 0, c1, c2);
@@ -387,111 +456,145 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             for (int x = plan.x_begin; x < plan.x_end; ++x, ++n) {
                 const int s = n % VS;
                 mbar_wait(bar(BAR_V_EMPTY + s), ((n / VS) & 1) ^ 1, abort_flag, p.status);
-                mbar_expect_tx(bar(BAR_V_FULL + s), L::kTileBytes);
-                int c1, c2;
-                coords(2, p.np + plan.anchor + x * BN - p.k_pos0, c1, c2);
-                for (int u = 0; u < NSUB; ++u)
-                    tma_load_4d(smem_base + L::kV + s * L::kTileBytes + u * L::kSubTileBytes, &map_v,
-                                bar(BAR_V_FULL + s), u * 64, c1, c2, batch);
+                if (leader) {
+                    mbar_expect_tx(bar(BAR_V_FULL + s), L::kTileBytes);
+                    int c1, c2;
+                    coords(2, p.np + plan.anchor + x * BN - p.k_pos0, c1, c2);
+                    for (int u = 0; u < NSUB; ++u)
+                        tma_load_4d(smem_base + L::kV + s * L::kTileBytes + u * L::kSubTileBytes, &map_v,
+                                    bar(BAR_V_FULL + s), u * 64, c1, c2, batch);
+                }
+                __syncwarp();
             }
-        } else if (warp == 10 && lane == 0) {
+        } else if (warp == 10) {
             // ---------------- tensor-core issue ----------------
+            // Everything here is kept in registers with compile-time query-tile indices: the issue
+            // path of this warp is what paces both softmax groups.
             const uint32_t fmt = BF16 ? 1u : 0u;
             const uint32_t idesc_qk_win = make_idesc(fmt, 0, BN);
             const uint32_t idesc_qk_pers = make_idesc(fmt, 0, (uint32_t)max(p.np_pad, 16));
             const uint32_t idesc_pv = make_idesc(fmt, 1, DH);
-            const uint32_t col_s[2] = {kColS0, kColS1};
-            const uint32_t col_o[2] = {kColO0, kColO1};
-            int k_confirmed = plan.x_begin;  // window tiles < k_confirmed are known to be in shared memory
-            int v_confirmed = plan.x_begin;
+            // high word of every descriptor: stride byte offset 1024, version 1, 128-byte swizzle
+            constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            auto desc_of = [](uint32_t lo) -> uint64_t { return ((uint64_t)kDescHi << 32) | lo; };
+            // low word: start address >> 4 | leading byte offset >> 4 << 16
+            auto lo_of = [](uint32_t addr, uint32_t lbo) -> uint32_t { return ((addr >> 4) & 0x3fffu) | ((lbo >> 4) << 16); };
+            const QtPlan q0 = plan.qt[0], q1 = plan.qt[1];
+            const int x_begin = plan.x_begin;
+            int k_confirmed = x_begin;  // window tiles < k_confirmed are known to be in shared memory
+            int v_confirmed = x_begin;
             bool pers_confirmed = false;
 
-            auto issue_qk = [&](int t, int item) {
-                const QtPlan& q = plan.qt[t];
-                const uint32_t q_addr = smem_base + L::kQ + t * L::kTileBytes;
-                uint32_t b_addr, b_sub, idesc;
-                int x = -1;
+            auto issue_qk = [&](auto tc, int item) {
+                constexpr int t = decltype(tc)::value;
+                const QtPlan& q = t == 0 ? q0 : q1;
+                const QtPlan& o = t == 0 ? q1 : q0;
+                const uint32_t a_lo = lo_of(smem_base + L::kQ + t * L::kTileBytes, 16);
+                const uint32_t d_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
                 if (item < q.has_pers) {
                     if (!pers_confirmed) {
                         mbar_wait(bar(BAR_KP_FULL), 0, abort_flag, p.status);
                         pers_confirmed = true;
                     }
-                    b_addr = smem_base + L::kP;
-                    b_sub = (uint32_t)p.np_pad * 128;
-                    idesc = idesc_qk_pers;
+                    tc_fence_after();
+                    if (leader) {
+                        const uint32_t b_lo = lo_of(smem_base + L::kP, 16);
+                        const uint32_t b_sub = (uint32_t)p.np_pad * 8;  // sub-tile stride >> 4
+#pragma unroll
+                        for (int kk = 0; kk < DH / 16; ++kk)
+                            mma_ss(d_tmem, desc_of(a_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2),
+                                   desc_of(b_lo + (kk / 4) * b_sub + (kk % 4) * 2), idesc_qk_pers, kk > 0 ? 1u : 0u);
+                        tc_commit(bar(BAR_S_FULL + t));
+                    }
                 } else {
-                    x = q.a + item - q.has_pers;
+                    const int x = q.a + item - q.has_pers;
                     while (k_confirmed <= x) {
-                        const int n = k_confirmed - plan.x_begin;
+                        const int n = k_confirmed - x_begin;
                         mbar_wait(bar(BAR_K_FULL + n % KS), (n / KS) & 1, abort_flag, p.status);
                         ++k_confirmed;
                     }
-                    b_addr = smem_base + L::kK + ((x - plan.x_begin) % KS) * L::kTileBytes;
-                    b_sub = L::kSubTileBytes;
-                    idesc = idesc_qk_win;
-                }
-                tc_fence_after();
+                    tc_fence_after();
+                    if (leader) {
+                        const int stage = (x - x_begin) % KS;
+                        const uint32_t b_lo = lo_of(smem_base + L::kK + stage * L::kTileBytes, 16);
 #pragma unroll
-                for (int kk = 0; kk < DH / 16; ++kk) {
-                    const uint64_t a_desc = make_desc(q_addr + (kk / 4) * L::kSubTileBytes + (kk % 4) * 32, 16, 1024);
-                    const uint64_t b_desc = make_desc(b_addr + (kk / 4) * b_sub + (kk % 4) * 32, 16, 1024);
-                    mma_ss(tmem_base + col_s[t], a_desc, b_desc, idesc, kk > 0 ? 1u : 0u);
+                        for (int kk = 0; kk < DH / 16; ++kk)
+                            mma_ss(d_tmem, desc_of(a_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2),
+                                   desc_of(b_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2), idesc_qk_win,
+                                   kk > 0 ? 1u : 0u);
+                        tc_commit(bar(BAR_S_FULL + t));
+                        const bool other_later = uses_tile(o, x) && qk_order(o, t ^ 1, x) > qk_order(q, t, x);
+                        if (!other_later) tc_commit(bar(BAR_K_EMPTY + stage));
+                    }
                 }
-                tc_commit(bar(BAR_S_FULL + t));
-                if (x >= 0) {
-                    const QtPlan& o = plan.qt[t ^ 1];
-                    const bool other_later = uses_tile(o, x) && qk_order(o, t ^ 1, x) > qk_order(q, t, x);
-                    if (!other_later) tc_commit(bar(BAR_K_EMPTY + (x - plan.x_begin) % KS));
-                }
+                __syncwarp();
             };
 
-            auto issue_pv = [&](int t, int item) {
-                const QtPlan& q = plan.qt[t];
-                uint32_t b_addr, lbo;
-                int ksteps, x = -1;
+            auto issue_pv = [&](auto tc, int item) {
+                constexpr int t = decltype(tc)::value;
+                const QtPlan& q = t == 0 ? q0 : q1;
+                const QtPlan& o = t == 0 ? q1 : q0;
+                const uint32_t d_tmem = tmem_base + (t == 0 ? kColO0 : kColO1);
+                const uint32_t a_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
                 if (item < q.has_pers) {
-                    b_addr = smem_base + L::kP + pers_bytes;
-                    lbo = (uint32_t)p.np_pad * 128;
-                    ksteps = p.np_pad / 16;
+                    tc_fence_after();
+                    if (leader) {
+                        const uint32_t b_lo = lo_of(smem_base + L::kP + pers_bytes, (uint32_t)p.np_pad * 128);
+                        for (int kk = 0; kk < p.np_pad / 16; ++kk)
+                            mma_ts(d_tmem, a_tmem + kk * 8, desc_of(b_lo + kk * 128), idesc_pv, kk > 0 ? 1u : 0u);
+                    }
                 } else {
-                    x = q.a + item - q.has_pers;
+                    const int x = q.a + item - q.has_pers;
                     while (v_confirmed <= x) {
-                        const int n = v_confirmed - plan.x_begin;
+                        const int n = v_confirmed - x_begin;
                         mbar_wait(bar(BAR_V_FULL + n % VS), (n / VS) & 1, abort_flag, p.status);
                         ++v_confirmed;
                     }
-                    b_addr = smem_base + L::kV + ((x - plan.x_begin) % VS) * L::kTileBytes;
-                    lbo = L::kSubTileBytes;
-                    ksteps = BN / 16;
+                    tc_fence_after();
+                    if (leader) {
+                        const int stage = (x - x_begin) % VS;
+                        // B = V tile, MN-major: 16 keys = two 8-row groups of 1024 bytes per k-step
+                        const uint32_t b_lo = lo_of(smem_base + L::kV + stage * L::kTileBytes, L::kSubTileBytes);
+                        const uint32_t acc0 = item > 0 ? 1u : 0u;
+#pragma unroll
+                        for (int kk = 0; kk < BN / 16; ++kk)
+                            mma_ts(d_tmem, a_tmem + kk * 8, desc_of(b_lo + kk * 128), idesc_pv, kk > 0 ? 1u : acc0);
+                        const bool other_later = uses_tile(o, x) && pv_order(o, t ^ 1, x) > pv_order(q, t, x);
+                        if (!other_later) tc_commit(bar(BAR_V_EMPTY + stage));
+                    }
                 }
-                tc_fence_after();
-                for (int kk = 0; kk < ksteps; ++kk) {
-                    // B = V tile, MN-major: 16 keys = two 8-row groups of 1024 bytes per k-step
-                    const uint64_t b_desc = make_desc(b_addr + kk * 2048, lbo, 1024);
-                    mma_ts(tmem_base + col_o[t], tmem_base + col_s[t] + kk * 8, b_desc, idesc_pv,
-                           (item > 0 || kk > 0) ? 1u : 0u);
-                }
-                if (x >= 0) {
-                    const QtPlan& o = plan.qt[t ^ 1];
-                    const bool other_later = uses_tile(o, x) && pv_order(o, t ^ 1, x) > pv_order(q, t, x);
-                    if (!other_later) tc_commit(bar(BAR_V_EMPTY + (x - plan.x_begin) % VS));
-                }
+                __syncwarp();
             };
 
-            for (int t = 0; t < 2; ++t) {
-                if (plan.qt[t].n_items == 0) continue;
-                mbar_wait(bar(BAR_Q_FULL + t), 0, abort_flag, p.status);
-                issue_qk(t, 0);
+            auto turn = [&](auto tc, int i) {
+                constexpr int t = decltype(tc)::value;
+                const QtPlan& q = t == 0 ? q0 : q1;
+                if (i >= q.n_items) return;
+                TRACE(100 + (i * 2 + t) * 4 + 0);
+                mbar_wait(bar(BAR_P_READY + t), i & 1, abort_flag, p.status);
+                TRACE(100 + (i * 2 + t) * 4 + 1);
+                issue_pv(tc, i);
+                TRACE(100 + (i * 2 + t) * 4 + 2);
+                if (i + 1 < q.n_items) issue_qk(tc, i + 1);
+                else if (leader) tc_commit(bar(BAR_O_DONE + t));
+                TRACE(100 + (i * 2 + t) * 4 + 3);
+            };
+
+            using T0 = std::integral_constant<int, 0>;
+            using T1 = std::integral_constant<int, 1>;
+            if (q0.n_items > 0) {
+                mbar_wait(bar(BAR_Q_FULL + 0), 0, abort_flag, p.status);
+                issue_qk(T0{}, 0);
             }
-            const int max_items = max(plan.qt[0].n_items, plan.qt[1].n_items);
+            if (q1.n_items > 0) {
+                mbar_wait(bar(BAR_Q_FULL + 1), 0, abort_flag, p.status);
+                issue_qk(T1{}, 0);
+            }
+            const int max_items = max(q0.n_items, q1.n_items);
+#pragma unroll 1
             for (int i = 0; i < max_items; ++i) {
-                for (int t = 0; t < 2; ++t) {
-                    if (i >= plan.qt[t].n_items) continue;
-                    mbar_wait(bar(BAR_P_READY + t), i & 1, abort_flag, p.status);
-                    issue_pv(t, i);
-                    if (i + 1 < plan.qt[t].n_items) issue_qk(t, i + 1);
-                    else tc_commit(bar(BAR_O_DONE + t));
-                }
+                turn(T0{}, i);
+                turn(T1{}, i);
             }
         }
     } else {
@@ -499,7 +602,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
         const int t = warp >> 2;                       // query tile of this group
         const int row = threadIdx.x & (BM - 1);        // row of the tile == tensor-memory lane
-        const QtPlan& q = plan.qt[t];
+        const QtPlan q = t == 0 ? plan.qt[0] : plan.qt[1];
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         const uint32_t s_addr = tmem_base + lane_addr + (t == 0 ? kColS0 : kColS1);
         const uint32_t o_addr = tmem_base + lane_addr + (t == 0 ? kColO0 : kColO1);
@@ -531,34 +634,44 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
             const int nchunks = (ncols + 31) / 32;
 
+            TRACE(1000 + t * 500 + item * 8 + 0 + ((warp & 3) ? 2000 : 0));
             mbar_wait(bar(BAR_S_FULL + t), item & 1, abort_flag, p.status);
             tc_fence_after();
+            TRACE(1000 + t * 500 + item * 8 + 1 + ((warp & 3) ? 2000 : 0));
 
             uint32_t s[4][32];
 #pragma unroll
             for (int c = 0; c < 4; ++c)
                 if (c < nchunks) tmem_ld32(s_addr + c * 32, s[c]);
             tc_wait_ld();
+            TRACE(1000 + t * 500 + item * 8 + 2 + ((warp & 3) ? 2000 : 0));
 
-            float tile_max = -INFINITY;
-            if (full) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(s[c][j]));
-            } else {
+            // mask (only the chunks in which some row of the warp has a hidden key), then the row maximum
+            // over four independent chains of 3-input max
+            if (!full) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
                     if (c < nchunks) {
+                        const int lo = j_lo - c * 32, hi = j_hi - c * 32;  // visible columns of the chunk: [lo, hi]
+                        if (!__all_sync(0xffffffffu, lo <= 0 && hi >= 31)) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int col = c * 32 + j;
-                            const float val = (col >= j_lo && col <= j_hi) ? __uint_as_float(s[c][j]) : -INFINITY;
-                            s[c][j] = __float_as_uint(val);
-                            tile_max = fmaxf(tile_max, val);
+                            for (int j = 0; j < 32; ++j)
+                                if (j < lo || j > hi) s[c][j] = 0xff800000u;  // -inf
                         }
                     }
             }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (c < nchunks) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            mx[k] = max3(mx[k], __uint_as_float(s[c][j + 2 * k]), __uint_as_float(s[c][j + 2 * k + 1]));
+                    }
+                }
+            float tile_max = max3(fmaxf(mx[0], mx[1]), mx[2], mx[3]);
             tile_max *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
 
             // lazy maximum: keep the old reference unless the new maximum is more than 2^8 above it
@@ -581,36 +694,63 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
             }
 
-            // P = exp2(S * c - m), packed two 16-bit values per column, written over S
+            TRACE(1000 + t * 500 + item * 8 + 3 + ((warp & 3) ? 2000 : 0));
+            // P = exp2(S * c - m), packed two 16-bit values per column, written over S.  kPolyOf4 of every
+            // four column pairs take the polynomial on the FMA pipe, the others the MUFU unit.
             const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+            const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
+            const uint64_t negm2 = pack2(neg_m, neg_m);
+            uint64_t lacc[2] = {0ull, 0ull};  // four partial row sums
 #pragma unroll
             for (int c = 0; c < 4; ++c)
                 if (c < nchunks) {
                     uint32_t packed[16];
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const float e0 = fast_exp2(fmaf(__uint_as_float(s[c][j]), p.scale_log2, neg_m));
-                        const float e1 = fast_exp2(fmaf(__uint_as_float(s[c][j + 1]), p.scale_log2, neg_m));
-                        l_sum += e0 + e1;
+                    for (int i = 0; i < 16; ++i) {
+                        const uint64_t x = fma2(pack2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
+                                                scale2, negm2);
+                        uint64_t e;
+                        float e0, e1;
+                        if ((i & 3) < kPolyOf4) {
+                            e = poly_exp2_x2(x);
+                            unpack2(e, e0, e1);
+                        } else {
+                            float x0, x1;
+                            unpack2(x, x0, x1);
+                            e0 = fast_exp2(x0);
+                            e1 = fast_exp2(x1);
+                            e = pack2(e0, e1);
+                        }
+                        lacc[i & 1] = add2(lacc[i & 1], e);
                         if (BF16) {
                             const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-                            packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h);
+                            packed[i] = *reinterpret_cast<const uint32_t*>(&h);
                         } else {
                             const __half2 h = __floats2half2_rn(e0, e1);
-                            packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h);
+                            packed[i] = *reinterpret_cast<const uint32_t*>(&h);
                         }
                     }
                     tmem_st16(s_addr + c * 16, packed);
                 }
+            {
+                float a0, a1, a2, a3;
+                unpack2(lacc[0], a0, a1);
+                unpack2(lacc[1], a2, a3);
+                l_sum += (a0 + a1) + (a2 + a3);
+            }
+            TRACE(1000 + t * 500 + item * 8 + 4 + ((warp & 3) ? 2000 : 0));
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(BAR_P_READY + t));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BAR_P_READY + t));
+            TRACE(1000 + t * 500 + item * 8 + 5 + ((warp & 3) ? 2000 : 0));
         }
 
         if (q.n_items > 0) {
             // ---------------- epilogue: O / l -> shared memory (swizzled) -> TMA store ----------------
             mbar_wait(bar(BAR_O_DONE + t), 0, abort_flag, p.status);
             tc_fence_after();
+            TRACE(1 + t * 4 + ((warp & 3) ? 2000 : 0));
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             uint8_t* stage = smem + L::kQ + t * L::kTileBytes;  // the Q tile is no longer needed
 #pragma unroll
@@ -649,6 +789,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     tma_store_4d(&map_o, smem_u32(stage + u * L::kSubTileBytes), u * 64, c1, c2, batch);
                 tma_store_commit_and_wait();
             }
+            TRACE(2 + t * 4 + ((warp & 3) ? 2000 : 0));
         }
     }
 
@@ -762,6 +903,12 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
 constexpr int kMaxDynamicSmem = 232448;  // 227 KB per CTA on sm_100
 
 }  // namespace
+
+#ifdef TMW_TRACE
+extern "C" __attribute__((visibility("default"))) int tmw_debug_trace(long long* host_out, int n) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * n);
+}
+#endif
 
 bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, const void*, const void*) {
     if (d.dtype != TMW_BF16 && d.dtype != TMW_F16) return false;
