@@ -85,13 +85,18 @@ struct Raw8<__half> {
     }
 };
 
-// WARPS = warps that share one (sequence, head) pair; a CTA holds 2 pairs when WARPS == 1, and nine
-// such CTAs fit on an SM (register bound), i.e. 2664 pairs are resident at once on 148 SMs.
+// WARPS = warps that share one (sequence, head) pair.  The launcher picks WARPS so that every pair is
+// resident at once (no second, partly filled wave of CTAs):
+//   WARPS 1: 2 pairs per 64-thread CTA, 9 CTAs per SM  -> up to 2664 pairs on 148 SMs
+//   WARPS 2: 1 pair  per 64-thread CTA, 9 CTAs per SM  -> up to 1332 pairs
+//   WARPS 4: 1 pair  per 128-thread CTA, 4 per SM      -> up to  592 pairs
+//   WARPS 8: 1 pair  per 256-thread CTA, 2 per SM      -> up to  296 pairs
 template <typename T, int DH, int WARPS>
-__global__ void __launch_bounds__(WARPS == 1 ? 64 : WARPS * 32, WARPS == 1 ? 9 : 1) decode_kernel(const DecodeParams p) {
-    // 16-byte loads in flight per lane for K, and again for V; fewer when one warp owns a pair, because
-    // then 18 warps per SM are resident and the register budget per thread is 112
-    constexpr int UNROLL = (WARPS == 1 ? 4 : 8) / (sizeof(T) == 4 ? 2 : 1);
+__global__ void __launch_bounds__(WARPS == 1 ? 64 : WARPS * 32, WARPS <= 2 ? 9 : (WARPS == 4 ? 4 : 2))
+decode_kernel(const DecodeParams p) {
+    // 16-byte loads in flight per lane for K, and again for V; fewer in the shapes with many resident
+    // warps per SM, whose register budget per thread is 112
+    constexpr int UNROLL = (WARPS <= 2 ? 4 : 8) / (sizeof(T) == 4 ? 2 : 1);
     constexpr int LPK = DH / 8;       // lanes per key row
     constexpr int RPW = 32 / LPK;     // key rows per warp per load instruction
     constexpr int STRIDE = RPW * WARPS;
@@ -285,16 +290,20 @@ __global__ void cache_fill_kernel(const FillParams p) {
     }
 }
 
-constexpr int kCtaWarps = 8;
-
 template <typename T, int DH>
 int launch_decode_shape(const DecodeParams& p, cudaStream_t stream) {
     const int pairs = p.batch * p.heads;
-    // enough pairs to give every SM a dozen warps: one warp per pair; otherwise a CTA per pair
-    if (pairs >= 1536) {
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (pairs > 9 * sms) {
         decode_kernel<T, DH, 1><<<(pairs + 1) / 2, 64, 0, stream>>>(p);
+    } else if (pairs > 4 * sms) {
+        decode_kernel<T, DH, 2><<<pairs, 64, 0, stream>>>(p);
+    } else if (pairs > 2 * sms) {
+        decode_kernel<T, DH, 4><<<pairs, 128, 0, stream>>>(p);
     } else {
-        decode_kernel<T, DH, kCtaWarps><<<pairs, kCtaWarps * 32, 0, stream>>>(p);
+        decode_kernel<T, DH, 8><<<pairs, 256, 0, stream>>>(p);
     }
     TMW_CUDA_TRY(cudaGetLastError());
     return TMW_OK;

@@ -3,12 +3,13 @@
 //
 // One CTA owns 256 consecutive query rows of one (batch, head) as two 128-row query
 // tiles.  Its 12 warps have fixed roles:
-//   warps 0-3   softmax group of query tile 0      (one thread per query row)
-//   warps 4-7   softmax group of query tile 1
-//   warp  8     TMA producer: Q tiles, then the K tiles of the window
-//   warp  9     TMA producer: persistent K/V tile, then the V tiles of the window
-//   warp  10    issues every tcgen05.mma (one elected thread)
-//   warp  11    allocates / frees tensor memory
+//   warp  0     TMA producer: Q tiles, then the K tiles of the window
+//   warp  1     TMA producer: persistent K/V tile, then the V tiles; allocates / frees tensor memory
+//   warp  2     issues the tcgen05.mma of query tile 0 (one elected thread)
+//   warp  3     issues the tcgen05.mma of query tile 1
+//   warps 4-7   softmax group of query tile 0      (one thread per query row)
+//   warps 8-11  softmax group of query tile 1
+// (the issuing warps come first so that they are the oldest warps of their schedulers)
 // Key positions are cut into 128-key tiles anchored at (first query position - w), so
 // the second query tile always needs the same tiles shifted by one: both tiles share
 // every K/V tile that is loaded, and tiles that lie outside a query tile's window are
@@ -241,18 +242,9 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+// Shared-memory matrix descriptors (128-byte swizzle, version 1 for sm_100) are built in the kernel as
 //   bits [0,14)  start address >> 4       bits [16,30) leading byte offset >> 4
 //   bits [32,46) stride byte offset >> 4  bits [46,48) version = 1    bits [61,64) layout = 2 (SWIZZLE_128B)
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
 
 // Instruction descriptor for kind::f16: fp32 accumulate, A K-major; B K-major or MN-major.
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
@@ -309,13 +301,6 @@ __device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block) {
     if (c.x_end == 0) c.x_begin = 0;
     return c;
 }
-
-// Does query tile `t` multiply window tile x?  And in which turn?  Item index of window tile x is
-// x - a + has_pers; QK of item i is issued in turn (i - 1, t), PV of item i in turn (i, t); turns
-// are ordered by 2 * turn + t.
-__device__ __forceinline__ bool uses_tile(const QtPlan& q, int x) { return x >= q.a && x < q.a + q.n_win; }
-__device__ __forceinline__ int qk_order(const QtPlan& q, int t, int x) { return 2 * (x - q.a + q.has_pers - 1) + t; }
-__device__ __forceinline__ int pv_order(const QtPlan& q, int t, int x) { return 2 * (x - q.a + q.has_pers) + t; }
 
 // ---------------------------------------------------------------------------------
 // The kernel
@@ -383,16 +368,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
         for (int s = 0; s < KS; ++s) {
             mbar_init(bar(BAR_K_FULL + s), 1);
-            mbar_init(bar(BAR_K_EMPTY + s), 1);
+            mbar_init(bar(BAR_K_EMPTY + s), 2);  // one arrival per issuing warp
         }
         for (int s = 0; s < VS; ++s) {
             mbar_init(bar(BAR_V_FULL + s), 1);
-            mbar_init(bar(BAR_V_EMPTY + s), 1);
+            mbar_init(bar(BAR_V_EMPTY + s), 2);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 11) {
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
                      "r"(kTmemCols)
                      : "memory");
@@ -408,12 +393,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         if ((p.dim_order >> which) & 1) { c1 = head; c2 = row; } else { c1 = row; c2 = head; }
     };
 
-    if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory");
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;" ::: "memory");
         // Every role warp runs its loop with all 32 lanes (so the warp never splits into a running
         // lane and 31 lanes parked at the final barrier); one lane issues the asynchronous operations.
         const bool leader = lane == 0;
-        if (warp == 8) {
+        if (warp == 0) {
             // ---------------- producer: Q tiles, then K tiles ----------------
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
@@ -439,7 +424,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 __syncwarp();
             }
-        } else if (warp == 9) {
+        } else if (warp == 1) {
             // ---------------- producer: persistent K/V, then V tiles ----------------
             if (p.np > 0 && leader) {
                 mbar_expect_tx(bar(BAR_KP_FULL), 2 * pers_bytes);
@@ -466,10 +451,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 __syncwarp();
             }
-        } else if (warp == 10) {
-            // ---------------- tensor-core issue ----------------
-            // Everything here is kept in registers with compile-time query-tile indices: the issue
-            // path of this warp is what paces both softmax groups.
+        } else {
+            // ---------------- tensor-core issue: warp 2 drives query tile 0, warp 3 query tile 1 ----------------
+            // Each warp issues, for its own query tile, QK of item i+1 right after PV of item i (P aliases S, and
+            // tcgen05 operations of one thread execute in issue order).  A K/V stage is free again once BOTH
+            // warps have arrived on its "empty" barrier: a warp that multiplies the tile arrives through
+            // tcgen05.commit after its last use, a warp that does not need the tile arrives once it has seen
+            // the tile land (so that the arrival is counted in the right phase).  All bookkeeping is kept
+            // incremental and in registers: this instruction stream paces the softmax groups.
+            const int t = warp - 2;
             const uint32_t fmt = BF16 ? 1u : 0u;
             const uint32_t idesc_qk_win = make_idesc(fmt, 0, BN);
             const uint32_t idesc_qk_pers = make_idesc(fmt, 0, (uint32_t)max(p.np_pad, 16));
@@ -479,128 +469,121 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             auto desc_of = [](uint32_t lo) -> uint64_t { return ((uint64_t)kDescHi << 32) | lo; };
             // low word: start address >> 4 | leading byte offset >> 4 << 16
             auto lo_of = [](uint32_t addr, uint32_t lbo) -> uint32_t { return ((addr >> 4) & 0x3fffu) | ((lbo >> 4) << 16); };
-            const QtPlan q0 = plan.qt[0], q1 = plan.qt[1];
-            const int x_begin = plan.x_begin;
-            int k_confirmed = x_begin;  // window tiles < k_confirmed are known to be in shared memory
-            int v_confirmed = x_begin;
-            bool pers_confirmed = false;
+            const QtPlan q = t == 0 ? plan.qt[0] : plan.qt[1];
+            const int n_tiles = plan.x_end - plan.x_begin;        // window tiles loaded by the producers
+            const int n_first = q.n_win > 0 ? q.a - plan.x_begin : n_tiles;  // my tiles: [n_first, n_first + n_win)
+            const uint32_t s_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
+            const uint32_t o_tmem = tmem_base + (t == 0 ? kColO0 : kColO1);
+            const uint32_t a_lo = lo_of(smem_base + L::kQ + t * L::kTileBytes, 16);
+            const uint32_t s_bar = bar(BAR_S_FULL + t), p_bar = bar(BAR_P_READY + t);
 
-            auto issue_qk = [&](auto tc, int item) {
-                constexpr int t = decltype(tc)::value;
-                const QtPlan& q = t == 0 ? q0 : q1;
-                const QtPlan& o = t == 0 ? q1 : q0;
-                const uint32_t a_lo = lo_of(smem_base + L::kQ + t * L::kTileBytes, 16);
-                const uint32_t d_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
-                if (item < q.has_pers) {
-                    if (!pers_confirmed) {
-                        mbar_wait(bar(BAR_KP_FULL), 0, abort_flag, p.status);
-                        pers_confirmed = true;
-                    }
-                    tc_fence_after();
-                    if (leader) {
-                        const uint32_t b_lo = lo_of(smem_base + L::kP, 16);
-                        const uint32_t b_sub = (uint32_t)p.np_pad * 8;  // sub-tile stride >> 4
+            // ring cursors: the next K tile / V tile this warp has not yet passed
+            int kn = 0, k_stage = 0;
+            uint32_t k_par = 0;
+            int vn = 0, v_stage = 0;
+            uint32_t v_par = 0;
+            auto k_advance = [&]() { ++kn; if (++k_stage == KS) { k_stage = 0; k_par ^= 1u; } };
+            auto v_advance = [&]() { ++vn; if (++v_stage == VS) { v_stage = 0; v_par ^= 1u; } };
+            // tiles this warp never multiplies: see them land, then hand the stage back
+            auto skip_k_until = [&](int n_stop) {
+                while (kn < n_stop) {
+                    mbar_wait(bar(BAR_K_FULL + k_stage), k_par, abort_flag, p.status);
+                    if (leader) mbar_arrive(bar(BAR_K_EMPTY + k_stage));
+                    k_advance();
+                }
+            };
+            auto skip_v_until = [&](int n_stop) {
+                while (vn < n_stop) {
+                    mbar_wait(bar(BAR_V_FULL + v_stage), v_par, abort_flag, p.status);
+                    if (leader) mbar_arrive(bar(BAR_V_EMPTY + v_stage));
+                    v_advance();
+                }
+            };
+
+            auto qk_pers = [&]() {
+                mbar_wait(bar(BAR_KP_FULL), 0, abort_flag, p.status);
+                const uint32_t b_lo = lo_of(smem_base + L::kP, 16);
+                const uint32_t b_sub = (uint32_t)p.np_pad * 8;  // sub-tile stride >> 4
+                tc_fence_after();
 #pragma unroll
-                        for (int kk = 0; kk < DH / 16; ++kk)
-                            mma_ss(d_tmem, desc_of(a_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2),
-                                   desc_of(b_lo + (kk / 4) * b_sub + (kk % 4) * 2), idesc_qk_pers, kk > 0 ? 1u : 0u);
-                        tc_commit(bar(BAR_S_FULL + t));
-                    }
-                } else {
-                    const int x = q.a + item - q.has_pers;
-                    while (k_confirmed <= x) {
-                        const int n = k_confirmed - x_begin;
-                        mbar_wait(bar(BAR_K_FULL + n % KS), (n / KS) & 1, abort_flag, p.status);
-                        ++k_confirmed;
-                    }
-                    tc_fence_after();
-                    if (leader) {
-                        const int stage = (x - x_begin) % KS;
-                        const uint32_t b_lo = lo_of(smem_base + L::kK + stage * L::kTileBytes, 16);
+                for (int kk = 0; kk < DH / 16; ++kk) {
+                    const uint64_t ad = desc_of(a_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2);
+                    const uint64_t bd = desc_of(b_lo + (kk / 4) * b_sub + (kk % 4) * 2);
+                    if (leader) mma_ss(s_tmem, ad, bd, idesc_qk_pers, kk > 0 ? 1u : 0u);
+                }
+                if (leader) tc_commit(s_bar);
+                __syncwarp();
+            };
+            // QK of the window tile under the K cursor (waits for the tile, releases its stage)
+            auto qk_win = [&]() {
+                mbar_wait(bar(BAR_K_FULL + k_stage), k_par, abort_flag, p.status);
+                const uint32_t b_lo = lo_of(smem_base + L::kK + k_stage * L::kTileBytes, 16);
+                const uint32_t e_bar = bar(BAR_K_EMPTY + k_stage);
+                tc_fence_after();
 #pragma unroll
-                        for (int kk = 0; kk < DH / 16; ++kk)
-                            mma_ss(d_tmem, desc_of(a_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2),
-                                   desc_of(b_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2), idesc_qk_win,
-                                   kk > 0 ? 1u : 0u);
-                        tc_commit(bar(BAR_S_FULL + t));
-                        const bool other_later = uses_tile(o, x) && qk_order(o, t ^ 1, x) > qk_order(q, t, x);
-                        if (!other_later) tc_commit(bar(BAR_K_EMPTY + stage));
-                    }
+                for (int kk = 0; kk < DH / 16; ++kk) {
+                    const uint64_t ad = desc_of(a_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2);
+                    const uint64_t bd = desc_of(b_lo + (kk / 4) * (L::kSubTileBytes >> 4) + (kk % 4) * 2);
+                    if (leader) mma_ss(s_tmem, ad, bd, idesc_qk_win, kk > 0 ? 1u : 0u);
+                }
+                if (leader) {
+                    tc_commit(s_bar);
+                    tc_commit(e_bar);
+                }
+                __syncwarp();
+                k_advance();
+            };
+            auto pv_pers = [&]() {
+                const uint32_t b_lo = lo_of(smem_base + L::kP + pers_bytes, (uint32_t)p.np_pad * 128);
+                tc_fence_after();
+                for (int kk = 0; kk < p.np_pad / 16; ++kk) {
+                    const uint64_t bd = desc_of(b_lo + kk * 128);
+                    if (leader) mma_ts(o_tmem, s_tmem + kk * 8, bd, idesc_pv, kk > 0 ? 1u : 0u);
                 }
                 __syncwarp();
             };
-
-            auto issue_pv = [&](auto tc, int item) {
-                constexpr int t = decltype(tc)::value;
-                const QtPlan& q = t == 0 ? q0 : q1;
-                const QtPlan& o = t == 0 ? q1 : q0;
-                const uint32_t d_tmem = tmem_base + (t == 0 ? kColO0 : kColO1);
-                const uint32_t a_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
-                if (item < q.has_pers) {
-                    tc_fence_after();
-                    if (leader) {
-                        const uint32_t b_lo = lo_of(smem_base + L::kP + pers_bytes, (uint32_t)p.np_pad * 128);
-                        for (int kk = 0; kk < p.np_pad / 16; ++kk)
-                            mma_ts(d_tmem, a_tmem + kk * 8, desc_of(b_lo + kk * 128), idesc_pv, kk > 0 ? 1u : 0u);
-                    }
-                } else {
-                    const int x = q.a + item - q.has_pers;
-                    while (v_confirmed <= x) {
-                        const int n = v_confirmed - x_begin;
-                        mbar_wait(bar(BAR_V_FULL + n % VS), (n / VS) & 1, abort_flag, p.status);
-                        ++v_confirmed;
-                    }
-                    tc_fence_after();
-                    if (leader) {
-                        const int stage = (x - x_begin) % VS;
-                        // B = V tile, MN-major: 16 keys = two 8-row groups of 1024 bytes per k-step
-                        const uint32_t b_lo = lo_of(smem_base + L::kV + stage * L::kTileBytes, L::kSubTileBytes);
-                        const uint32_t acc0 = item > 0 ? 1u : 0u;
+            // PV of the window tile under the V cursor; acc0 = 0 only for the very first product of the tile
+            auto pv_win = [&](uint32_t acc0) {
+                mbar_wait(bar(BAR_V_FULL + v_stage), v_par, abort_flag, p.status);
+                // B = V tile, MN-major: 16 keys = two 8-row groups of 1024 bytes per k-step
+                const uint32_t b_lo = lo_of(smem_base + L::kV + v_stage * L::kTileBytes, L::kSubTileBytes);
+                const uint32_t e_bar = bar(BAR_V_EMPTY + v_stage);
+                tc_fence_after();
 #pragma unroll
-                        for (int kk = 0; kk < BN / 16; ++kk)
-                            mma_ts(d_tmem, a_tmem + kk * 8, desc_of(b_lo + kk * 128), idesc_pv, kk > 0 ? 1u : acc0);
-                        const bool other_later = uses_tile(o, x) && pv_order(o, t ^ 1, x) > pv_order(q, t, x);
-                        if (!other_later) tc_commit(bar(BAR_V_EMPTY + stage));
-                    }
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint64_t bd = desc_of(b_lo + kk * 128);
+                    if (leader) mma_ts(o_tmem, s_tmem + kk * 8, bd, idesc_pv, kk > 0 ? 1u : acc0);
                 }
+                if (leader) tc_commit(e_bar);
                 __syncwarp();
+                v_advance();
             };
 
-            auto turn = [&](auto tc, int i) {
-                constexpr int t = decltype(tc)::value;
-                const QtPlan& q = t == 0 ? q0 : q1;
-                if (i >= q.n_items) return;
-                TRACE(100 + (i * 2 + t) * 4 + 0);
-                mbar_wait(bar(BAR_P_READY + t), i & 1, abort_flag, p.status);
-                TRACE(100 + (i * 2 + t) * 4 + 1);
-                issue_pv(tc, i);
-                TRACE(100 + (i * 2 + t) * 4 + 2);
-                if (i + 1 < q.n_items) issue_qk(tc, i + 1);
-                else if (leader) tc_commit(bar(BAR_O_DONE + t));
-                TRACE(100 + (i * 2 + t) * 4 + 3);
-            };
-
-            using T0 = std::integral_constant<int, 0>;
-            using T1 = std::integral_constant<int, 1>;
-            if (q0.n_items > 0) {
-                mbar_wait(bar(BAR_Q_FULL + 0), 0, abort_flag, p.status);
-                issue_qk(T0{}, 0);
-            }
-            if (q1.n_items > 0) {
-                mbar_wait(bar(BAR_Q_FULL + 1), 0, abort_flag, p.status);
-                issue_qk(T1{}, 0);
-            }
-            const int max_items = max(q0.n_items, q1.n_items);
+            if (q.n_items > 0) {
+                mbar_wait(bar(BAR_Q_FULL + t), 0, abort_flag, p.status);
+                skip_k_until(n_first);
+                if (q.has_pers) qk_pers(); else qk_win();
+                skip_v_until(n_first);
 #pragma unroll 1
-            for (int i = 0; i < max_items; ++i) {
-                turn(T0{}, i);
-                turn(T1{}, i);
+                for (int i = 0; i < q.n_items; ++i) {
+                    TRACE(100 + (i * 2 + t) * 4 + 0);
+                    mbar_wait(p_bar, i & 1, abort_flag, p.status);
+                    TRACE(100 + (i * 2 + t) * 4 + 1);
+                    if (i < q.has_pers) pv_pers(); else pv_win(i > 0 ? 1u : 0u);
+                    TRACE(100 + (i * 2 + t) * 4 + 2);
+                    if (i + 1 < q.n_items) qk_win();
+                    else if (leader) tc_commit(bar(BAR_O_DONE + t));
+                    TRACE(100 + (i * 2 + t) * 4 + 3);
+                }
             }
+            // hand back the stages of the tiles behind my last one (or all of them if I had none)
+            skip_k_until(n_tiles);
+            skip_v_until(n_tiles);
         }
     } else {
         // ---------------- softmax groups ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;" ::: "memory");
-        const int t = warp >> 2;                       // query tile of this group
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;" ::: "memory");
+        const int t = (warp >> 2) - 1;                 // query tile of this group
         const int row = threadIdx.x & (BM - 1);        // row of the tile == tensor-memory lane
         const QtPlan q = t == 0 ? plan.qt[0] : plan.qt[1];
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -795,7 +778,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 11) {
+    if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }

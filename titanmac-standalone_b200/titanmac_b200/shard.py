@@ -1,0 +1,182 @@
+"""Sequence-sharded prefill: contiguous row blocks per rank, one K/V halo from the left.
+
+The reference has no distributed code; this is the multi-GPU form of its attention
+core for contexts that do not fit (or are too slow on) one GPU.  Rows are counted
+over the whole length ``L = Np + T`` like in the module (the first ``Np`` rows are
+the persistent rows, titans_core/attn/windowed_attention.py:113-118).  Rank 0 owns
+rows ``[0, Np + T_0)``, rank ``r > 0`` owns a block of sequence rows.  A sequence row
+``i`` needs the keys ``max(Np, i - w) .. i`` (windowed_attention.py:136-150) and the
+``Np`` persistent keys, so a rank needs from its left neighbours only the ``w`` rows
+before its first row, plus the persistent K/V from rank 0.
+
+Everything lands in the rank's own HBM first — a K and a V buffer laid out as
+``[persistent | halo | own rows]`` — and is then read by ordinary per-CTA TMA loads;
+nothing is read from a peer's memory by the attention kernel.  The rows whose window
+lies inside the rank's own block are launched before the halo arrives (on a side
+stream), the first ``w`` rows after it.
+
+The planning and the exchange work on CPU tensors with the ``gloo`` backend as well
+(that is how they are tested without GPUs); the attention calls need CUDA.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(total_rows: int, n_persistent: int, world: int) -> List[Tuple[int, int]]:
+    """Row ranges ``[r0, r1)`` per rank: the ``T = total_rows - Np`` sequence rows are split as evenly
+    as possible into contiguous blocks; rank 0's block also contains the ``Np`` persistent rows."""
+    if n_persistent >= total_rows:
+        raise ValueError(f"num_persistent_tokens ({n_persistent}) must be < seq_len ({total_rows})")
+    T = total_rows - n_persistent
+    base, rem = divmod(T, world)
+    bounds, start = [], n_persistent
+    for r in range(world):
+        n = base + (1 if r < rem else 0)
+        bounds.append((0 if r == 0 else start, start + n))
+        start += n
+    return bounds
+
+
+@dataclass(frozen=True)
+class Transfer:
+    src: int          # sending rank
+    dst: int          # receiving rank
+    src_row0: int     # first row (whole-length numbering) sent
+    rows: int
+    dst_offset: int   # row offset inside the receiver's halo region
+
+
+def plan_halo(bounds: Sequence[Tuple[int, int]], window: int, n_persistent: int) -> List[Transfer]:
+    """All halo transfers of one exchange.  Rank ``r > 0`` receives rows ``[max(Np, r0 - w), r0)``,
+    which may span several left neighbours when a block is shorter than the window."""
+    if window < 0:
+        raise ValueError(f"window_size must be non-negative, got {window}")
+    out: List[Transfer] = []
+    for dst in range(1, len(bounds)):
+        r0 = bounds[dst][0]
+        lo = max(n_persistent, r0 - window)
+        for src in range(dst):
+            s0, s1 = max(bounds[src][0], lo), min(bounds[src][1], r0)
+            if s1 > s0:
+                out.append(Transfer(src, dst, s0, s1 - s0, s0 - lo))
+    return out
+
+
+def halo_rows(bounds: Sequence[Tuple[int, int]], rank: int, window: int, n_persistent: int) -> int:
+    if rank == 0:
+        return 0
+    r0 = bounds[rank][0]
+    return r0 - max(n_persistent, r0 - window)
+
+
+class ShardedKV:
+    """This rank's K/V buffers ``[B, H, Np + halo + own, dh]`` and the positions that go with them."""
+
+    def __init__(self, k_own: torch.Tensor, v_own: torch.Tensor, total_rows: int, window: int, n_persistent: int,
+                 group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.window, self.n_persistent, self.total_rows = window, n_persistent, total_rows
+        self.bounds = shard_bounds(total_rows, n_persistent, self.world)
+        self.r0, self.r1 = self.bounds[self.rank]
+        if k_own.shape[2] != self.r1 - self.r0 or v_own.shape != k_own.shape:
+            raise ValueError(f"rank {self.rank} must hold rows [{self.r0}, {self.r1}) of K and V")
+        B, H, _, dh = k_own.shape
+        Np = n_persistent
+        self.halo = halo_rows(self.bounds, self.rank, window, Np)
+        own = self.r1 - self.r0
+        if self.rank == 0:
+            # rank 0's own block already starts with the persistent rows
+            self.k, self.v = k_own.contiguous(), v_own.contiguous()
+            self.own_offset = 0
+            self.k_pos0 = Np
+        else:
+            shape = (B, H, Np + self.halo + own, dh)
+            self.k = torch.empty(shape, dtype=k_own.dtype, device=k_own.device)
+            self.v = torch.empty(shape, dtype=v_own.dtype, device=v_own.device)
+            self.own_offset = Np + self.halo
+            self.k[:, :, self.own_offset:] = k_own
+            self.v[:, :, self.own_offset:] = v_own
+            self.k_pos0 = self.r0 - self.halo  # position of buffer row Np
+        self.q_pos0 = self.r0
+
+    def exchange(self) -> None:
+        """Persistent K/V from rank 0 and the halo rows from the left neighbours, into this rank's buffers."""
+        self.exchange_persistent()
+        self.exchange_halo()
+
+    def exchange_persistent(self) -> None:
+        Np = self.n_persistent
+        B, H, _, dh = self.k.shape
+        if Np > 0 and self.world > 1:
+            pers = torch.empty((2, B, H, Np, dh), dtype=self.k.dtype, device=self.k.device)
+            if self.rank == 0:
+                pers[0], pers[1] = self.k[:, :, :Np], self.v[:, :, :Np]
+            dist.broadcast(pers, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
+                           group=self.group)
+            if self.rank != 0:
+                self.k[:, :, :Np], self.v[:, :, :Np] = pers[0], pers[1]
+
+    def exchange_halo(self) -> None:
+        Np = self.n_persistent
+        B, H, _, dh = self.k.shape
+        ops, landing = [], []
+        for tr in plan_halo(self.bounds, self.window, Np):
+            if tr.src == self.rank:
+                a = self.own_offset + (tr.src_row0 - self.r0)
+                # one message per transfer: K and V rows stacked
+                msg = torch.stack([self.k[:, :, a:a + tr.rows], self.v[:, :, a:a + tr.rows]]).contiguous()
+                ops.append(dist.P2POp(dist.isend, msg, self._global(tr.dst), group=self.group))
+            elif tr.dst == self.rank:
+                buf = torch.empty((2, B, H, tr.rows, dh), dtype=self.k.dtype, device=self.k.device)
+                ops.append(dist.P2POp(dist.irecv, buf, self._global(tr.src), group=self.group))
+                landing.append((tr, buf))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+        for tr, buf in landing:
+            a = Np + tr.dst_offset
+            self.k[:, :, a:a + tr.rows], self.v[:, :, a:a + tr.rows] = buf[0], buf[1]
+
+    def _global(self, group_rank: int) -> int:
+        return dist.get_global_rank(self.group, group_rank) if self.group is not None else group_rank
+
+
+def sharded_prefill(q_own: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tensor, total_rows: int, window: int,
+                    n_persistent: int, group: Optional[dist.ProcessGroup] = None, overlap: bool = True,
+                    algo: int = 0) -> torch.Tensor:
+    """Attention output for this rank's rows (``[B, H, own, dh]``), CUDA only.
+
+    ``q_own, k_own, v_own``: ``[B, H, r1 - r0, dh]`` — this rank's rows of the whole-length tensors
+    (rank 0's block starts with the persistent rows).
+    """
+    from . import _native
+
+    kv = ShardedKV(k_own, v_own, total_rows, window, n_persistent, group)
+    B, H, own, dh = q_own.shape
+    out = torch.empty((B, own, H, dh), dtype=q_own.dtype, device=q_own.device).permute(0, 2, 1, 3)
+    # rows whose window needs the halo: the first `window` rows of ranks > 0
+    need_halo = min(own, window) if kv.rank > 0 else 0
+    if not overlap or need_halo == 0 or need_halo == own:
+        kv.exchange()
+        _native.prefill(q_own, kv.k, kv.v, window, n_persistent, out=out, q_pos0=kv.q_pos0, k_pos0=kv.k_pos0, algo=algo)
+        return out
+    kv.exchange_persistent()  # 2 * B * H * Np * dh elements: needed by every row, so it goes first
+    main = torch.cuda.current_stream(q_own.device)
+    side = torch.cuda.Stream(q_own.device)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):  # interior rows: every key they need is already in this rank's block
+        _native.prefill(q_own[:, :, need_halo:], kv.k, kv.v, window, n_persistent, out=out[:, :, need_halo:],
+                        q_pos0=kv.q_pos0 + need_halo, k_pos0=kv.k_pos0, algo=algo)
+    kv.exchange_halo()
+    _native.prefill(q_own[:, :, :need_halo], kv.k, kv.v, window, n_persistent, out=out[:, :, :need_halo],
+                    q_pos0=kv.q_pos0, k_pos0=kv.k_pos0, algo=algo)
+    main.wait_stream(side)
+    return out
