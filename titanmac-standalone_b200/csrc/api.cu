@@ -20,7 +20,7 @@ void set_cuda_error(cudaError_t e, const char* where) {
 
 // One status word per device: a __device__ variable is instantiated in every
 // context that loads this module.
-__device__ int g_device_status = 0;
+__device__ int g_device_status[4] = {0, 0, 0, 0};  // [0] status, [1..3] where the first expired wait was
 
 int* device_status_word() {
     constexpr int kMaxDevices = 64;
@@ -172,11 +172,16 @@ int tmw_poll_status(void* stream) {
     TMW_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     int* word = tmw::device_status_word();
     if (word == nullptr) return TMW_ERR_CUDA;
-    int value = 0;
-    TMW_CUDA_TRY(cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost));
-    if (value != 0) {
-        const int zero = 0;
-        TMW_CUDA_TRY(cudaMemcpy(word, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    int value[4] = {0, 0, 0, 0};
+    TMW_CUDA_TRY(cudaMemcpy(value, word, sizeof(value), cudaMemcpyDeviceToHost));
+    if (value[0] != 0) {
+        const int zero[4] = {0, 0, 0, 0};
+        TMW_CUDA_TRY(cudaMemcpy(word, zero, sizeof(zero), cudaMemcpyHostToDevice));
+        char text[160];
+        std::snprintf(text, sizeof(text), "device wait expired: barrier at shared offset %d parity %d, block (%d,%d,%d), warp %d",
+                      value[1] & 0xffff, (value[1] >> 16) & 1, value[2] & 0xffff, (value[2] >> 16) & 0xffff,
+                      value[3] & 0xffff, (value[3] >> 16) & 0xffff);
+        tmw::set_error_text(text);
         return TMW_ERR_DEVICE_TIMEOUT;
     }
     return TMW_OK;

@@ -39,14 +39,27 @@ namespace tmw {
 namespace {
 
 constexpr int kThreadsTc = 384;
+static_assert(128 * (168 - 80) >= 256 * (208 - 168), "setmaxnreg: the issuing warps must release what the softmax warps request");
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per tile
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
-constexpr int kPolyOf4 = 2;  // of every 4 column pairs, how many take the polynomial exp2
+#ifndef TMW_POLY_OF4
+#define TMW_POLY_OF4 2
+#endif
+constexpr int kPolyOf4 = TMW_POLY_OF4;  // of every 4 column pairs, how many take the polynomial exp2
 
 // tensor-memory columns (32-bit each, 128 lanes): S0 | S1 | O0 | O1; P aliases S
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+// head_dim 64 : S0 0 | S1 128 | P0 256 | P1 320 | O0 384 | O1 448   (P has its own columns: the next QK
+//                may overwrite S while the softmax group still turns the previous S into P)
+// head_dim 128: S0 0 | S1 128 | O0 256 | O1 384                      (P is written over S)
+template <int DH>
+struct TmemMap {
+    static constexpr bool kSplitP = DH == 64;
+    __host__ __device__ static constexpr uint32_t s(int t) { return t == 0 ? 0u : 128u; }
+    __host__ __device__ static constexpr uint32_t p(int t) { return kSplitP ? (t == 0 ? 256u : 320u) : s(t); }
+    __host__ __device__ static constexpr uint32_t o(int t) { return kSplitP ? (t == 0 ? 384u : 448u) : (t == 0 ? 256u : 384u); }
+};
 
 #ifdef TMW_TRACE
 // Build-time instrumentation (never part of the shipped library): clock stamps of one CTA.
@@ -89,7 +102,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  `abort_flag` lives in shared memory; once it is set nobody waits any more.
+// Bounded wait.  `abort_flag` lives in shared memory; once it is set nobody waits any more.  The first
+// wait that expires on the device also records where it was: status[1] = shared-memory offset of the
+// barrier and parity, status[2] = blockIdx.x | blockIdx.y << 16, status[3] = blockIdx.z | warp << 16.
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
     if (mbar_try_wait(bar, parity)) return;
     const long long t0 = clock64();
@@ -99,7 +114,11 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return;
             if (clock64() - t0 > kWaitLimitCycles) {
                 *abort_flag = 1;
-                atomicExch(status, (int)TMW_ERR_DEVICE_TIMEOUT);
+                if (atomicCAS(status, 0, (int)TMW_ERR_DEVICE_TIMEOUT) == 0) {
+                    status[1] = (int)((bar & 0xffffu) | (parity << 16));
+                    status[2] = (int)(blockIdx.x | (blockIdx.y << 16));
+                    status[3] = (int)(blockIdx.z | ((threadIdx.x >> 5) << 16));
+                }
                 return;
             }
         }
@@ -327,7 +346,9 @@ enum BarSlot {
     BAR_K_EMPTY = 13,      // [KS]
     BAR_V_FULL = 17,       // [VS <= 4]
     BAR_V_EMPTY = 21,      // [VS]
-    BAR_COUNT = 25
+    BAR_S_FREE = 25,       // [2] softmax group has S in registers (only when P has its own columns)
+    BAR_PV_DONE = 27,      // [2] P V of the previous item has finished (only when P has its own columns)
+    BAR_COUNT = 29
 };
 
 template <int DH, int KS, int VS, bool BF16>
@@ -365,6 +386,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             mbar_init(bar(BAR_S_FULL + t), 1);
             mbar_init(bar(BAR_P_READY + t), BM / 32);  // one arrival per softmax warp
             mbar_init(bar(BAR_O_DONE + t), 1);
+            mbar_init(bar(BAR_S_FREE + t), BM / 32);
+            mbar_init(bar(BAR_PV_DONE + t), 1);
         }
         for (int s = 0; s < KS; ++s) {
             mbar_init(bar(BAR_K_FULL + s), 1);
@@ -394,7 +417,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     };
 
     if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;" ::: "memory");
+        // Register budget.  The CTA is launched with 384 x 168 registers; setmaxnreg.inc below blocks until
+        // the registers it asks for have been released INSIDE THIS CTA, and nothing bounds that wait, so
+        // the numbers must add up:  released 128 x (168 - 80) = 11264  >=  requested 256 x (208 - 168) = 10240.
+#ifndef TMW_NO_SETMAXNREG
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::: "memory");
+#endif
         // Every role warp runs its loop with all 32 lanes (so the warp never splits into a running
         // lane and 31 lanes parked at the final barrier); one lane issues the asynchronous operations.
         const bool leader = lane == 0;
@@ -472,8 +500,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const QtPlan q = t == 0 ? plan.qt[0] : plan.qt[1];
             const int n_tiles = plan.x_end - plan.x_begin;        // window tiles loaded by the producers
             const int n_first = q.n_win > 0 ? q.a - plan.x_begin : n_tiles;  // my tiles: [n_first, n_first + n_win)
-            const uint32_t s_tmem = tmem_base + (t == 0 ? kColS0 : kColS1);
-            const uint32_t o_tmem = tmem_base + (t == 0 ? kColO0 : kColO1);
+            using TM = TmemMap<DH>;
+            const uint32_t s_tmem = tmem_base + TM::s(t);
+            const uint32_t p_tmem = tmem_base + TM::p(t);
+            const uint32_t o_tmem = tmem_base + TM::o(t);
             const uint32_t a_lo = lo_of(smem_base + L::kQ + t * L::kTileBytes, 16);
             const uint32_t s_bar = bar(BAR_S_FULL + t), p_bar = bar(BAR_P_READY + t);
 
@@ -484,19 +514,20 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             uint32_t v_par = 0;
             auto k_advance = [&]() { ++kn; if (++k_stage == KS) { k_stage = 0; k_par ^= 1u; } };
             auto v_advance = [&]() { ++vn; if (++v_stage == VS) { v_stage = 0; v_par ^= 1u; } };
-            // tiles this warp never multiplies: see them land, then hand the stage back
-            auto skip_k_until = [&](int n_stop) {
-                while (kn < n_stop) {
-                    mbar_wait(bar(BAR_K_FULL + k_stage), k_par, abort_flag, p.status);
-                    if (leader) mbar_arrive(bar(BAR_K_EMPTY + k_stage));
-                    k_advance();
-                }
-            };
-            auto skip_v_until = [&](int n_stop) {
-                while (vn < n_stop) {
-                    mbar_wait(bar(BAR_V_FULL + v_stage), v_par, abort_flag, p.status);
-                    if (leader) mbar_arrive(bar(BAR_V_EMPTY + v_stage));
-                    v_advance();
+            // Tiles this warp never multiplies: see them land, then hand the stage back.  K and V tiles are
+            // taken alternately — a warp that sat on the K ring alone would starve the V ring (and with it
+            // the other warp) as soon as it had more tiles to pass than the ring has stages.
+            auto skip_tiles_until = [&](int n_stop) {
+                while (kn < n_stop || vn < n_stop) {
+                    if (kn < n_stop && kn <= vn) {
+                        mbar_wait(bar(BAR_K_FULL + k_stage), k_par, abort_flag, p.status);
+                        if (leader) mbar_arrive(bar(BAR_K_EMPTY + k_stage));
+                        k_advance();
+                    } else {
+                        mbar_wait(bar(BAR_V_FULL + v_stage), v_par, abort_flag, p.status);
+                        if (leader) mbar_arrive(bar(BAR_V_EMPTY + v_stage));
+                        v_advance();
+                    }
                 }
             };
 
@@ -538,7 +569,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 tc_fence_after();
                 for (int kk = 0; kk < p.np_pad / 16; ++kk) {
                     const uint64_t bd = desc_of(b_lo + kk * 128);
-                    if (leader) mma_ts(o_tmem, s_tmem + kk * 8, bd, idesc_pv, kk > 0 ? 1u : 0u);
+                    if (leader) mma_ts(o_tmem, p_tmem + kk * 8, bd, idesc_pv, kk > 0 ? 1u : 0u);
                 }
                 __syncwarp();
             };
@@ -552,7 +583,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint64_t bd = desc_of(b_lo + kk * 128);
-                    if (leader) mma_ts(o_tmem, s_tmem + kk * 8, bd, idesc_pv, kk > 0 ? 1u : acc0);
+                    if (leader) mma_ts(o_tmem, p_tmem + kk * 8, bd, idesc_pv, kk > 0 ? 1u : acc0);
                 }
                 if (leader) tc_commit(e_bar);
                 __syncwarp();
@@ -561,34 +592,46 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
             if (q.n_items > 0) {
                 mbar_wait(bar(BAR_Q_FULL + t), 0, abort_flag, p.status);
-                skip_k_until(n_first);
+                if (q.n_win > 0) skip_tiles_until(n_first);  // at most one tile: the other query tile's first
                 if (q.has_pers) qk_pers(); else qk_win();
-                skip_v_until(n_first);
 #pragma unroll 1
                 for (int i = 0; i < q.n_items; ++i) {
+                    if (TM::kSplitP && i + 1 < q.n_items) {
+                        // S of item i is in the softmax group's registers: the next S may be produced
+                        // while the group is still busy with the exponentials of item i
+                        mbar_wait(bar(BAR_S_FREE + t), i & 1, abort_flag, p.status);
+                        qk_win();
+                    }
                     TRACE(100 + (i * 2 + t) * 4 + 0);
                     mbar_wait(p_bar, i & 1, abort_flag, p.status);
                     TRACE(100 + (i * 2 + t) * 4 + 1);
                     if (i < q.has_pers) pv_pers(); else pv_win(i > 0 ? 1u : 0u);
                     TRACE(100 + (i * 2 + t) * 4 + 2);
-                    if (i + 1 < q.n_items) qk_win();
-                    else if (leader) tc_commit(bar(BAR_O_DONE + t));
+                    if (TM::kSplitP) {
+                        if (leader) tc_commit(bar(i + 1 < q.n_items ? BAR_PV_DONE + t : BAR_O_DONE + t));
+                    } else {
+                        if (i + 1 < q.n_items) qk_win();
+                        else if (leader) tc_commit(bar(BAR_O_DONE + t));
+                    }
                     TRACE(100 + (i * 2 + t) * 4 + 3);
                 }
             }
             // hand back the stages of the tiles behind my last one (or all of them if I had none)
-            skip_k_until(n_tiles);
-            skip_v_until(n_tiles);
+            skip_tiles_until(n_tiles);
         }
     } else {
         // ---------------- softmax groups ----------------
+#ifndef TMW_NO_SETMAXNREG
         asm volatile("setmaxnreg.inc.sync.aligned.u32 208;" ::: "memory");
+#endif
         const int t = (warp >> 2) - 1;                 // query tile of this group
         const int row = threadIdx.x & (BM - 1);        // row of the tile == tensor-memory lane
         const QtPlan q = t == 0 ? plan.qt[0] : plan.qt[1];
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_addr + (t == 0 ? kColS0 : kColS1);
-        const uint32_t o_addr = tmem_base + lane_addr + (t == 0 ? kColO0 : kColO1);
+        using TM = TmemMap<DH>;
+        const uint32_t s_addr = tmem_base + lane_addr + TM::s(t);
+        const uint32_t p_addr = tmem_base + lane_addr + TM::p(t);
+        const uint32_t o_addr = tmem_base + lane_addr + TM::o(t);
         const int pos = q.p_lo + row;
         float m_used = -INFINITY;  // maximum the stored P and O are relative to (log2 domain)
         float l_sum = 0.f;
@@ -627,6 +670,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             for (int c = 0; c < 4; ++c)
                 if (c < nchunks) tmem_ld32(s_addr + c * 32, s[c]);
             tc_wait_ld();
+            if (TM::kSplitP) {
+                // S is in registers now: let the issuing warp overwrite it with the next item's scores
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_S_FREE + t));
+            }
             TRACE(1000 + t * 500 + item * 8 + 2 + ((warp & 3) ? 2000 : 0));
 
             // mask (only the chunks in which some row of the warp has a hidden key), then the row maximum
@@ -650,13 +699,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)
+                        for (int k = 0; k < 4; ++k) {
+#ifdef TMW_MAX2
+                            mx[k] = fmaxf(fmaxf(mx[k], __uint_as_float(s[c][j + 2 * k])), __uint_as_float(s[c][j + 2 * k + 1]));
+#else
                             mx[k] = max3(mx[k], __uint_as_float(s[c][j + 2 * k]), __uint_as_float(s[c][j + 2 * k + 1]));
+#endif
+                        }
                     }
                 }
             float tile_max = max3(fmaxf(mx[0], mx[1]), mx[2], mx[3]);
             tile_max *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
 
+            if (TM::kSplitP && item > 0) {
+                // the previous P V must have finished before O is rescaled or P is overwritten
+                mbar_wait(bar(BAR_PV_DONE + t), (item - 1) & 1, abort_flag, p.status);
+                tc_fence_after();
+            }
             // lazy maximum: keep the old reference unless the new maximum is more than 2^8 above it
             const bool grow = tile_max > m_used + 8.0f;
             if (item == 0) {
@@ -713,7 +772,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                             packed[i] = *reinterpret_cast<const uint32_t*>(&h);
                         }
                     }
-                    tmem_st16(s_addr + c * 16, packed);
+                    tmem_st16(p_addr + c * 16, packed);
                 }
             {
                 float a0, a1, a2, a3;
@@ -780,6 +839,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
+        if (*abort_flag) {
+            // a wait expired somewhere in this CTA: give asynchronous copies and matrix products that may
+            // still be in flight time to finish before tensor memory and shared memory are handed back
+            const long long t0 = clock64();
+            while (clock64() - t0 < 400000) __nanosleep(1000);
+        }
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }

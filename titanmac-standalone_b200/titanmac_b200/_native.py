@@ -132,7 +132,7 @@ def check(status: int) -> None:
     text = lib().tmw_strerror(status).decode()
     if status in (TMW_ERR_PERSISTENT_GE_LEN, TMW_ERR_NEGATIVE_WINDOW):
         raise ValueError(text)  # build_band_mask raises ValueError for both
-    if status == TMW_ERR_CUDA:
+    if status in (TMW_ERR_CUDA, TMW_ERR_DEVICE_TIMEOUT):
         text += ": " + lib().tmw_last_cuda_error().decode()
     raise TmwError(status, text)
 
