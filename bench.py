@@ -46,6 +46,13 @@ WORKLOADS = {
                                   dtype="bf16"),
     "config1_layer_prefill_fp32": dict(batch=2, T=512, d_model=512, heads=8, window=256, n_persistent=16,
                                        dtype="fp32"),
+    # BASELINE config 4: 16-layer default model, ring-cache decode; `batch` is the WHOLE-job batch here
+    # (256 sequences sharded over the GPUs), prompt 2048 tokens, then `--steps` single-token steps
+    "config4_decode": dict(batch=256, T=2048, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
+                           layers=16, d_ff=2560, vocab=50000),
+    # BASELINE config 5: attention core only, Q/K/V given; the sequence is sharded over the GPUs
+    "config5_long_prefill": dict(batch=1, T=131072, d_model=2048, heads=16, window=1024, n_persistent=16,
+                                 dtype="bf16"),
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention-core kernel,
@@ -309,10 +316,248 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
             "gpu_launches": args.steps,
             "clocks": clocks.report(),
         }
+        if world == 1:
+            line["extra"] = {"decode_attention_config4_one_layer": decode_attention_probe(dev, peaks)}
         if world == 1 and not args.no_cpu_baseline:
             sec, cflops, cores, desc = cpu_reference_sample(wl, iters=5, warmup=1)
             line["cpu_baseline"] = {"value": cflops / sec / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def decode_attention_probe(dev, peaks, batch=256, heads=10, dh=64, window=512, n_persistent=16, layers=4, iters=10):
+    """The decode kernel alone on BASELINE config 4's geometry: one launch = one layer's attention for the whole
+    batch.  `layers` independent ring caches are cycled so that a launch never finds its ring in L2."""
+    from titanmac_b200 import _native
+
+    caches = [_native.RingCache(batch, heads, dh, window, n_persistent, torch.bfloat16, dev) for _ in range(layers)]
+    for c in caches:
+        c.k_ring.normal_(); c.v_ring.normal_(); c.k_pers.normal_(); c.v_pers.normal_()
+    qkv = torch.randn(batch, 3, heads, dh, device=dev, dtype=torch.bfloat16)
+    pos = torch.full((batch,), 2048, dtype=torch.int32, device=dev)
+    out = torch.empty(batch, heads, dh, device=dev, dtype=torch.bfloat16)
+    for c in caches:
+        c.decode(qkv[:, 0], qkv[:, 1], qkv[:, 2], pos, out)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        for c in caches:
+            c.decode(qkv[:, 0], qkv[:, 1], qkv[:, 2], pos, out)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / (iters * layers)
+    nbytes = batch * heads * (window + 1 + n_persistent) * dh * 2 * 2
+    gbs = nbytes / ms / 1e6
+    return {"bound": "hbm", "kernel": "decode_kernel (tmw_decode)", "achieved": gbs, "peak": peaks["hbm_gbs"],
+            "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "avg_launch_ms": ms,
+            "algorithmic_bytes_per_launch": nbytes, "peak_source": f"{peaks['source']} copy bandwidth"}
+
+
+def _dist_setup(args):
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in the product)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    return dist, world, rank, local, dev
+
+
+def run_decode(args, wl_name: str, wl: dict) -> None:
+    """BASELINE config 4: prompt through the 16-layer model once, then `--steps` decode steps (CUDA graph)."""
+    from titanmac_b200 import TitanMAC, TitanMACConfig, _native
+
+    dist, world, rank, local, dev = _dist_setup(args)
+    if wl["batch"] % world:
+        raise SystemExit("the batch must divide by the number of GPUs")
+    B = wl["batch"] // world
+    cfg = TitanMACConfig(vocab_size=wl["vocab"], d_model=wl["d_model"], n_heads=wl["heads"], n_layers=wl["layers"],
+                         d_ff=wl["d_ff"], max_seq_len=4096, window_size=wl["window"], n_persistent=wl["n_persistent"])
+    g = torch.Generator(device="cpu").manual_seed(0)
+    model = TitanMAC(cfg).eval()
+    with torch.no_grad():  # every weight N(0, 0.02), biases 0, norm scales 1
+        for name, prm in model.named_parameters():
+            if name.endswith("scale"):
+                prm.fill_(1.0)
+            elif name.endswith("bias"):
+                prm.zero_()
+            else:
+                prm.copy_(torch.randn(prm.shape, generator=g) * 0.02)
+    model = model.to(device=dev, dtype=torch.bfloat16)
+    g = torch.Generator(device="cpu").manual_seed(1 + rank)
+    prompt = torch.randint(0, wl["vocab"], (B, wl["T"]), generator=g).to(dev)
+    forced = torch.randint(0, wl["vocab"], (B, args.steps + args.warmup + 2), generator=g).to(dev)
+
+    chunk = max(1, min(B, 32))  # prompt in slices of the batch: bounds the activation footprint
+    caches = model.new_caches(B, dev, torch.bfloat16)
+    t_pre = time.perf_counter()
+    for b0 in range(0, B, chunk):
+        sub = model.new_caches(min(chunk, B - b0), dev, torch.bfloat16)
+        model.prefill(prompt[b0:b0 + chunk], sub)
+        for full, part in zip(caches, sub):
+            full.k_ring[b0:b0 + chunk].copy_(part.k_ring); full.v_ring[b0:b0 + chunk].copy_(part.v_ring)
+            full.k_pers.copy_(part.k_pers); full.v_pers.copy_(part.v_pers)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t_pre
+
+    tok = forced[:, 0].clone()
+    pos = torch.full((B,), wl["T"], dtype=torch.int32, device=dev)
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        model.decode_step(tok, pos, caches)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        logits = model.decode_step(tok, pos, caches)
+        pos += 1
+    step_i = 0
+
+    def one_step():
+        nonlocal step_i
+        tok.copy_(forced[:, step_i % forced.shape[1]], non_blocking=True)  # teacher-forced ids, already on the device
+        graph.replay()
+        step_i += 1
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        one_step()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        barrier()
+        a.record()
+        for _ in range(args.steps):
+            one_step()
+        b.record()
+        barrier()
+    ms = a.elapsed_time(b)
+    _native.poll_status(dev)
+
+    # end to end: the step's token ids come from pinned host memory, the greedy choice goes back to the host
+    tok_host = forced[:, :8].cpu().pin_memory()
+    res_host = torch.empty((B,), dtype=torch.int64).pin_memory()
+    e2e_steps = max(3, min(args.steps, 64))
+
+    def e2e_step(i):
+        tok.copy_(tok_host[:, i % 8], non_blocking=True)
+        graph.replay()
+        res_host.copy_(logits.argmax(dim=-1), non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    a2, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a2.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    b2.record()
+    barrier()
+    e2e_ms = a2.elapsed_time(b2)
+
+    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = (float(v) for v in t.cpu())
+    if rank == 0:
+        peaks = load_peaks()
+        L, D, H, w, Np = wl["layers"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
+        kv_bytes = B * L * (w + 1) * D * 2 * 2
+        weight_bytes = sum(p.numel() for p in model.parameters()) * 2
+        step_bytes = kv_bytes + weight_bytes
+        probe = decode_attention_probe(dev, peaks, batch=B, heads=H, dh=D // H, window=w, n_persistent=Np)
+        line = {
+            "metric": "decode_tokens_per_s", "value": wl["batch"] * args.steps / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload=wl_name, **wl, batch_per_gpu=B, parallelism=f"batch-sharded x{world}",
+                           decode="CUDA-graph step, teacher-forced ids", prefill_seconds=prefill_s,
+                           l2="ring caches 10.8 GB per 256 sequences >> 126 MB L2",
+                           algorithmic_bytes_per_step_per_gpu=step_bytes),
+            "roofline": dict(probe, note="decode attention kernel timed alone on this geometry",
+                             step_hbm_frac=step_bytes / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]),
+            "e2e": {"value": wl["batch"] * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": args.steps * L,
+            "clocks": clocks.report(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_long(args, wl_name: str, wl: dict) -> None:
+    """BASELINE config 5: attention core over one long sequence, rows sharded over the GPUs with a K/V halo."""
+    from oracle import windowed_oracle as wo
+    from titanmac_b200 import _native, shard
+
+    dist, world, rank, local, dev = _dist_setup(args)
+    H, w, Np = wl["heads"], wl["window"], wl["n_persistent"]
+    dh = wl["d_model"] // H
+    Ltot = Np + wl["T"]
+    bounds = shard.shard_bounds(Ltot, Np, world)
+    r0, r1 = bounds[rank]
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    own = r1 - r0
+    q, k, v = (torch.randn(1, own, H, dh, generator=g).to(torch.bfloat16).to(dev).permute(0, 2, 1, 3) for _ in range(3))
+    flops = H * live_pairs(Ltot, w, Np) * 4 * dh
+
+    def step():
+        if world == 1:
+            return _native.prefill(q, k, v, w, Np)
+        return shard.sharded_prefill(q, k, v, Ltot, w, Np)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        barrier()
+        a.record()
+        for _ in range(args.steps):
+            step()
+        b.record()
+        barrier()
+    ms = a.elapsed_time(b)
+    _native.poll_status(dev)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.cpu()[0])
+    if rank == 0:
+        peaks = load_peaks()
+        value = flops * args.steps / (ms * 1e-3) / 1e12
+        line = {
+            "metric": "windowed_attn_core_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload=wl_name, **wl, parallelism=f"sequence-sharded x{world}, halo {w} rows",
+                           l2="Q+K+V+O = 2.1 GB per step > 126 MB L2", algorithmic_flops_per_step=flops),
+            "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill)", "achieved": value / world,
+                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
+                         "peak_source": f"{peaks['source']} bf16 burst", "traffic": None,
+                         "note": "per GPU, halo exchange included when sharded"},
+            "gpu_launches": args.steps * (1 if world == 1 else 2),
+            "clocks": clocks.report(),
+        }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -331,6 +576,10 @@ def main() -> None:
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, args.workload, wl)
+    elif args.workload == "config4_decode":
+        run_decode(args, args.workload, wl)
+    elif args.workload == "config5_long_prefill":
+        run_long(args, args.workload, wl)
     else:
         run_ours(args, args.workload, wl)
 

@@ -44,7 +44,7 @@ constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per tile
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 #ifndef TMW_POLY_OF4
-#define TMW_POLY_OF4 2
+#define TMW_POLY_OF4 1
 #endif
 constexpr int kPolyOf4 = TMW_POLY_OF4;  // of every 4 column pairs, how many take the polynomial exp2
 
@@ -379,6 +379,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 #endif
 
     if (threadIdx.x == 0) {
+        // the tensor maps live in the kernel parameters; fetch them into the descriptor cache early
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kp) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vp) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_o) : "memory");
         mbar_init(bar(BAR_Q_FULL + 0), 1);
         mbar_init(bar(BAR_Q_FULL + 1), 1);
         mbar_init(bar(BAR_KP_FULL), 1);

@@ -2,6 +2,9 @@
 
 from .config import TitanMACConfig, WindowConfig
 from .attn.windowed_attention import WindowedAttention
+from .blocks.titan_block import MLPBlock, RMSNorm, TitanBlock
+from .models.titanmac import TitanMAC
 from . import _native
 
-__all__ = ["TitanMACConfig", "WindowConfig", "WindowedAttention", "_native"]
+__all__ = ["TitanMACConfig", "WindowConfig", "WindowedAttention", "TitanBlock", "RMSNorm", "MLPBlock", "TitanMAC",
+           "_native"]

@@ -1,0 +1,67 @@
+"""The block around the attention module: pre-norm residual wiring, RMSNorm and the MLP.
+
+Mirrors titans_core/blocks/titan_block.py:41-102, blocks/norms.py:39-60 and
+blocks/mlp.py:28-67 of the reference (same submodule names, so checkpoints load
+unchanged).  Only the attention is this package's own code; norm and MLP are plain
+PyTorch, as in the reference.  The reference's default ``use_block_sparse=True``
+selects a different attention class with different math, which this package does
+not provide: it is refused here instead of being silently replaced.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..attn.windowed_attention import WindowedAttention
+
+
+class RMSNorm(nn.Module):
+    """``x / sqrt(mean(x^2) + eps) * scale`` (blocks/norms.py:55-58)."""
+
+    def __init__(self, dim: int, eps: float = 1e-5):
+        super().__init__()
+        self.eps = eps
+        self.scale = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        rms = torch.sqrt(torch.mean(x ** 2, dim=-1, keepdim=True) + self.eps)
+        return x / rms * self.scale
+
+
+class MLPBlock(nn.Module):
+    """Linear(+bias) → exact GELU → Linear(+bias) (blocks/mlp.py:36-65)."""
+
+    def __init__(self, d_model: int, d_ff: int, dropout: float = 0.0):
+        super().__init__()
+        self.d_model, self.d_ff, self.dropout_p = d_model, d_ff, dropout
+        self.fc1 = nn.Linear(d_model, d_ff)
+        self.fc2 = nn.Linear(d_ff, d_model)
+        self.activation = nn.GELU()
+        self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.dropout(self.fc2(self.activation(self.fc1(x))))
+
+
+class TitanBlock(nn.Module):
+    """``x + Attention(RMSNorm(x))`` then ``x + MLP(RMSNorm(x))`` (titan_block.py:92-100)."""
+
+    def __init__(self, config):
+        super().__init__()
+        if getattr(config, "use_block_sparse", False):
+            raise NotImplementedError(
+                "use_block_sparse=True selects the reference's BlockSparseAttention, which is different math "
+                "and not part of this package; build the config with use_block_sparse=False"
+            )
+        self.config = config
+        self.norm_attn = RMSNorm(config.d_model, eps=config.norm_eps)
+        self.norm_mlp = RMSNorm(config.d_model, eps=config.norm_eps)
+        self.attention = WindowedAttention(config)
+        self.mlp = MLPBlock(d_model=config.d_model, d_ff=config.d_ff, dropout=config.dropout)
+
+    def forward(self, x: torch.Tensor, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = x + self.attention(self.norm_attn(x), attn_mask=attn_mask)
+        return x + self.mlp(self.norm_mlp(x))
