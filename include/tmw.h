@@ -134,6 +134,22 @@ TMW_API int tmw_decode(const tmw_cache_desc* cache, const void* q, const void* k
                const int64_t q_stride[2], const int64_t kv_new_stride[2], const int64_t o_stride[2],
                const int32_t* pos, void* stream);
 
+/*
+ * The same step for small batches: the keys of every (sequence, head) pair are cut into `splits` ranges
+ * (1..TMW_MAX_DECODE_SPLITS) that are scanned by separate CTAs; the CTA of a pair that finishes last merges
+ * the partial results.  Partial results and one arrival counter per pair live in caller-provided scratch
+ * memory (device, 16-byte aligned) of at least tmw_decode_split_scratch_bytes() bytes.  The scratch memory
+ * must be ZERO-FILLED ONCE before its first use with a given geometry; every call leaves the counters at
+ * zero again.  Two calls that use the same scratch memory must not overlap on the GPU.
+ * Like tmw_decode it has no counterpart in the reference (examples/train_math.py:146-161 re-runs the
+ * forward); it pays off below a few hundred pairs, where one CTA per pair cannot keep HBM busy.
+ */
+#define TMW_MAX_DECODE_SPLITS 16
+TMW_API size_t tmw_decode_split_scratch_bytes(const tmw_cache_desc* cache, int32_t splits);
+TMW_API int tmw_decode_split(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new, void* o,
+                     const int64_t q_stride[2], const int64_t kv_new_stride[2], const int64_t o_stride[2],
+                     const int32_t* pos, int32_t splits, void* scratch, size_t scratch_bytes, void* stream);
+
 /* Library facts. */
 TMW_API int tmw_version(void);
 TMW_API const char* tmw_strerror(int status);

@@ -126,3 +126,19 @@ def test_cache_entry_points_reject_bad_arguments_on_the_host():
     assert lib.tmw_decode(ctypes.byref(c), ok, ok, ok, ok, s2, s2, s2, ok, None) == _native.TMW_ERR_UNSUPPORTED
     c.head_dim = 64  # rings are NULL
     assert lib.tmw_decode(ctypes.byref(c), ok, ok, ok, ok, s2, s2, s2, ok, None) == _native.TMW_ERR_INVALID_ARGUMENT
+
+
+def test_split_decode_scratch_size_and_argument_checks():
+    lib = _native.lib()
+    c = _native.CacheDesc()
+    c.dtype, c.batch, c.heads, c.head_dim, c.window, c.n_persistent = _native.TMW_BF16, 32, 10, 64, 512, 0
+    c.k_ring = c.v_ring = 0x1000
+    assert lib.tmw_decode_split_scratch_bytes(ctypes.byref(c), 4) == 32 * 10 * 4 * (64 + 2) * 4 + 32 * 10 * 4
+    assert lib.tmw_decode_split_scratch_bytes(ctypes.byref(c), 0) == 0
+    assert lib.tmw_decode_split_scratch_bytes(ctypes.byref(c), _native.MAX_DECODE_SPLITS + 1) == 0
+    s2 = (ctypes.c_int64 * 2)(640, 64)
+    ok = ctypes.c_void_p(0x1000)
+    args = (ctypes.byref(c), ok, ok, ok, ok, s2, s2, s2, ok)
+    assert lib.tmw_decode_split(*args, 0, ok, 1 << 30, None) == _native.TMW_ERR_INVALID_ARGUMENT   # splits
+    assert lib.tmw_decode_split(*args, 4, None, 1 << 30, None) == _native.TMW_ERR_INVALID_ARGUMENT  # no scratch
+    assert lib.tmw_decode_split(*args, 4, ok, 1024, None) == _native.TMW_ERR_TOO_LARGE            # scratch too small

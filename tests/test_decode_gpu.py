@@ -90,3 +90,36 @@ def test_cache_fill_keeps_only_the_window():
     assert sorted(ring) == [7.0, 8.0, 9.0, 10.0, 11.0]       # row i holds value i = token 3+i
     for tok in range(10, 15):
         assert ring[tok % 5] == float(tok - 3)
+
+
+@pytest.mark.parametrize("splits", [0, 1, 3, 16])
+def test_split_and_unsplit_decode_agree(splits):
+    """The split launch (partials in scratch memory + merge kernel) returns what the one-CTA-per-pair launch
+    returns, for every split count, with ragged positions (some splits of short sequences are empty)."""
+    dh, w, Np, B, H = 64, 200, 16, 5, 3
+    L = Np + 400
+    q, k, v = (t.to(torch.bfloat16) for t in wo.qkv_inputs(B, H, L, dh, seed=21))
+    k[1:, :, :Np] = k[:1, :, :Np]
+    v[1:, :, :Np] = v[:1, :, :Np]
+    ts = [0, 1, 57, 200, 399]
+    outs = []
+    for s in (splits, 0):
+        cache = _native.RingCache(B, H, dh, w, Np, torch.bfloat16, DEV)
+        cache.splits = s
+        cache.set_persistent(k[0, :, :Np].to(DEV), v[0, :, :Np].to(DEV))
+        for b, t in enumerate(ts):
+            if t > 0:
+                cb = _native.RingCache(1, H, dh, w, Np, torch.bfloat16, DEV)
+                cb.fill(k[b:b + 1, :, Np:Np + t].to(DEV), v[b:b + 1, :, Np:Np + t].to(DEV))
+                cache.k_ring[b].copy_(cb.k_ring[0])
+                cache.v_ring[b].copy_(cb.v_ring[0])
+        qn = torch.stack([q[b, :, Np + t] for b, t in enumerate(ts)]).to(DEV)
+        kn = torch.stack([k[b, :, Np + t] for b, t in enumerate(ts)]).to(DEV)
+        vn = torch.stack([v[b, :, Np + t] for b, t in enumerate(ts)]).to(DEV)
+        pos = torch.tensor(ts, dtype=torch.int32, device=DEV)
+        outs.append((cache.decode(qn, kn, vn, pos).float().cpu(), cache.k_ring.clone().cpu()))
+    assert (outs[0][0] - outs[1][0]).abs().max().item() <= 4e-3   # same math, different merge order
+    assert torch.equal(outs[0][1], outs[1][1])                    # the new token landed in the same slots
+    for b, t in enumerate(ts):
+        want = wo.attention_core_rows(q[b:b + 1, :, Np + t:Np + t + 1], k[b:b + 1], v[b:b + 1], Np + t, w, Np)
+        assert (outs[0][0][b] - want[0, :, 0]).abs().max().item() <= 2e-2

@@ -95,6 +95,24 @@ int validate_cache(const tmw_cache_desc* c) {
 }
 
 }  // namespace
+
+// Checks shared by every decode entry point (everything except the scratch memory).
+int validate_decode_call(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new,
+                         const void* o, const int64_t q_stride[2], const int64_t kv_new_stride[2],
+                         const int64_t o_stride[2], const int32_t* pos) {
+    const int rc = validate_cache(cache);
+    if (rc != TMW_OK) return rc;
+    if (q_stride == nullptr || kv_new_stride == nullptr || o_stride == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (cache->batch == 0 || cache->heads == 0) return TMW_OK;
+    if (q == nullptr || k_new == nullptr || v_new == nullptr || o == nullptr || pos == nullptr)
+        return TMW_ERR_INVALID_ARGUMENT;
+    if (!aligned16(q) || !aligned16(k_new) || !aligned16(v_new) || !aligned16(o)) return TMW_ERR_INVALID_ARGUMENT;
+    if (!strides_ok(q_stride, 2, cache->dtype) || !strides_ok(kv_new_stride, 2, cache->dtype) ||
+        !strides_ok(o_stride, 2, cache->dtype))
+        return TMW_ERR_INVALID_ARGUMENT;
+    return TMW_OK;
+}
+
 }  // namespace tmw
 
 extern "C" {
@@ -153,19 +171,32 @@ int tmw_cache_fill(const tmw_cache_desc* cache, const void* k, const void* v, co
 int tmw_decode(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new, void* o,
                const int64_t q_stride[2], const int64_t kv_new_stride[2], const int64_t o_stride[2],
                const int32_t* pos, void* stream) {
-    const int rc = tmw::validate_cache(cache);
+    const int rc = tmw::validate_decode_call(cache, q, k_new, v_new, o, q_stride, kv_new_stride, o_stride, pos);
     if (rc != TMW_OK) return rc;
-    if (q_stride == nullptr || kv_new_stride == nullptr || o_stride == nullptr) return TMW_ERR_INVALID_ARGUMENT;
     if (cache->batch == 0 || cache->heads == 0) return TMW_OK;
-    if (q == nullptr || k_new == nullptr || v_new == nullptr || o == nullptr || pos == nullptr)
-        return TMW_ERR_INVALID_ARGUMENT;
-    if (!tmw::aligned16(q) || !tmw::aligned16(k_new) || !tmw::aligned16(v_new) || !tmw::aligned16(o))
-        return TMW_ERR_INVALID_ARGUMENT;
-    if (!tmw::strides_ok(q_stride, 2, cache->dtype) || !tmw::strides_ok(kv_new_stride, 2, cache->dtype) ||
-        !tmw::strides_ok(o_stride, 2, cache->dtype))
-        return TMW_ERR_INVALID_ARGUMENT;
-    return tmw::launch_decode(*cache, q, k_new, v_new, o, q_stride, kv_new_stride, o_stride, pos,
+    return tmw::launch_decode(*cache, q, k_new, v_new, o, q_stride, kv_new_stride, o_stride, pos, 0, nullptr, nullptr,
                               static_cast<cudaStream_t>(stream));
+}
+
+size_t tmw_decode_split_scratch_bytes(const tmw_cache_desc* cache, int32_t splits) {
+    if (tmw::validate_cache(cache) != TMW_OK || splits < 1 || splits > TMW_MAX_DECODE_SPLITS) return 0;
+    return tmw::decode_partials_bytes(cache->batch, cache->heads, cache->head_dim, splits) +
+           (size_t)cache->batch * (size_t)cache->heads * sizeof(unsigned int);
+}
+
+int tmw_decode_split(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new, void* o,
+                     const int64_t q_stride[2], const int64_t kv_new_stride[2], const int64_t o_stride[2],
+                     const int32_t* pos, int32_t splits, void* scratch, size_t scratch_bytes, void* stream) {
+    const int rc = tmw::validate_decode_call(cache, q, k_new, v_new, o, q_stride, kv_new_stride, o_stride, pos);
+    if (rc != TMW_OK) return rc;
+    if (splits < 1 || splits > TMW_MAX_DECODE_SPLITS) return TMW_ERR_INVALID_ARGUMENT;
+    if (cache->batch == 0 || cache->heads == 0) return TMW_OK;
+    if (scratch == nullptr || !tmw::aligned16(scratch)) return TMW_ERR_INVALID_ARGUMENT;
+    if (scratch_bytes < tmw_decode_split_scratch_bytes(cache, splits)) return TMW_ERR_TOO_LARGE;
+    unsigned int* counters = reinterpret_cast<unsigned int*>(
+        static_cast<char*>(scratch) + tmw::decode_partials_bytes(cache->batch, cache->heads, cache->head_dim, splits));
+    return tmw::launch_decode(*cache, q, k_new, v_new, o, q_stride, kv_new_stride, o_stride, pos, splits,
+                              static_cast<float*>(scratch), counters, static_cast<cudaStream_t>(stream));
 }
 
 int tmw_poll_status(void* stream) {

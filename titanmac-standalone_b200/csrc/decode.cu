@@ -31,6 +31,9 @@ struct DecodeParams {
     long long qs[2], ns[2], os[2];
     int batch, heads, slots, np;
     float scale_log2;
+    int splits;              // > 0: the keys of a pair are cut into this many ranges, one CTA each
+    float* scratch;          // [pairs][splits][DH + 2] partial results (accumulator, running maximum, sum)
+    unsigned int* counters;  // [pairs] arrivals of a pair's CTAs; zero between launches
 };
 
 // 8 consecutive elements as raw bits, loaded through the read-only path without keeping
@@ -91,7 +94,11 @@ struct Raw8<__half> {
 //   WARPS 2: 1 pair  per 64-thread CTA, 9 CTAs per SM  -> up to 1332 pairs
 //   WARPS 4: 1 pair  per 128-thread CTA, 4 per SM      -> up to  592 pairs
 //   WARPS 8: 1 pair  per 256-thread CTA, 2 per SM      -> up to  296 pairs
-template <typename T, int DH, int WARPS>
+//
+// SPLIT: few pairs (small batches).  A pair's keys are cut into p.splits ranges, each scanned by its own
+// CTA, which leaves an unnormalised partial result in scratch memory and counts itself in; the CTA that
+// arrives last merges the pair's partial results, writes the output and puts the counter back to zero.
+template <typename T, int DH, int WARPS, bool SPLIT = false>
 __global__ void __launch_bounds__(WARPS == 1 ? 64 : WARPS * 32, WARPS <= 2 ? 9 : (WARPS == 4 ? 4 : 2))
 decode_kernel(const DecodeParams p) {
     // 16-byte loads in flight per lane for K, and again for V; fewer in the shapes with many resident
@@ -103,7 +110,8 @@ decode_kernel(const DecodeParams p) {
     static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "head_dim must be 8 * 2^n, at most 256");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int pair = WARPS == 1 ? blockIdx.x * 2 + warp : blockIdx.x;
+    const int pair = SPLIT ? blockIdx.x / p.splits : (WARPS == 1 ? blockIdx.x * 2 + warp : blockIdx.x);
+    const int split = SPLIT ? blockIdx.x % p.splits : 0;
     if (pair >= p.batch * p.heads) return;  // whole warps leave together; no block barrier when WARPS == 1
     const int b = pair / p.heads, h = pair % p.heads;
     const int wslot = WARPS == 1 ? 0 : warp;  // which share of the keys this warp scans
@@ -126,11 +134,14 @@ decode_kernel(const DecodeParams p) {
 
     // Virtual key index i: [0, np) persistent keys, np = the new token (read from k_new / v_new, so the
     // ring slot written below is never read back), then the count-1 older ring slots in slot order.
-    const int n_keys = p.np + count;
+    const int n_all = p.np + count;
+    const int per_split = SPLIT ? (n_all + p.splits - 1) / p.splits : n_all;
+    const int k_lo = split * per_split;
+    const int n_keys = min(n_all, k_lo + per_split);  // this CTA scans the virtual keys [k_lo, n_keys)
     float m = -CUDART_INF_F, l = 0.f;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 
-    for (int i0 = 0; i0 < n_keys; i0 += STRIDE * UNROLL) {
+    for (int i0 = k_lo; i0 < n_keys; i0 += STRIDE * UNROLL) {
         Raw8<T> kraw[UNROLL], vraw[UNROLL];
         bool ok[UNROLL];
 #pragma unroll
@@ -194,7 +205,7 @@ decode_kernel(const DecodeParams p) {
     }
 
     // the new token's key and value go into their ring slot for the following steps
-    if (wslot == 0 && grp == 0) {
+    if (wslot == 0 && grp == 0 && split == 0) {
         float tmp[8];
         load8<T>(kn + sub * 8, tmp);
         store8<T>(kr + (long long)slot_new * DH + sub * 8, tmp);
@@ -254,10 +265,48 @@ decode_kernel(const DecodeParams p) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) res[e] += sm_acc[w][tid * 8 + e] * a;
             }
-            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+            if (SPLIT) {
+                float* part = p.scratch + ((long long)pair * p.splits + split) * (DH + 2);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) res[e] *= inv;
-            store8<T>(out + tid * 8, res);
+                for (int e = 0; e < 8; ++e) part[tid * 8 + e] = res[e];
+                if (tid == 0) {
+                    part[DH] = m_all;
+                    part[DH + 1] = l_all;
+                }
+            } else {
+                const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) res[e] *= inv;
+                store8<T>(out + tid * 8, res);
+            }
+        }
+        if (SPLIT) {
+            // last CTA of the pair merges (the usual fence / counter / fence hand-over through global memory)
+            __shared__ int is_last;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                const unsigned int prev = atomicAdd(p.counters + pair, 1u);
+                is_last = prev == (unsigned int)p.splits - 1u;
+            }
+            __syncthreads();
+            if (is_last) {
+                __threadfence();
+                const volatile float* all = p.scratch + (long long)pair * p.splits * (DH + 2);
+                float m_all = -CUDART_INF_F;
+                for (int sp = 0; sp < p.splits; ++sp) m_all = fmaxf(m_all, all[sp * (DH + 2) + DH]);
+                for (int d = tid; d < DH; d += WARPS * 32) {
+                    float l_all = 0.f, a_all = 0.f;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        const float m_s = all[sp * (DH + 2) + DH];
+                        const float a = m_s > -CUDART_INF_F ? exp2f(m_s - m_all) : 0.f;
+                        l_all += all[sp * (DH + 2) + DH + 1] * a;
+                        a_all += all[sp * (DH + 2) + d] * a;
+                    }
+                    out[d] = from_f32<T>(l_all > 0.f ? a_all / l_all : 0.f);
+                }
+                if (tid == 0) p.counters[pair] = 0u;  // ready for the next launch
+            }
         }
     }
 }
@@ -293,6 +342,11 @@ __global__ void cache_fill_kernel(const FillParams p) {
 template <typename T, int DH>
 int launch_decode_shape(const DecodeParams& p, cudaStream_t stream) {
     const int pairs = p.batch * p.heads;
+    if (p.splits > 0) {
+        decode_kernel<T, DH, 4, true><<<pairs * p.splits, 128, 0, stream>>>(p);
+        TMW_CUDA_TRY(cudaGetLastError());
+        return TMW_OK;
+    }
     int sms = 148;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -326,7 +380,7 @@ int launch_decode_dh(const DecodeParams& p, int dh, cudaStream_t stream) {
 
 int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, const void* v_new, void* o,
                   const int64_t qs[2], const int64_t ns[2], const int64_t os[2], const int32_t* pos,
-                  cudaStream_t stream) {
+                  int splits, float* scratch, unsigned int* counters, cudaStream_t stream) {
     if (c.batch == 0 || c.heads == 0) return TMW_OK;
     if ((long long)c.batch * c.heads > (1LL << 30)) return TMW_ERR_TOO_LARGE;
     DecodeParams p;
@@ -334,6 +388,7 @@ int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, con
     p.q = q; p.k_new = k_new; p.v_new = v_new; p.o = o; p.pos = pos;
     for (int i = 0; i < 2; ++i) { p.qs[i] = qs[i]; p.ns[i] = ns[i]; p.os[i] = os[i]; }
     p.batch = c.batch; p.heads = c.heads; p.slots = c.window + 1; p.np = c.n_persistent;
+    p.splits = splits; p.scratch = scratch; p.counters = counters;
     const float scale = c.scale != 0.f ? c.scale : 1.0f / sqrtf((float)c.head_dim);
     p.scale_log2 = scale * 1.4426950408889634f;
     switch (c.dtype) {

@@ -110,7 +110,13 @@ int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, c
 bool prefill_tc_supports(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o);
 int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, const void* v_new, void* o,
                   const int64_t qs[2], const int64_t ns[2], const int64_t os[2], const int32_t* pos,
-                  cudaStream_t stream);
+                  int splits, float* scratch, unsigned int* counters, cudaStream_t stream);
+
+// layout of the split-decode scratch memory: partial results, then (16-byte aligned) one counter per pair
+inline size_t decode_partials_bytes(int batch, int heads, int head_dim, int splits) {
+    const size_t n = (size_t)batch * heads * splits * ((size_t)head_dim + 2) * sizeof(float);
+    return (n + 15) & ~(size_t)15;
+}
 int launch_cache_fill(const tmw_cache_desc& c, const void* k, const void* v, const int64_t ks[3],
                       const int64_t vs[3], int rows, int t0, cudaStream_t stream);
 

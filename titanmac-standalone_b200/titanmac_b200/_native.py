@@ -102,7 +102,16 @@ SIGNATURES = {
          ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
          ctypes.c_void_p, ctypes.c_void_p],
     ),
+    "tmw_decode_split_scratch_bytes": (ctypes.c_size_t, [ctypes.POINTER(CacheDesc), ctypes.c_int32]),
+    "tmw_decode_split": (
+        ctypes.c_int,
+        [ctypes.POINTER(CacheDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+         ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
+         ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p],
+    ),
 }
+
+MAX_DECODE_SPLITS = 16
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -212,6 +221,20 @@ class RingCache:
         self.v_ring = torch.zeros_like(self.k_ring)
         self.k_pers = torch.zeros((heads, n_persistent, head_dim), dtype=dtype, device=device)
         self.v_pers = torch.zeros_like(self.k_pers)
+        # A handful of (sequence, head) pairs with a long window cannot fill the GPU with one CTA per pair:
+        # then every pair's keys are split over several CTAs (tmw_decode_split) through a scratch buffer
+        # owned by this object.  Measured on B200: it wins from about 2000 keys per pair and fewer pairs than
+        # half the SMs; at window 512 the unsplit launch is faster for every batch size.
+        self.splits = self.pick_splits(batch * heads, self.slots, self.device)
+        self._scratch = None
+
+    @staticmethod
+    def pick_splits(pairs: int, slots: int, device) -> int:
+        """0 = one CTA (or warp) per pair; otherwise the number of key ranges per pair."""
+        sms = torch.cuda.get_device_properties(device).multi_processor_count if torch.cuda.is_available() else 148
+        if pairs == 0 or 2 * pairs > sms or slots < 1024:
+            return 0
+        return max(2, min(MAX_DECODE_SPLITS, 2 * sms // pairs, slots // 128))
 
     def desc(self) -> CacheDesc:
         c = CacheDesc()
@@ -257,8 +280,17 @@ class RingCache:
         ns = (ctypes.c_int64 * 2)(k_new.stride(0), k_new.stride(1))
         os_ = (ctypes.c_int64 * 2)(out.stride(0), out.stride(1))
         with torch.cuda.device(self.device):
-            check(lib().tmw_decode(ctypes.byref(c), q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
-                                   out.data_ptr(), qs, ns, os_, pos.data_ptr(), _stream_ptr(self.device)))
+            if self.splits > 0:
+                if self._scratch is None:
+                    nbytes = lib().tmw_decode_split_scratch_bytes(ctypes.byref(c), self.splits)
+                    self._scratch = torch.zeros(nbytes // 4, dtype=torch.float32, device=self.device)  # counters start at 0
+                check(lib().tmw_decode_split(ctypes.byref(c), q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+                                             out.data_ptr(), qs, ns, os_, pos.data_ptr(), self.splits,
+                                             self._scratch.data_ptr(), self._scratch.numel() * 4,
+                                             _stream_ptr(self.device)))
+            else:
+                check(lib().tmw_decode(ctypes.byref(c), q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+                                       out.data_ptr(), qs, ns, os_, pos.data_ptr(), _stream_ptr(self.device)))
         return out
 
 
