@@ -150,6 +150,27 @@ TMW_API int tmw_decode_split(const tmw_cache_desc* cache, const void* q, const v
                      const int64_t q_stride[2], const int64_t kv_new_stride[2], const int64_t o_stride[2],
                      const int32_t* pos, int32_t splits, void* scratch, size_t scratch_bytes, void* stream);
 
+/*
+ * tmw_decode_split for callers that cannot allocate device memory (no counterpart in the reference).
+ *
+ * Who needs it: a serving process that gave all of HBM to its own memory pool and forbids cudaMalloc
+ * after start-up, or a decode loop in which an allocation - a synchronising driver call - is not
+ * acceptable.  The scratch memory of the split launch is then a fixed 2 MiB array inside the library
+ * (one per GPU that loads the library, held until the process exits) instead of a caller buffer.
+ *
+ * Limits: batch x heads <= 4096 and batch x heads x splits x (head_dim + 2) x 4 bytes <= 2 MiB - 16 KiB;
+ * anything larger returns TMW_ERR_TOO_LARGE (tmw_last_cuda_error() says by how much).  The call never
+ * calls cudaMalloc, cudaFree or any other allocating routine.
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress with that device
+ * current); make that first call outside any stream capture.  All calls on one GPU share the one array:
+ * every call clears the arrival counters it needs and overwrites the partial results, so calls may follow
+ * one another on a stream, but two calls that overlap on the GPU (different streams) race.
+ */
+TMW_API int tmw_decode_split_static(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new,
+                            void* o, const int64_t q_stride[2], const int64_t kv_new_stride[2],
+                            const int64_t o_stride[2], const int32_t* pos, int32_t splits, void* stream);
+
 /* Library facts. */
 TMW_API int tmw_version(void);
 TMW_API const char* tmw_strerror(int status);

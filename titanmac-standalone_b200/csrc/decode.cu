@@ -12,6 +12,8 @@
 // quantisation); with few pairs a whole CTA of 8 warps shares one pair.
 #include <math_constants.h>
 
+#include <cstdio>
+
 #include "tmw_common.cuh"
 
 namespace tmw {
@@ -422,3 +424,76 @@ int launch_cache_fill(const tmw_cache_desc& c, const void* k, const void* v, con
 }
 
 }  // namespace tmw
+
+// -----------------------------------------------------------------------------------------------------
+// Split decode without any allocation.
+//
+// Some hosts may not allocate device memory around a decode step: an inference server that has handed
+// all HBM to its own pool and forbids cudaMalloc after start-up, or a latency-critical loop in which an
+// allocation (a synchronising driver call) is unacceptable.  For them the scratch memory of the split
+// launch is a fixed array inside this library.  It exists once per GPU that loads the library and stays
+// until the process exits; its size is the limit of this entry point.
+//
+// In host code the array's NAME is only a handle for the runtime, not a device address.  The device
+// address is asked for once per device (cudaGetSymbolAddress, with that device current) and kept.
+// -----------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticCounterBytes = 16 * 1024;            // 4096 arrival counters, always at the start
+constexpr size_t kStaticScratchBytes = 2 * 1024 * 1024;      // the whole array: counters, then partial results
+constexpr int kStaticMaxPairs = (int)(kStaticCounterBytes / sizeof(unsigned int));
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+// device address of the array on the current device; nullptr (and the CUDA error recorded) on failure
+unsigned char* static_scratch_on_current_device() {
+    constexpr int kMaxDevices = 64;
+    static unsigned char* address[kMaxDevices] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        tmw::set_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidDevice, "cudaGetDevice");
+        return nullptr;
+    }
+    if (address[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+        if (e != cudaSuccess) {
+            tmw::set_cuda_error(e, "cudaGetSymbolAddress(g_decode_static_scratch)");
+            return nullptr;
+        }
+        address[dev] = static_cast<unsigned char*>(ptr);
+    }
+    return address[dev];
+}
+
+}  // namespace
+
+extern "C" int tmw_decode_split_static(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new,
+                                       void* o, const int64_t q_stride[2], const int64_t kv_new_stride[2],
+                                       const int64_t o_stride[2], const int32_t* pos, int32_t splits, void* stream) {
+    const int rc = tmw::validate_decode_call(cache, q, k_new, v_new, o, q_stride, kv_new_stride, o_stride, pos);
+    if (rc != TMW_OK) return rc;
+    if (splits < 1 || splits > TMW_MAX_DECODE_SPLITS) return TMW_ERR_INVALID_ARGUMENT;
+    if (cache->batch == 0 || cache->heads == 0) return TMW_OK;
+    const long long pairs = (long long)cache->batch * cache->heads;
+    const size_t partial_bytes = tmw::decode_partials_bytes(cache->batch, cache->heads, cache->head_dim, splits);
+    if (pairs > kStaticMaxPairs || partial_bytes > kStaticScratchBytes - kStaticCounterBytes) {
+        char text[200];
+        std::snprintf(text, sizeof(text),
+                      "tmw_decode_split_static: %lld pairs x %d splits need %zu bytes of partial results; the built-in "
+                      "scratch memory holds %d pairs and %zu bytes",
+                      pairs, (int)splits, partial_bytes, kStaticMaxPairs, kStaticScratchBytes - kStaticCounterBytes);
+        tmw::set_error_text(text);
+        return TMW_ERR_TOO_LARGE;
+    }
+    unsigned char* base = static_scratch_on_current_device();
+    if (base == nullptr) return TMW_ERR_CUDA;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the last call left in it.  Partial results are rewritten completely by every
+    // launch; the arrival counters must start at zero, so they are cleared here (an aborted earlier launch
+    // could have left them half counted).
+    TMW_CUDA_TRY(cudaMemsetAsync(base, 0, (size_t)pairs * sizeof(unsigned int), s));
+    return tmw::launch_decode(*cache, q, k_new, v_new, o, q_stride, kv_new_stride, o_stride, pos, splits,
+                              reinterpret_cast<float*>(base + kStaticCounterBytes),
+                              reinterpret_cast<unsigned int*>(base), s);
+}

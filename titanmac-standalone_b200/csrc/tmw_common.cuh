@@ -102,6 +102,11 @@ int* device_status_word();  // per-device int in global memory, 0 = fine
         }                                                    \
     } while (0)
 
+// Argument checks shared by the decode entry points (defined with the entry points in api.cu).
+int validate_decode_call(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new,
+                         const void* o, const int64_t q_stride[2], const int64_t kv_new_stride[2],
+                         const int64_t o_stride[2], const int32_t* pos);
+
 // Kernel launchers (one per translation unit).
 int launch_prefill_simt(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
                         cudaStream_t stream);

@@ -109,6 +109,12 @@ SIGNATURES = {
          ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
          ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p],
     ),
+    "tmw_decode_split_static": (
+        ctypes.c_int,
+        [ctypes.POINTER(CacheDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+         ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
+         ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p],
+    ),
 }
 
 MAX_DECODE_SPLITS = 16
