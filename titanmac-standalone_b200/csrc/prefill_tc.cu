@@ -38,27 +38,53 @@
 namespace tmw {
 namespace {
 
-constexpr int kThreadsTc = 384;
-static_assert(128 * (168 - 80) >= 256 * (208 - 168), "setmaxnreg: the issuing warps must release what the softmax warps request");
+// Threads and register budget per query tiles of a CTA.  Two tiles: 384 threads launched with 168 registers
+// (one CTA per SM).  One tile: 256 threads launched with 128 registers (two CTAs per SM).  The four
+// producer / issuing warps shrink to kRegsService, the softmax warps grow to kRegsSoftmax; setmaxnreg.inc
+// blocks until the registers it asks for have been released INSIDE THE CTA and nothing bounds that wait, so
+// the numbers must add up.
+template <int TILES>
+struct Budget {
+    static constexpr int kThreads = 128 + TILES * 128;
+    static constexpr int kRegsLaunch = TILES == 2 ? 168 : 128;
+    static constexpr int kRegsService = TILES == 2 ? 80 : 56;
+    static constexpr int kRegsSoftmax = TILES == 2 ? 208 : 200;
+    static_assert(kThreads * kRegsLaunch <= 65536 / (TILES == 2 ? 1 : 2), "register file");
+    static_assert(128 * (kRegsLaunch - kRegsService) >= TILES * 128 * (kRegsSoftmax - kRegsLaunch),
+                  "setmaxnreg: the issuing warps must release what the softmax warps request");
+};
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per tile
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 #ifndef TMW_POLY_OF4
 #define TMW_POLY_OF4 1
 #endif
-constexpr int kPolyOf4 = TMW_POLY_OF4;  // of every 4 column pairs, how many take the polynomial exp2
+constexpr int kPolyOf4 = TMW_POLY_OF4;
+#ifndef TMW_ALTERNATE
+#define TMW_ALTERNATE 2
+#endif
+// the two softmax groups take turns with their exponentials: 0 never, 1 always, 2 only for head_dim 128
+// (measured: +10 % at head_dim 128 / window 1024, -6 % at head_dim 64 / window 512)
+template <int DH>
+struct Alternate { static constexpr bool value = TMW_ALTERNATE == 1 || (TMW_ALTERNATE == 2 && DH == 128); };  // of every 4 column pairs, how many take the polynomial exp2
 
 // tensor-memory columns (32-bit each, 128 lanes): S0 | S1 | O0 | O1; P aliases S
-constexpr uint32_t kTmemCols = 512;
 // head_dim 64 : S0 0 | S1 128 | P0 256 | P1 320 | O0 384 | O1 448   (P has its own columns: the next QK
 //                may overwrite S while the softmax group still turns the previous S into P)
 // head_dim 128: S0 0 | S1 128 | O0 256 | O1 384                      (P is written over S)
-template <int DH>
+// one query tile per CTA (256 columns, two CTAs share the SM's 512):
+// head_dim 64 : S 0 | P 128 | O 192        head_dim 128: S 0 | O 128
+template <int DH, int TILES>
 struct TmemMap {
     static constexpr bool kSplitP = DH == 64;
+    static constexpr uint32_t kCols = TILES * 256;
     __host__ __device__ static constexpr uint32_t s(int t) { return t == 0 ? 0u : 128u; }
-    __host__ __device__ static constexpr uint32_t p(int t) { return kSplitP ? (t == 0 ? 256u : 320u) : s(t); }
-    __host__ __device__ static constexpr uint32_t o(int t) { return kSplitP ? (t == 0 ? 384u : 448u) : (t == 0 ? 256u : 384u); }
+    __host__ __device__ static constexpr uint32_t p(int t) {
+        return TILES == 1 ? (kSplitP ? 128u : 0u) : kSplitP ? (t == 0 ? 256u : 320u) : s(t);
+    }
+    __host__ __device__ static constexpr uint32_t o(int t) {
+        return TILES == 1 ? (kSplitP ? 192u : 128u) : kSplitP ? (t == 0 ? 384u : 448u) : (t == 0 ? 256u : 384u);
+    }
 };
 
 #ifdef TMW_TRACE
@@ -292,9 +318,9 @@ struct CtaPlan {
 
 __device__ __forceinline__ int floor_div(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
 
-__device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block) {
+__device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block, int tiles) {
     CtaPlan c;
-    const int r0 = block * 2 * BM;
+    const int r0 = block * tiles * BM;
     c.anchor = p.q_pos0 + r0 - p.window;
     c.x_begin = 1 << 30;
     c.x_end = 0;
@@ -302,7 +328,7 @@ __device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block) {
     for (int t = 0; t < 2; ++t) {
         QtPlan& q = c.qt[t];
         q.p_lo = p.q_pos0 + r0 + t * BM;
-        q.rows = max(0, min(BM, p.q_rows - (r0 + t * BM)));
+        q.rows = t < tiles ? max(0, min(BM, p.q_rows - (r0 + t * BM))) : 0;
         q.has_pers = (q.rows > 0 && p.np > 0) ? 1 : 0;
         const int p_hi = q.p_lo + q.rows - 1;
         if (q.rows > 0 && p_hi >= p.np) {
@@ -324,12 +350,12 @@ __device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block) {
 // ---------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------
-template <int DH, int KS, int VS>
+template <int DH, int KS, int VS, int TILES>
 struct TcSmem {
     static constexpr int kTileBytes = BN * DH * 2;       // one K or V or Q tile
     static constexpr int kSubTileBytes = BN * 128;       // 128 rows x 64 columns of 16-bit
-    static constexpr int kQ = 0;                         // 2 tiles
-    static constexpr int kK = kQ + 2 * kTileBytes;       // KS tiles
+    static constexpr int kQ = 0;                         // TILES tiles
+    static constexpr int kK = kQ + TILES * kTileBytes;   // KS tiles
     static constexpr int kV = kK + KS * kTileBytes;      // VS tiles
     static constexpr int kP = kV + VS * kTileBytes;      // persistent K then V: np_pad x DH x 2 bytes each
     static int total_bytes(int np_pad) { return kP + 2 * np_pad * DH * 2 + 1024 /*barriers*/ + 1024 /*alignment*/; }
@@ -348,16 +374,18 @@ enum BarSlot {
     BAR_V_EMPTY = 21,      // [VS]
     BAR_S_FREE = 25,       // [2] softmax group has S in registers (only when P has its own columns)
     BAR_PV_DONE = 27,      // [2] P V of the previous item has finished (only when P has its own columns)
-    BAR_COUNT = 29
+    BAR_TURN = 29,         // [2] the other softmax group has finished its exponentials (alternation)
+    BAR_COUNT = 31
 };
 
-template <int DH, int KS, int VS, bool BF16>
-__global__ void __launch_bounds__(kThreadsTc, 1)
+template <int DH, int KS, int VS, bool BF16, int TILES>
+__global__ void __launch_bounds__(Budget<TILES>::kThreads, TILES == 2 ? 1 : 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                   const __grid_constant__ CUtensorMap map_kp, const __grid_constant__ CUtensorMap map_vp,
                   const TcParams p) {
-    using L = TcSmem<DH, KS, VS>;
+    using L = TcSmem<DH, KS, VS, TILES>;
+    constexpr uint32_t kTmemCols = TmemMap<DH, TILES>::kCols;
     constexpr int NSUB = DH / 64;  // 64-column sub-tiles per tile
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -372,7 +400,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y, batch = blockIdx.z;
-    const CtaPlan plan = make_plan(p, blockIdx.x);
+    const CtaPlan plan = make_plan(p, blockIdx.x, TILES);
 #ifdef TMW_TRACE
     const bool trace_on = blockIdx.x == 8 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
     if (trace_on && threadIdx.x == 0) g_trace[0] = clock64();
@@ -395,14 +423,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             mbar_init(bar(BAR_O_DONE + t), 1);
             mbar_init(bar(BAR_S_FREE + t), BM / 32);
             mbar_init(bar(BAR_PV_DONE + t), 1);
+            mbar_init(bar(BAR_TURN + t), BM / 32);
         }
         for (int s = 0; s < KS; ++s) {
             mbar_init(bar(BAR_K_FULL + s), 1);
-            mbar_init(bar(BAR_K_EMPTY + s), 2);  // one arrival per issuing warp
+            mbar_init(bar(BAR_K_EMPTY + s), TILES);  // one arrival per issuing warp
         }
         for (int s = 0; s < VS; ++s) {
             mbar_init(bar(BAR_V_FULL + s), 1);
-            mbar_init(bar(BAR_V_EMPTY + s), 2);
+            mbar_init(bar(BAR_V_EMPTY + s), TILES);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -424,23 +453,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     };
 
     if (warp < 4) {
-        // Register budget.  The CTA is launched with 384 x 168 registers; setmaxnreg.inc below blocks until
-        // the registers it asks for have been released INSIDE THIS CTA, and nothing bounds that wait, so
-        // the numbers must add up:  released 128 x (168 - 80) = 11264  >=  requested 256 x (208 - 168) = 10240.
-#ifndef TMW_NO_SETMAXNREG
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::: "memory");
-#endif
+        // register budget: see Budget<TILES>
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Budget<TILES>::kRegsService) : "memory");
         // Every role warp runs its loop with all 32 lanes (so the warp never splits into a running
         // lane and 31 lanes parked at the final barrier); one lane issues the asynchronous operations.
         const bool leader = lane == 0;
         if (warp == 0) {
             // ---------------- producer: Q tiles, then K tiles ----------------
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
+            for (int t = 0; t < TILES; ++t) {
                 if (plan.qt[t].rows == 0 || !leader) continue;
                 mbar_expect_tx(bar(BAR_Q_FULL + t), L::kTileBytes);
                 int c1, c2;
-                coords(0, blockIdx.x * 2 * BM + t * BM, c1, c2);
+                coords(0, (blockIdx.x * TILES + t) * BM, c1, c2);
                 for (int s = 0; s < NSUB; ++s)
                     tma_load_4d(smem_base + L::kQ + t * L::kTileBytes + s * L::kSubTileBytes, &map_q,
                                 bar(BAR_Q_FULL + t), s * 64, c1, c2, batch);
@@ -486,7 +511,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 __syncwarp();
             }
-        } else {
+        } else if (warp - 2 < TILES) {
             // ---------------- tensor-core issue: warp 2 drives query tile 0, warp 3 query tile 1 ----------------
             // Each warp issues, for its own query tile, QK of item i+1 right after PV of item i (P aliases S, and
             // tcgen05 operations of one thread execute in issue order).  A K/V stage is free again once BOTH
@@ -507,7 +532,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const QtPlan q = t == 0 ? plan.qt[0] : plan.qt[1];
             const int n_tiles = plan.x_end - plan.x_begin;        // window tiles loaded by the producers
             const int n_first = q.n_win > 0 ? q.a - plan.x_begin : n_tiles;  // my tiles: [n_first, n_first + n_win)
-            using TM = TmemMap<DH>;
+            using TM = TmemMap<DH, TILES>;
             const uint32_t s_tmem = tmem_base + TM::s(t);
             const uint32_t p_tmem = tmem_base + TM::p(t);
             const uint32_t o_tmem = tmem_base + TM::o(t);
@@ -628,20 +653,26 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
     } else {
         // ---------------- softmax groups ----------------
-#ifndef TMW_NO_SETMAXNREG
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;" ::: "memory");
-#endif
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Budget<TILES>::kRegsSoftmax) : "memory");
         const int t = (warp >> 2) - 1;                 // query tile of this group
         const int row = threadIdx.x & (BM - 1);        // row of the tile == tensor-memory lane
         const QtPlan q = t == 0 ? plan.qt[0] : plan.qt[1];
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-        using TM = TmemMap<DH>;
+        using TM = TmemMap<DH, TILES>;
         const uint32_t s_addr = tmem_base + lane_addr + TM::s(t);
         const uint32_t p_addr = tmem_base + lane_addr + TM::p(t);
         const uint32_t o_addr = tmem_base + lane_addr + TM::o(t);
         const int pos = q.p_lo + row;
         float m_used = -INFINITY;  // maximum the stored P and O are relative to (log2 domain)
         float l_sum = 0.f;
+
+        // Alternation of the two softmax groups: both share the four schedulers and their special-function
+        // units, and left alone they fall into step and queue for the exponentials together.  Group 0 goes
+        // first; a group starts the exponentials of round r only after the other group has issued those of
+        // its previous round.  Both groups run max(items of tile 0, items of tile 1) rounds.
+        constexpr bool kAlternate = TILES == 2 && Alternate<DH>::value;
+        const int rounds = kAlternate ? max(plan.qt[0].n_items, plan.qt[1].n_items) : 0;
+        const uint32_t my_turn = bar(BAR_TURN + t), other_turn = bar(BAR_TURN + (t ^ 1));
 
         for (int item = 0; item < q.n_items; ++item) {
             // visible columns of this row inside the tile: [j_lo, j_hi]
@@ -719,7 +750,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tile_max *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
 
             if (TM::kSplitP && item > 0) {
-                // the previous P V must have finished before O is rescaled or P is overwritten
+                // the previous P V must have finished before O is rescaled or P is overwritten.  (Keeping the
+                // exponentials in registers until then, to take this wait off the path previous P -> P V ->
+                // this P, was measured: the 64 extra live registers spill and the kernel is 1.5 x slower.)
                 mbar_wait(bar(BAR_PV_DONE + t), (item - 1) & 1, abort_flag, p.status);
                 tc_fence_after();
             }
@@ -750,6 +783,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
             const uint64_t negm2 = pack2(neg_m, neg_m);
             uint64_t lacc[2] = {0ull, 0ull};  // four partial row sums
+            if (kAlternate) mbar_wait(my_turn, (uint32_t)(item & 1) ^ (t == 0 ? 1u : 0u), abort_flag, p.status);
 #pragma unroll
             for (int c = 0; c < 4; ++c)
                 if (c < nchunks) {
@@ -788,11 +822,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 l_sum += (a0 + a1) + (a2 + a3);
             }
             TRACE(1000 + t * 500 + item * 8 + 4 + ((warp & 3) ? 2000 : 0));
+            if (kAlternate) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(other_turn);
+            }
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(BAR_P_READY + t));
             TRACE(1000 + t * 500 + item * 8 + 5 + ((warp & 3) ? 2000 : 0));
+        }
+
+        for (int r = q.n_items; r < rounds; ++r) {  // keep the hand-over going for the group with more items
+            mbar_wait(my_turn, (uint32_t)(r & 1) ^ (t == 0 ? 1u : 0u), abort_flag, p.status);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(other_turn);
         }
 
         if (q.n_items > 0) {
@@ -833,7 +877,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             named_barrier_sync(1 + t, BM);
             if (row == 0) {
                 int c1, c2;
-                coords(3, blockIdx.x * 2 * BM + t * BM, c1, c2);
+                coords(3, (blockIdx.x * TILES + t) * BM, c1, c2);
                 for (int u = 0; u < NSUB; ++u)
                     tma_store_4d(&map_o, smem_u32(stage + u * L::kSubTileBytes), u * 64, c1, c2, batch);
                 tma_store_commit_and_wait();
@@ -919,9 +963,9 @@ bool make_map(CUtensorMap* map, const void* base, int dtype, int batch, int head
 
 int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
 
-template <int DH, int KS, int VS>
+template <int DH, int KS, int VS, int TILES>
 int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream) {
-    using L = TcSmem<DH, KS, VS>;
+    using L = TcSmem<DH, KS, VS, TILES>;
     const int np_pad = np_pad_of(d.n_persistent);
     CUtensorMap mq, mk, mv, mo, mkp, mvp;
     bool hf[4] = {false, false, false, false}, hf_p[2];
@@ -941,13 +985,14 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     p.status = device_status_word();
     if (p.status == nullptr) return TMW_ERR_CUDA;
     const int smem_bytes = L::total_bytes(np_pad);
-    dim3 grid((d.q_rows + 2 * BM - 1) / (2 * BM), d.heads, d.batch);
+    dim3 grid((d.q_rows + TILES * BM - 1) / (TILES * BM), d.heads, d.batch);
+    constexpr int kThreadsTc = Budget<TILES>::kThreads;
     if (d.dtype == TMW_BF16) {
-        auto kern = prefill_tc_kernel<DH, KS, VS, true>;
+        auto kern = prefill_tc_kernel<DH, KS, VS, true, TILES>;
         TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         kern<<<grid, kThreadsTc, smem_bytes, stream>>>(mq, mk, mv, mo, mkp, mvp, p);
     } else {
-        auto kern = prefill_tc_kernel<DH, KS, VS, false>;
+        auto kern = prefill_tc_kernel<DH, KS, VS, false, TILES>;
         TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         kern<<<grid, kThreadsTc, smem_bytes, stream>>>(mq, mk, mv, mo, mkp, mvp, p);
     }
@@ -956,6 +1001,10 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
 }
 
 constexpr int kMaxDynamicSmem = 232448;  // 227 KB per CTA on sm_100
+constexpr int kTwoCtaSmem = (233472 - 2 * 1024) / 2;  // 228 KB per SM, 1 KB per CTA reserved by the system
+#ifndef TMW_TILES64
+#define TMW_TILES64 1
+#endif
 
 }  // namespace
 
@@ -971,7 +1020,7 @@ bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, co
     if (d.batch > 65535 || d.heads > 65535) return false;
     const int np_pad = np_pad_of(d.n_persistent);
     if (np_pad > 128) return false;
-    const int need = d.head_dim == 64 ? TcSmem<64, 3, 3>::total_bytes(np_pad) : TcSmem<128, 2, 2>::total_bytes(np_pad);
+    const int need = d.head_dim == 64 ? TcSmem<64, 3, 3, 2>::total_bytes(np_pad) : TcSmem<128, 2, 2, 2>::total_bytes(np_pad);
     if (need > kMaxDynamicSmem) return false;
     // positions are combined in 32-bit arithmetic inside the kernel
     if ((int64_t)d.q_pos0 + d.q_rows + d.window + 4 * BN >= (int64_t)1 << 30) return false;
@@ -980,8 +1029,15 @@ bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, co
 
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
                       cudaStream_t stream) {
-    if (d.head_dim == 64) return launch_tc<64, 3, 3>(d, q, k, v, o, stream);
-    return launch_tc<128, 2, 2>(d, q, k, v, o, stream);
+    if (d.head_dim == 64) {
+        // One query tile per CTA and two CTAs per SM when two such CTAs fit into shared memory (they do
+        // unless there are many persistent keys): independent CTAs drift apart, so one CTA's exponentials,
+        // start-up and output phase overlap the other's matrix products.
+        if (TMW_TILES64 == 1 && TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem)
+            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream);
+        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream);
+    }
+    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream);
 }
 
 }  // namespace tmw
