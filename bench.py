@@ -50,6 +50,9 @@ WORKLOADS = {
     # (256 sequences sharded over the GPUs), prompt 2048 tokens, then `--steps` single-token steps
     "config4_decode": dict(batch=256, T=2048, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
                            layers=16, d_ff=2560, vocab=50000),
+    # BASELINE config 3: whole 16-layer model forward (prefill), 2 sequences of 8192 tokens per GPU
+    "config3_model_prefill": dict(batch=2, T=8192, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
+                                  layers=16, d_ff=2560, vocab=50000),
     # BASELINE config 5: attention core only, Q/K/V given; the sequence is sharded over the GPUs
     "config5_long_prefill": dict(batch=1, T=131072, d_model=2048, heads=16, window=1024, n_persistent=16,
                                  dtype="bf16"),
@@ -266,26 +269,34 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
     _native.poll_status(dev)
 
     # ---- end to end: host buffers, copies inside the timed region -------------------
+    # Every step copies its input from pinned host memory and its output back; HostPipeline (public API)
+    # overlaps the two copies and the forward of consecutive steps on three streams.
+    from titanmac_b200 import HostPipeline
+
     x_host = x_cpu.to(dtype).pin_memory()
-    y_host = torch.empty((B, L, D), dtype=dtype).pin_memory()
-    x_dev = torch.empty((B, L, D), dtype=dtype, device=dev)
+    y_hosts = [torch.empty((B, L, D), dtype=dtype).pin_memory() for _ in range(2)]
+    pipe = HostPipeline(mod, (B, L, D), dtype, dev, depth=2)
+    main_stream = torch.cuda.current_stream(dev)
 
-    def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        y = mod(x_dev)
-        y_host.copy_(y, non_blocking=True)
-
-    for _ in range(max(3, args.warmup // 4)):
-        e2e_step()
+    for i in range(max(3, args.warmup // 4)):
+        pipe.submit(x_host, y_hosts[i % 2])
+    pipe.drain()
     e2e_steps = max(3, min(args.steps, 50))
     barrier()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2.record()
+    s2.record(main_stream)
+    pipe.follow(main_stream)
+    for i in range(e2e_steps):
+        pipe.submit(x_host, y_hosts[i % 2])
+    pipe.join(main_stream)
+    e2.record(main_stream)
     barrier()
     e2e_ms = s2.elapsed_time(e2)
+    if rank == 0:  # the result really came back: compare the last output with a device-resident forward
+        ref = mod(x_host.to(dev)).float().cpu()
+        err = (y_hosts[(e2e_steps - 1) % 2].float() - ref).abs().max().item()
+        if not err <= 1e-2:
+            raise SystemExit(f"end-to-end output differs from the device-resident forward by {err}")
 
     t = torch.tensor([elapsed_ms, e2e_ms, sum(core_ms) / max(1, len(core_ms))], device=dev, dtype=torch.float64)
     if world > 1:
@@ -311,8 +322,9 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
                          "traffic": NCU_TRAFFIC_BYTES.get(wl_name),
                          "algorithmic_flops_per_launch": flops["core"]},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
-                    "d2h_bytes_per_step": y_host.numel() * y_host.element_size(), "steps": e2e_steps,
-                    "ms_per_step": e2e_ms / e2e_steps},
+                    "d2h_bytes_per_step": y_hosts[0].numel() * y_hosts[0].element_size(), "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps,
+                    "how": "HostPipeline: H2D copy, forward and D2H copy of consecutive steps overlap on 3 streams"},
             "gpu_launches": args.steps,
             "clocks": clocks.report(),
         }
@@ -500,6 +512,106 @@ def run_decode(args, wl_name: str, wl: dict) -> None:
         dist.destroy_process_group()
 
 
+def run_model_prefill(args, wl_name: str, wl: dict) -> None:
+    """BASELINE config 3: forward of the whole default model over `batch` sequences per GPU (weak scaling).
+
+    FLOPs are the reference forward's: per layer the attention module (QKV, live pairs, output projection) and
+    the MLP, plus the LM head over all L rows.  The attention core's share of the step is measured with CUDA
+    events around every tmw_prefill call."""
+    from titanmac_b200 import TitanMAC, TitanMACConfig, _native
+
+    dist, world, rank, local, dev = _dist_setup(args)
+    B, T, D, H, w, Np = wl["batch"], wl["T"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
+    L, V, F_, NL = Np + T, wl["vocab"], wl["d_ff"], wl["layers"]
+    cfg = TitanMACConfig(vocab_size=V, d_model=D, n_heads=H, n_layers=NL, d_ff=F_, max_seq_len=T, window_size=w,
+                         n_persistent=Np)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    model = TitanMAC(cfg).eval()
+    with torch.no_grad():  # every weight N(0, 0.02), biases 0, norm scales 1
+        for name, prm in model.named_parameters():
+            if name.endswith("scale"):
+                prm.fill_(1.0)
+            elif name.endswith("bias"):
+                prm.zero_()
+            else:
+                prm.copy_(torch.randn(prm.shape, generator=g) * 0.02)
+    model = model.to(device=dev, dtype=torch.bfloat16)
+    g = torch.Generator(device="cpu").manual_seed(1 + rank)
+    ids = [torch.randint(0, V, (B, T), generator=g).to(dev) for _ in range(2)]
+    lf = layer_flops(wl)
+    flops = NL * (lf["total"] + 2 * 2 * B * L * D * F_) + 2 * B * L * D * V
+    core_flops = NL * lf["core"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        model(ids[i % 2])
+    events = []
+    for layer in model.layers:
+        layer.attention.core_events = events
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        barrier()
+        a.record()
+        for i in range(args.steps):
+            out = model(ids[i % 2])["logits"]
+        b.record()
+        barrier()
+    ms = a.elapsed_time(b)
+    core_ms = sum(x.elapsed_time(y) for x, y in events) / args.steps
+    for layer in model.layers:
+        layer.attention.core_events = None
+    _native.poll_status(dev)
+
+    # end to end: token ids from pinned host memory, the last position's logits back to the host
+    ids_host = ids[0].cpu().pin_memory()
+    ids_dev = torch.empty_like(ids[0])
+    last_host = torch.empty((B, V), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        ids_dev.copy_(ids_host, non_blocking=True)
+        last_host.copy_(model(ids_dev)["logits"][:, -1], non_blocking=True)
+    e2.record()
+    barrier()
+    e2e_ms = s2.elapsed_time(e2)
+
+    t = torch.tensor([ms, core_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, core_ms, e2e_ms = (float(v) for v in t.cpu())
+    if rank == 0:
+        peaks = load_peaks()
+        value = flops * world * args.steps / (ms * 1e-3) / 1e12
+        achieved = core_flops / (core_ms * 1e-3) / 1e12
+        line = {
+            "metric": "model_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload=wl_name, **wl, global_batch=B * world, parallelism=f"batch-sharded x{world}",
+                           l2="activations and logits per step (> 2 GB) exceed the 126 MB L2",
+                           flops_per_step_per_gpu=flops, attention_core_flops_per_step_per_gpu=core_flops),
+            "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill), 16 launches per step",
+                         "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_tflops"], "peak_source": f"{peaks['source']} bf16 burst",
+                         "core_ms_per_step": core_ms, "core_share_of_step": core_ms / (ms / args.steps),
+                         "step_frac_of_peak": value / world / peaks["bf16_tflops"], "traffic": None},
+            "e2e": {"value": flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": B * V * 2, "steps": e2e_steps,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": args.steps * NL,
+            "clocks": clocks.report(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_long(args, wl_name: str, wl: dict) -> None:
     """BASELINE config 5: attention core over one long sequence, rows sharded over the GPUs with a K/V halo."""
     from oracle import windowed_oracle as wo
@@ -575,7 +687,14 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
+        if "layer_prefill" not in args.workload:
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "the CPU reference arm is timed on the layer workloads only"}), flush=True)
+            return
         run_reference_arm(args, args.workload, wl)
+    elif args.workload == "config3_model_prefill":
+        run_model_prefill(args, args.workload, wl)
     elif args.workload == "config4_decode":
         run_decode(args, args.workload, wl)
     elif args.workload == "config5_long_prefill":

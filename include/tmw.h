@@ -171,6 +171,19 @@ TMW_API int tmw_decode_split_static(const tmw_cache_desc* cache, const void* q, 
                             void* o, const int64_t q_stride[2], const int64_t kv_new_stride[2],
                             const int64_t o_stride[2], const int32_t* pos, int32_t splits, void* stream);
 
+/*
+ * Residual add + RMSNorm over contiguous rows [rows, dim] (dim a multiple of 8, pointers 16-byte aligned):
+ *     h = x + residual          (residual may be NULL: h = x)
+ *     sum_out = h               (sum_out may be NULL, and may be x itself: the residual stream in place)
+ *     y = h / sqrt(mean(h^2) + eps) * scale
+ * Replaces the element-wise PyTorch operations around the attention call in the reference's block:
+ * the residual adds of titans_core/blocks/titan_block.py:94-100 and RMSNorm.forward,
+ * titans_core/blocks/norms.py:55-58 (seven kernels there, one pass over HBM here).  h is rounded to the
+ * storage type before the norm, as the reference's own addition does; the norm is computed in fp32.
+ */
+TMW_API int tmw_add_rmsnorm(int32_t dtype, int64_t rows, int32_t dim, const void* x, const void* residual,
+                            const void* scale, float eps, void* sum_out, void* y, void* stream);
+
 /* Library facts. */
 TMW_API int tmw_version(void);
 TMW_API const char* tmw_strerror(int status);

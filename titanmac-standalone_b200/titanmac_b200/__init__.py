@@ -4,7 +4,8 @@ from .config import TitanMACConfig, WindowConfig
 from .attn.windowed_attention import WindowedAttention
 from .blocks.titan_block import MLPBlock, RMSNorm, TitanBlock
 from .models.titanmac import TitanMAC
+from .host_pipeline import HostPipeline
 from . import _native
 
 __all__ = ["TitanMACConfig", "WindowConfig", "WindowedAttention", "TitanBlock", "RMSNorm", "MLPBlock", "TitanMAC",
-           "_native"]
+           "HostPipeline", "_native"]

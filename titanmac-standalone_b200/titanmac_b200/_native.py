@@ -115,6 +115,11 @@ SIGNATURES = {
          ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
          ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p],
     ),
+    "tmw_add_rmsnorm": (
+        ctypes.c_int,
+        [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+         ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p],
+    ),
 }
 
 MAX_DECODE_SPLITS = 16
@@ -298,6 +303,39 @@ class RingCache:
                 check(lib().tmw_decode(ctypes.byref(c), q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
                                        out.data_ptr(), qs, ns, os_, pos.data_ptr(), _stream_ptr(self.device)))
         return out
+
+
+def add_rmsnorm_supported(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype in _DTYPES and x.shape[-1] % 8 == 0
+
+
+def add_rmsnorm(x: torch.Tensor, residual: Optional[torch.Tensor], scale: torch.Tensor, eps: float,
+                inplace_sum: bool = False):
+    """``h = x + residual`` (``residual`` may be None), ``y = h / sqrt(mean(h^2) + eps) * scale`` in one
+    pass (RMSNorm of titans_core/blocks/norms.py:55-58 with the residual add of titan_block.py:94-100
+    folded in).  Returns ``(h, y)``; ``h`` is ``x`` itself when there is no residual, and is written into
+    ``x`` when ``inplace_sum``."""
+    _require_cuda(x, scale)
+    dim = x.shape[-1]
+    if x.dtype not in _DTYPES or scale.dtype != x.dtype or scale.shape != (dim,):
+        raise TypeError("add_rmsnorm: fp32 / bf16 / fp16 rows and a scale vector of the same type and length")
+    x = x if x.is_contiguous() else x.contiguous()
+    scale = scale if scale.is_contiguous() else scale.contiguous()
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype or residual.device != x.device:
+            raise ValueError("add_rmsnorm: x and residual must agree in shape, dtype and device")
+        residual = residual if residual.is_contiguous() else residual.contiguous()
+    y = torch.empty_like(x)
+    h = x if (residual is None or inplace_sum) else torch.empty_like(x)
+    rows = x.numel() // dim if dim else 0
+    if rows == 0:  # nothing to do (and an empty tensor has no address to pass)
+        return h, y
+    with torch.cuda.device(x.device):
+        check(lib().tmw_add_rmsnorm(_DTYPES[x.dtype], rows, dim, x.data_ptr(),
+                                    residual.data_ptr() if residual is not None else None, scale.data_ptr(),
+                                    float(eps), h.data_ptr() if residual is not None else None, y.data_ptr(),
+                                    _stream_ptr(x.device)))
+    return h, y
 
 
 def poll_status(device: Optional[torch.device] = None) -> None:

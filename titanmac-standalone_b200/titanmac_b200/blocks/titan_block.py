@@ -2,10 +2,12 @@
 
 Mirrors titans_core/blocks/titan_block.py:41-102, blocks/norms.py:39-60 and
 blocks/mlp.py:28-67 of the reference (same submodule names, so checkpoints load
-unchanged).  Only the attention is this package's own code; norm and MLP are plain
-PyTorch, as in the reference.  The reference's default ``use_block_sparse=True``
-selects a different attention class with different math, which this package does
-not provide: it is refused here instead of being silently replaced.
+unchanged).  The attention is this package's own code, and so is the element-wise work around
+it on a GPU: RMSNorm with the preceding residual add folded in is one kernel
+(``tmw_add_rmsnorm``); the MLP's linears and its GELU stay library calls.  The reference's
+default ``use_block_sparse=True`` selects a different attention class with different math,
+which this package does not provide: it is refused here instead of being silently replaced.
+The package is forward-only; an input that carries a gradient takes the plain PyTorch norm.
 """
 
 from __future__ import annotations
@@ -15,6 +17,7 @@ from typing import Optional
 import torch
 import torch.nn as nn
 
+from .. import _native
 from ..attn.windowed_attention import WindowedAttention
 
 
@@ -27,8 +30,18 @@ class RMSNorm(nn.Module):
         self.scale = nn.Parameter(torch.ones(dim))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if _native.add_rmsnorm_supported(x) and not (torch.is_grad_enabled() and x.requires_grad):
+            return _native.add_rmsnorm(x, None, self.scale, self.eps)[1]
         rms = torch.sqrt(torch.mean(x ** 2, dim=-1, keepdim=True) + self.eps)
         return x / rms * self.scale
+
+    def add_forward(self, x: torch.Tensor, residual: torch.Tensor, inplace: bool = False):
+        """``h = x + residual`` and ``RMSNorm(h)`` together: returns ``(h, normed)``."""
+        if _native.add_rmsnorm_supported(x) and not (
+                torch.is_grad_enabled() and (x.requires_grad or residual.requires_grad)):
+            return _native.add_rmsnorm(x, residual, self.scale, self.eps, inplace_sum=inplace)
+        h = x + residual
+        return h, self.forward(h)
 
 
 class MLPBlock(nn.Module):
@@ -63,5 +76,6 @@ class TitanBlock(nn.Module):
         self.mlp = MLPBlock(d_model=config.d_model, d_ff=config.d_ff, dropout=config.dropout)
 
     def forward(self, x: torch.Tensor, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-        x = x + self.attention(self.norm_attn(x), attn_mask=attn_mask)
-        return x + self.mlp(self.norm_mlp(x))
+        a = self.attention(self.norm_attn(x), attn_mask=attn_mask)
+        x, h = self.norm_mlp.add_forward(x, a)
+        return x + self.mlp(h)

@@ -73,9 +73,19 @@ class TitanMAC(nn.Module):
                 attention_mask: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
         Np = self.config.n_persistent
         x = self._embed(input_ids)
+        # Same wiring as TitanBlock.forward, with every residual add folded into the RMSNorm that follows it
+        # (one kernel): the MLP output of a layer is added by the next layer's first norm, or by the final norm.
+        pending = None
         for layer in self.layers:
-            x = layer(x, attn_mask=None)
-        logits = self.lm_head(self.norm(x))
+            if pending is None:
+                h = layer.norm_attn(x)
+            else:
+                x, h = layer.norm_attn.add_forward(x, pending, inplace=True)
+            a = layer.attention(h, attn_mask=None)
+            x, h = layer.norm_mlp.add_forward(x, a, inplace=True)
+            pending = layer.mlp(h)
+        h = self.norm(x) if pending is None else self.norm.add_forward(x, pending, inplace=True)[1]
+        logits = self.lm_head(h)
         logits = logits[:, Np:, :] if Np > 0 else logits
         out = {"logits": logits}
         if labels is not None:
@@ -99,9 +109,13 @@ class TitanMAC(nn.Module):
         x = self._embed(input_ids)
         if caches is None:
             caches = self.new_caches(B, x.device, x.dtype)
+        pending = None
         for layer, cache in zip(self.layers, caches):
             attn = layer.attention
-            h = layer.norm_attn(x)
+            if pending is None:
+                h = layer.norm_attn(x)
+            else:
+                x, h = layer.norm_attn.add_forward(x, pending, inplace=True)
             L = h.shape[1]
             attn._check_lengths(L)
             attn._check_supported(h, None)
@@ -113,9 +127,10 @@ class TitanMAC(nn.Module):
             if Np > 0:
                 cache.set_persistent(k[0, :, :Np], v[0, :, :Np])
             cache.fill(k[:, :, Np:], v[:, :, Np:], t0=0)
-            x = x + attn.out_proj(o.view(B, L, -1))
-            x = x + layer.mlp(layer.norm_mlp(x))
-        logits = self.lm_head(self.norm(x[:, -1]))
+            x, h = layer.norm_mlp.add_forward(x, attn.out_proj(o.view(B, L, -1)), inplace=True)
+            pending = layer.mlp(h)
+        last = self.norm(x[:, -1]) if pending is None else self.norm.add_forward(x[:, -1], pending[:, -1])[1]
+        logits = self.lm_head(last)
         return logits, caches
 
     @torch.no_grad()
@@ -125,13 +140,19 @@ class TitanMAC(nn.Module):
         c = self.config
         B = token_ids.shape[0]
         x = self.embed_tokens(token_ids) + self.embed_positions(pos.long())
+        pending = None
         for layer, cache in zip(self.layers, caches):
             attn = layer.attention
-            qkv = attn.qkv_proj(layer.norm_attn(x)).view(B, 3, c.n_heads, c.d_head)
+            if pending is None:
+                h = layer.norm_attn(x)
+            else:
+                x, h = layer.norm_attn.add_forward(x, pending, inplace=True)
+            qkv = attn.qkv_proj(h).view(B, 3, c.n_heads, c.d_head)
             o = cache.decode(qkv[:, 0], qkv[:, 1], qkv[:, 2], pos)
-            x = x + attn.out_proj(o.view(B, -1))
-            x = x + layer.mlp(layer.norm_mlp(x))
-        return self.lm_head(self.norm(x))
+            x, h = layer.norm_mlp.add_forward(x, attn.out_proj(o.view(B, -1)), inplace=True)
+            pending = layer.mlp(h)
+        h = self.norm(x) if pending is None else self.norm.add_forward(x, pending, inplace=True)[1]
+        return self.lm_head(h)
 
     @torch.no_grad()
     def generate(self, input_ids: torch.Tensor, max_new_tokens: int, use_cuda_graph: bool = True) -> torch.Tensor:
