@@ -54,6 +54,25 @@ def test_decode_bf16_matches_fp32_oracle(dh, w, Np, B, H, L, pre):
     assert (got - want).abs().max().item() <= 2e-2
 
 
+@pytest.mark.parametrize("dh,w,Np,B,H,steps,pre,dtype", [
+    (64, 40, 5, 80, 8, 60, 0, torch.bfloat16),    # 640 pairs: every SM gets more than four -> streaming kernel
+    (64, 37, 16, 100, 10, 30, 30, torch.bfloat16),
+    (128, 21, 0, 75, 8, 50, 3, torch.float16),    # no persistent keys, ring shorter than one chunk at first
+    (128, 33, 7, 160, 4, 20, 40, torch.bfloat16),
+])
+def test_decode_streaming_kernel_many_pairs(dh, w, Np, B, H, steps, pre, dtype):
+    """Batches with more than four (sequence, head) pairs per SM run the shared-memory streaming variant:
+    same contract - first tokens, a ring that is not full yet, and several wraps of the ring."""
+    L = Np + pre + steps
+    q, k, v = (t.to(dtype) for t in wo.qkv_inputs(B, H, L, dh, seed=dh + w + B))
+    k[1:, :, :Np] = k[:1, :, :Np]
+    v[1:, :, :Np] = v[:1, :, :Np]
+    got = run_decode(q, k, v, w, Np, pre, dtype).float().cpu()
+    want = wo.attention_core_rows(q[:, :, Np + pre:].float(), k.float(), v.float(), Np + pre, w, Np)
+    assert (got - want).abs().max().item() <= 2e-2
+    _native.poll_status(torch.device(DEV))
+
+
 def test_decode_ragged_positions_and_strided_inputs():
     """Sequences at different positions in one call; q/k/v taken as strided views of one [B, 3D] buffer."""
     dh, w, Np, B, H = 64, 50, 4, 4, 3
