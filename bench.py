@@ -60,7 +60,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention-core kernel,
 # taken from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126424576 + 25449728}
+NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126414080 + 25901568}
 
 
 def live_pairs(L: int, w: int, Np: int) -> int:
