@@ -697,6 +697,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 full = q.p_lo >= p.np && g0 >= p.np && g0 + BN - 1 <= q.p_lo && q.p_lo + BM - 1 - g0 <= p.window;
             }
             const int nchunks = (ncols + 31) / 32;
+            // 32-column chunks in which no row of this warp sees a key (beyond the diagonal, or before the
+            // window's left edge): not loaded, not exponentiated, P = 0
+            bool hid[4] = {false, false, false, false};
+            if (!full) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    hid[c] = __all_sync(0xffffffffu, j_hi - c * 32 < 0 || j_lo - c * 32 > 31);
+            }
 
             TRACE(1000 + t * 500 + item * 8 + 0 + ((warp & 3) ? 2000 : 0));
             mbar_wait(bar(BAR_S_FULL + t), item & 1, abort_flag, p.status);
@@ -706,7 +714,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             uint32_t s[4][32];
 #pragma unroll
             for (int c = 0; c < 4; ++c)
-                if (c < nchunks) tmem_ld32(s_addr + c * 32, s[c]);
+                if (c < nchunks && !hid[c]) tmem_ld32(s_addr + c * 32, s[c]);
             tc_wait_ld();
             if (TM::kSplitP) {
                 // S is in registers now: let the issuing warp overwrite it with the next item's scores
@@ -721,7 +729,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             if (!full) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
-                    if (c < nchunks) {
+                    if (c < nchunks && !hid[c]) {
                         const int lo = j_lo - c * 32, hi = j_hi - c * 32;  // visible columns of the chunk: [lo, hi]
                         if (!__all_sync(0xffffffffu, lo <= 0 && hi >= 31)) {
 #pragma unroll
@@ -733,7 +741,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c = 0; c < 4; ++c)
-                if (c < nchunks) {
+                if (c < nchunks && !hid[c]) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
 #pragma unroll
@@ -788,6 +796,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             for (int c = 0; c < 4; ++c)
                 if (c < nchunks) {
                     uint32_t packed[16];
+                    if (hid[c]) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) packed[i] = 0u;
+                        tmem_st16(p_addr + c * 16, packed);
+                        continue;
+                    }
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint64_t x = fma2(pack2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
