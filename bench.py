@@ -627,11 +627,18 @@ def run_long(args, wl_name: str, wl: dict) -> None:
     own = r1 - r0
     q, k, v = (torch.randn(1, own, H, dh, generator=g).to(torch.bfloat16).to(dev).permute(0, 2, 1, 3) for _ in range(3))
     flops = H * live_pairs(Ltot, w, Np) * 4 * dh
+    kv = None
+    if world > 1:
+        # K and V of this rank live in the sharded buffers from the start (the producer writes them there):
+        # a step is then the persistent broadcast, the halo exchange and two kernel launches
+        kv = shard.ShardedKV.allocate(1, H, dh, Ltot, w, Np, torch.bfloat16, dev)
+        kv.k_own.copy_(k)
+        kv.v_own.copy_(v)
 
     def step():
         if world == 1:
             return _native.prefill(q, k, v, w, Np)
-        return shard.sharded_prefill(q, k, v, Ltot, w, Np)
+        return shard.sharded_prefill(q, None, None, Ltot, w, Np, kv=kv)
 
     def barrier():
         if world > 1:
@@ -650,10 +657,32 @@ def run_long(args, wl_name: str, wl: dict) -> None:
         barrier()
     ms = a.elapsed_time(b)
     _native.poll_status(dev)
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+
+    # end to end: this rank's rows of Q, K, V from pinned host memory, its rows of O back
+    hosts = [x.contiguous().cpu().pin_memory() for x in (q, k, v)]
+    devs = [torch.empty_like(x.contiguous()) for x in (q, k, v)]
+    o_host = torch.empty((1, H, own, dh), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_step():
+        for d_, h_ in zip(devs, hosts):
+            d_.copy_(h_, non_blocking=True)
+        o = _native.prefill(*devs, w, Np) if world == 1 else shard.sharded_prefill(*devs, Ltot, w, Np)  # copying form
+        o_host.copy_(o, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2.record()
+    barrier()
+    e2e_ms = s2.elapsed_time(e2)
+    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.cpu()[0])
+    ms, e2e_ms = (float(x) for x in t.cpu())
     if rank == 0:
         peaks = load_peaks()
         value = flops * args.steps / (ms * 1e-3) / 1e12
@@ -667,6 +696,9 @@ def run_long(args, wl_name: str, wl: dict) -> None:
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
                          "peak_source": f"{peaks['source']} bf16 burst", "traffic": None,
                          "note": "per GPU, halo exchange included when sharded"},
+            "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": 3 * hosts[0].numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": args.steps * (1 if world == 1 else 2),
             "clocks": clocks.report(),
         }

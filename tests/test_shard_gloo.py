@@ -58,6 +58,13 @@ def _worker(rank, world, port, L, w, Np, out_dir):
         else:
             want_k = torch.cat([k[:, :, :Np], k[:, :, r0 - halo:r1]], dim=2)
         assert torch.equal(kv.k, want_k), f"rank {rank}: K buffer differs"
+        # the buffers made first and filled in place by the producer end up the same
+        kv2 = shard.ShardedKV.allocate(1, 2, 16, L, w, Np, k.dtype, "cpu")
+        kv2.k_own.copy_(k[:, :, r0:r1])
+        kv2.v_own.copy_(v[:, :, r0:r1])
+        kv2.exchange()
+        assert torch.equal(kv2.k, kv.k) and torch.equal(kv2.v, kv.v), f"rank {rank}: allocate() path differs"
+        assert (kv2.q_pos0, kv2.k_pos0, kv2.own_offset) == (kv.q_pos0, kv.k_pos0, kv.own_offset)
         assert kv.q_pos0 == r0 and kv.k_pos0 == (Np if rank == 0 else r0 - halo)
         o = c_oracle.attention(q[:, :, r0:r1], kv.k, kv.v, w, Np, q_pos0=kv.q_pos0, k_pos0=kv.k_pos0)
         np.save(os.path.join(out_dir, f"o{rank}.npy"), o)

@@ -76,36 +76,61 @@ def halo_rows(bounds: Sequence[Tuple[int, int]], rank: int, window: int, n_persi
 
 
 class ShardedKV:
-    """This rank's K/V buffers ``[B, H, Np + halo + own, dh]`` and the positions that go with them."""
+    """This rank's K/V buffers ``[B, H, Np + halo + own, dh]`` and the positions that go with them.
+
+    ``ShardedKV(k_own, v_own, ...)`` copies the rank's rows into fresh buffers.  ``ShardedKV.allocate(...)``
+    only makes the buffers: the producer of K and V (the QKV projection) then writes this rank's rows straight
+    into ``k_own`` / ``v_own`` — views of the buffers — and no copy of the rank's 2 x own x H x dh elements is
+    made per call.
+    """
 
     def __init__(self, k_own: torch.Tensor, v_own: torch.Tensor, total_rows: int, window: int, n_persistent: int,
                  group: Optional[dist.ProcessGroup] = None):
+        B, H, _, dh = k_own.shape
+        self._layout(total_rows, window, n_persistent, group)
+        if k_own.shape[2] != self.r1 - self.r0 or v_own.shape != k_own.shape:
+            raise ValueError(f"rank {self.rank} must hold rows [{self.r0}, {self.r1}) of K and V")
+        if self.rank == 0:
+            # rank 0's own block already starts with the persistent rows
+            self.k, self.v = k_own.contiguous(), v_own.contiguous()
+        else:
+            self._buffers(B, H, dh, k_own.dtype, k_own.device)
+            self.k[:, :, self.own_offset:] = k_own
+            self.v[:, :, self.own_offset:] = v_own
+
+    @classmethod
+    def allocate(cls, batch: int, heads: int, head_dim: int, total_rows: int, window: int, n_persistent: int,
+                 dtype: torch.dtype, device, group: Optional[dist.ProcessGroup] = None) -> "ShardedKV":
+        self = cls.__new__(cls)
+        self._layout(total_rows, window, n_persistent, group)
+        self._buffers(batch, heads, head_dim, dtype, device)
+        return self
+
+    def _layout(self, total_rows: int, window: int, n_persistent: int, group) -> None:
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.window, self.n_persistent, self.total_rows = window, n_persistent, total_rows
         self.bounds = shard_bounds(total_rows, n_persistent, self.world)
         self.r0, self.r1 = self.bounds[self.rank]
-        if k_own.shape[2] != self.r1 - self.r0 or v_own.shape != k_own.shape:
-            raise ValueError(f"rank {self.rank} must hold rows [{self.r0}, {self.r1}) of K and V")
-        B, H, _, dh = k_own.shape
-        Np = n_persistent
-        self.halo = halo_rows(self.bounds, self.rank, window, Np)
-        own = self.r1 - self.r0
-        if self.rank == 0:
-            # rank 0's own block already starts with the persistent rows
-            self.k, self.v = k_own.contiguous(), v_own.contiguous()
-            self.own_offset = 0
-            self.k_pos0 = Np
-        else:
-            shape = (B, H, Np + self.halo + own, dh)
-            self.k = torch.empty(shape, dtype=k_own.dtype, device=k_own.device)
-            self.v = torch.empty(shape, dtype=v_own.dtype, device=v_own.device)
-            self.own_offset = Np + self.halo
-            self.k[:, :, self.own_offset:] = k_own
-            self.v[:, :, self.own_offset:] = v_own
-            self.k_pos0 = self.r0 - self.halo  # position of buffer row Np
+        self.halo = halo_rows(self.bounds, self.rank, window, n_persistent)
+        # rank 0: buffer == own rows (they start with the persistent rows); rank r > 0: [persistent | halo | own]
+        self.own_offset = 0 if self.rank == 0 else n_persistent + self.halo
+        self.k_pos0 = n_persistent if self.rank == 0 else self.r0 - self.halo  # position of buffer row Np
         self.q_pos0 = self.r0
+
+    def _buffers(self, B: int, H: int, dh: int, dtype: torch.dtype, device) -> None:
+        shape = (B, H, self.own_offset + (self.r1 - self.r0), dh)
+        self.k = torch.empty(shape, dtype=dtype, device=device)
+        self.v = torch.empty(shape, dtype=dtype, device=device)
+
+    @property
+    def k_own(self) -> torch.Tensor:
+        return self.k[:, :, self.own_offset:]
+
+    @property
+    def v_own(self) -> torch.Tensor:
+        return self.v[:, :, self.own_offset:]
 
     def exchange(self) -> None:
         """Persistent K/V from rank 0 and the halo rows from the left neighbours, into this rank's buffers."""
@@ -149,17 +174,29 @@ class ShardedKV:
         return dist.get_global_rank(self.group, group_rank) if self.group is not None else group_rank
 
 
-def sharded_prefill(q_own: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tensor, total_rows: int, window: int,
-                    n_persistent: int, group: Optional[dist.ProcessGroup] = None, overlap: bool = True,
-                    algo: int = 0) -> torch.Tensor:
+_side_streams = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    key = (device.type, device.index)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device)
+    return _side_streams[key]
+
+
+def sharded_prefill(q_own: torch.Tensor, k_own: Optional[torch.Tensor], v_own: Optional[torch.Tensor],
+                    total_rows: int, window: int, n_persistent: int, group: Optional[dist.ProcessGroup] = None,
+                    overlap: bool = True, algo: int = 0, kv: Optional[ShardedKV] = None) -> torch.Tensor:
     """Attention output for this rank's rows (``[B, H, own, dh]``), CUDA only.
 
     ``q_own, k_own, v_own``: ``[B, H, r1 - r0, dh]`` — this rank's rows of the whole-length tensors
-    (rank 0's block starts with the persistent rows).
+    (rank 0's block starts with the persistent rows).  With ``kv`` (from :meth:`ShardedKV.allocate`, its
+    ``k_own`` / ``v_own`` views already filled) ``k_own`` and ``v_own`` are ignored and nothing is copied.
     """
     from . import _native
 
-    kv = ShardedKV(k_own, v_own, total_rows, window, n_persistent, group)
+    if kv is None:
+        kv = ShardedKV(k_own, v_own, total_rows, window, n_persistent, group)
     B, H, own, dh = q_own.shape
     out = torch.empty((B, own, H, dh), dtype=q_own.dtype, device=q_own.device).permute(0, 2, 1, 3)
     # rows whose window needs the halo: the first `window` rows of ranks > 0
@@ -170,7 +207,7 @@ def sharded_prefill(q_own: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tenso
         return out
     kv.exchange_persistent()  # 2 * B * H * Np * dh elements: needed by every row, so it goes first
     main = torch.cuda.current_stream(q_own.device)
-    side = torch.cuda.Stream(q_own.device)
+    side = _side_stream(q_own.device)
     side.wait_stream(main)
     with torch.cuda.stream(side):  # interior rows: every key they need is already in this rank's block
         _native.prefill(q_own[:, :, need_halo:], kv.k, kv.v, window, n_persistent, out=out[:, :, need_halo:],
