@@ -746,11 +746,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     for (int j = 0; j < 32; j += 8) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-#ifdef TMW_MAX2
-                            mx[k] = fmaxf(fmaxf(mx[k], __uint_as_float(s[c][j + 2 * k])), __uint_as_float(s[c][j + 2 * k + 1]));
-#else
                             mx[k] = max3(mx[k], __uint_as_float(s[c][j + 2 * k]), __uint_as_float(s[c][j + 2 * k + 1]));
-#endif
                         }
                     }
                 }
