@@ -184,6 +184,14 @@ TMW_API int tmw_decode_split_static(const tmw_cache_desc* cache, const void* q, 
 TMW_API int tmw_add_rmsnorm(int32_t dtype, int64_t rows, int32_t dim, const void* x, const void* residual,
                             const void* scale, float eps, void* sum_out, void* y, void* stream);
 
+/*
+ * y = 0.5 x (1 + erf(x / sqrt 2)) over n contiguous elements (n a multiple of 8, pointers 16-byte aligned;
+ * y may be x).  Replaces the nn.GELU() between the two linears of the reference's MLP,
+ * titans_core/blocks/mlp.py:58-65 (exact form, not the tanh approximation).  erf is evaluated with an
+ * absolute error below 1.5e-7.
+ */
+TMW_API int tmw_gelu(int32_t dtype, int64_t n, const void* x, void* y, void* stream);
+
 /* Library facts. */
 TMW_API int tmw_version(void);
 TMW_API const char* tmw_strerror(int status);

@@ -65,3 +65,23 @@ def test_rejects_bad_arguments():
         _native.add_rmsnorm(x, None, torch.ones(12, device=DEV), 1e-5)
     with pytest.raises(TypeError):
         _native.add_rmsnorm(torch.randn(4, 16, device=DEV), None, torch.ones(16, device=DEV, dtype=torch.bfloat16), 1e-5)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2e-2), (torch.float16, 4e-3)])
+def test_gelu_is_the_exact_erf_form(dtype, tol):
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(33, 2560, generator=g) * 3).to(dtype)
+    x[0, :8] = torch.tensor([0.0, -0.0, 1e-6, -1e-6, 12.0, -12.0, 40.0, -40.0]).to(dtype)
+    ref = torch.nn.functional.gelu(x.float())  # approximate="none": 0.5 x (1 + erf(x / sqrt 2)), mlp.py:58-65
+    y = _native.gelu(x.to(DEV))
+    assert y.dtype == dtype and (y.float().cpu() - ref).abs().max().item() <= tol
+    z = x.to(DEV).clone()
+    out = _native.gelu(z, inplace=True)
+    assert out.data_ptr() == z.data_ptr() and torch.equal(out, y)
+
+
+def test_gelu_rejects_bad_arguments():
+    with pytest.raises(_native.TmwError):
+        _native.gelu(torch.randn(12, device=DEV))  # not a multiple of 8
+    with pytest.raises(TypeError):
+        _native.gelu(torch.randn(4, 16, device=DEV)[:, ::2])

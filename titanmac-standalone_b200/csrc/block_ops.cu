@@ -18,8 +18,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 add_rmsnorm_kernel(const T* x, const T* __restrict__ res, const T* __restrict__ scale, float eps,
                    T* sum_out, T* __restrict__ y, long long rows, int dim) {
     const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-    if (row >= rows) return;
+    const long long warps = (long long)gridDim.x * kWarpsPerBlock;
+    // a resident grid: every warp walks over rows (a block that lives for one row per warp spends most of
+    // its life being scheduled)
+    for (long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); row < rows; row += warps) {
     const T* xr = x + row * dim;
     const T* rr = res != nullptr ? res + row * dim : nullptr;
     T* sr = sum_out != nullptr ? sum_out + row * dim : nullptr;
@@ -62,13 +64,14 @@ add_rmsnorm_kernel(const T* x, const T* __restrict__ res, const T* __restrict__ 
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rms = sqrtf(ss / (float)dim + eps);  // same operation order as the reference: x / rms * scale
+    // the reference computes x / rms * scale; multiplying by the reciprocal differs by at most one fp32 ulp
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
 
     auto emit = [&](int v, const float (&h)[8]) {
         float g[8], out[8];
         load8<T>(scale + v * 8, g);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) out[i] = h[i] / rms * g[i];
+        for (int i = 0; i < 8; ++i) out[i] = h[i] * inv * g[i];
         store8<T>(yr + v * 8, out);
     };
     if (NV > 0) {
@@ -84,12 +87,16 @@ add_rmsnorm_kernel(const T* x, const T* __restrict__ res, const T* __restrict__ 
             emit(v, h);
         }
     }
+    }  // rows
 }
 
 template <typename T>
 int launch_add_rmsnorm(long long rows, int dim, const void* x, const void* res, const void* scale, float eps,
                        void* sum_out, void* y, cudaStream_t stream) {
-    const unsigned blocks = (unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long want = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const unsigned blocks = (unsigned)(want < (long long)sms * 8 ? want : (long long)sms * 8);  // 8 blocks of 256 threads per SM
     const int nv = (dim / 8 + 31) / 32;
 #define TMW_NORM_CASE(N)                                                                                     \
     add_rmsnorm_kernel<T, N><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(                                    \
@@ -107,8 +114,72 @@ int launch_add_rmsnorm(long long rows, int dim, const void* x, const void* res, 
     return TMW_OK;
 }
 
+// ---- exact GELU --------------------------------------------------------------------------------------
+// 0.5 x (1 + erf(x / sqrt 2)), the default nn.GELU() of the reference's MLP (titans_core/blocks/mlp.py:58-65).
+// erf by Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7, below fp32 rounding of the result): a reciprocal,
+// five multiply-adds and one exp2 instead of the branchy library erff, so that the kernel stays bound by
+// HBM (one read, one write) and not by arithmetic.
+__device__ __forceinline__ float gelu_erf(float x) {
+    const float z = fabsf(x) * 0.70710678118654752f;
+    const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    const float erfc_z = poly * t * exp2f(-z * z * 1.4426950408889634f);  // 1 - erf(z), z >= 0
+    const float erf_abs = 1.0f - erfc_z;
+    return 0.5f * x * (1.0f + copysignf(erf_abs, x));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gelu_kernel(const T* __restrict__ x, T* __restrict__ y, long long nvec) {
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+        float a[8];
+        load8<T>(x + v * 8, a);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a[i] = gelu_erf(a[i]);
+        store8<T>(y + v * 8, a);
+    }
+}
+
+template <typename T>
+int launch_gelu(long long n, const void* x, void* y, cudaStream_t stream) {
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long nvec = n / 8;
+    const long long want = (nvec + 255) / 256;
+    const unsigned blocks = (unsigned)(want < (long long)sms * 8 ? want : (long long)sms * 8);
+    gelu_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(y), nvec);
+    TMW_CUDA_TRY(cudaGetLastError());
+    return TMW_OK;
+}
+
 }  // namespace
 }  // namespace tmw
+
+extern "C" int tmw_gelu(int32_t dtype, int64_t n, const void* x, void* y, void* stream) {
+    using namespace tmw;
+    if (n < 0 || (n > 0 && (x == nullptr || y == nullptr))) {
+        set_error_text("tmw_gelu: null pointer or negative size");
+        return TMW_ERR_INVALID_ARGUMENT;
+    }
+    if (dtype != TMW_F32 && dtype != TMW_BF16 && dtype != TMW_F16) return TMW_ERR_INVALID_ARGUMENT;
+    if (n % 8 != 0) {
+        set_error_text("tmw_gelu: the element count must be a multiple of 8");
+        return TMW_ERR_UNSUPPORTED;
+    }
+    if ((((uintptr_t)x | (uintptr_t)y) & 15) != 0) {
+        set_error_text("tmw_gelu: both pointers must be 16-byte aligned");
+        return TMW_ERR_INVALID_ARGUMENT;
+    }
+    if (n == 0) return TMW_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case TMW_F32: return launch_gelu<float>(n, x, y, s);
+        case TMW_BF16: return launch_gelu<__nv_bfloat16>(n, x, y, s);
+        default: return launch_gelu<__half>(n, x, y, s);
+    }
+}
 
 extern "C" int tmw_add_rmsnorm(int32_t dtype, int64_t rows, int32_t dim, const void* x, const void* residual,
                                const void* scale, float eps, void* sum_out, void* y, void* stream) {
@@ -128,7 +199,6 @@ extern "C" int tmw_add_rmsnorm(int32_t dtype, int64_t rows, int32_t dim, const v
         return TMW_ERR_INVALID_ARGUMENT;
     }
     if (rows == 0) return TMW_OK;
-    if ((rows + kWarpsPerBlock - 1) / kWarpsPerBlock > 0x7fffffffLL) return TMW_ERR_TOO_LARGE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (dtype) {
         case TMW_F32: return launch_add_rmsnorm<float>(rows, dim, x, residual, scale, eps, sum_out, y, s);

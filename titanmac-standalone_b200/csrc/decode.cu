@@ -24,6 +24,9 @@
 #ifndef TMW_DECODE_STREAM
 #define TMW_DECODE_STREAM 1
 #endif
+#ifndef TMW_DECODE_STREAM_WPP
+#define TMW_DECODE_STREAM_WPP 0
+#endif
 #ifndef TMW_DECODE_STREAM_MIN_PAIRS_PER_SM
 #define TMW_DECODE_STREAM_MIN_PAIRS_PER_SM 4
 #endif
@@ -342,7 +345,7 @@ decode_kernel(const DecodeParams p) {
 constexpr int kStreamStages = 3;
 constexpr int kStreamChunkBytes = 2048;
 constexpr int kStreamWarpBytes = kStreamStages * 2 * kStreamChunkBytes;
-constexpr int kStreamSmemBytes = 2 * kStreamWarpBytes + 2 * kStreamStages * 8;
+constexpr int stream_smem_bytes(int warps) { return warps * kStreamWarpBytes + warps * kStreamStages * 8; }
 constexpr long long kStreamWaitCycles = 2000000000LL;  // about one second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -378,8 +381,12 @@ __device__ __forceinline__ void unpack16<__half>(const uint4& a, float (&f)[8]) 
     }
 }
 
-template <typename T, int DH>
-__global__ void __launch_bounds__(64, 9) decode_stream_kernel(const DecodeParams p) {
+// WPP = warps per pair.  1: two pairs per 64-thread CTA, nine CTAs per SM (all pairs of a large batch resident);
+// 2 and 4: one pair per CTA, the warps take the chunks in turn and merge their partial results through shared
+// memory at the end (smaller batches: more bytes in flight per pair).
+template <typename T, int DH, int WPP>
+__global__ void __launch_bounds__(WPP == 1 ? 64 : WPP * 32, WPP == 1 ? 9 : (WPP == 2 ? 9 : 4))
+decode_stream_kernel(const DecodeParams p) {
     static_assert(sizeof(T) == 2, "the streaming variant is for 16-bit caches");
     constexpr int LPK = DH / 8;                    // lanes per key row
     constexpr int RPW = 32 / LPK;                  // key rows per warp per pass
@@ -389,12 +396,14 @@ __global__ void __launch_bounds__(64, 9) decode_stream_kernel(const DecodeParams
     static_assert(CH % RPW == 0 && PASSES >= 1, "chunk geometry");
     extern __shared__ __align__(128) unsigned char stream_smem[];
 
+    constexpr int NW = WPP == 1 ? 2 : WPP;  // warps per CTA
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int pair = blockIdx.x * 2 + warp;
-    if (pair >= p.batch * p.heads) return;  // whole warps leave together; the warps of a CTA never synchronise
+    const int pair = WPP == 1 ? blockIdx.x * 2 + warp : blockIdx.x;
+    const int wslot = WPP == 1 ? 0 : warp;  // which share of the chunks this warp scans
+    if (pair >= p.batch * p.heads) return;  // WPP == 1 only (whole warps; those warps never synchronise)
     unsigned char* stage_mem = stream_smem + warp * kStreamWarpBytes;
     const uint32_t stage_u32 = smem_u32(stage_mem);
-    const uint32_t bar0 = smem_u32(stream_smem + 2 * kStreamWarpBytes) + warp * kStreamStages * 8;
+    const uint32_t bar0 = smem_u32(stream_smem + NW * kStreamWarpBytes) + warp * kStreamStages * 8;
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < kStreamStages; ++s)
@@ -424,13 +433,15 @@ __global__ void __launch_bounds__(64, 9) decode_stream_kernel(const DecodeParams
         r0 = (ring ? c - n_pc : c) * CH;
         return min(CH, (ring ? count : p.np) - r0);
     };
-    auto issue = [&](int c) {  // lane 0
+    // this warp's chunks are wslot, wslot + WPP, ...; n counts them
+    const int my_chunks = n_chunks > wslot ? (n_chunks - wslot + WPP - 1) / WPP : 0;
+    auto issue = [&](int n) {  // lane 0
         int r0;
         bool ring;
-        const int nr = chunk_rows(c, r0, ring);
+        const int nr = chunk_rows(n * WPP + wslot, r0, ring);
         const uint32_t bytes = (uint32_t)nr * ROWB;
-        const uint32_t bar = bar0 + (c % kStreamStages) * 8;
-        const uint32_t dst = stage_u32 + (c % kStreamStages) * 2 * kStreamChunkBytes;
+        const uint32_t bar = bar0 + (n % kStreamStages) * 8;
+        const uint32_t dst = stage_u32 + (n % kStreamStages) * 2 * kStreamChunkBytes;
         const T* ksrc = (ring ? kr : kp) + (long long)r0 * DH;
         const T* vsrc = (ring ? vr : vp) + (long long)r0 * DH;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
@@ -440,7 +451,7 @@ __global__ void __launch_bounds__(64, 9) decode_stream_kernel(const DecodeParams
                      ::"r"(dst + kStreamChunkBytes), "l"(vsrc), "r"(bytes), "r"(bar) : "memory");
     };
     if (lane == 0)
-        for (int c = 0; c < min(kStreamStages, n_chunks); ++c) issue(c);
+        for (int n = 0; n < min(kStreamStages, my_chunks); ++n) issue(n);
 
     // the new token (every lane group computes its score, group 0 owns it)
     float qreg[8];
@@ -455,17 +466,18 @@ __global__ void __launch_bounds__(64, 9) decode_stream_kernel(const DecodeParams
         for (int e = 0; e < 8; ++e) part = fmaf(qreg[e], kf[e], part);
 #pragma unroll
         for (int off = 1; off < LPK; off <<= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-        m = grp == 0 ? part * p.scale_log2 : -CUDART_INF_F;
-        l = grp == 0 ? 1.f : 0.f;
+        const bool owner = grp == 0 && wslot == 0;
+        m = owner ? part * p.scale_log2 : -CUDART_INF_F;
+        l = owner ? 1.f : 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = grp == 0 ? vf[e] : 0.f;
+        for (int e = 0; e < 8; ++e) acc[e] = owner ? vf[e] : 0.f;
     }
 
     bool failed = false;
-    for (int c = 0; c < n_chunks; ++c) {
-        const int stage = c % kStreamStages;
+    for (int n = 0; n < my_chunks; ++n) {
+        const int stage = n % kStreamStages;
         const uint32_t bar = bar0 + stage * 8;
-        const uint32_t parity = (uint32_t)(c / kStreamStages) & 1u;
+        const uint32_t parity = (uint32_t)(n / kStreamStages) & 1u;
         if (!__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) {  // the whole warp takes the slow path together
             const long long t0 = clock64();
             bool expired = false;
@@ -482,7 +494,7 @@ __global__ void __launch_bounds__(64, 9) decode_stream_kernel(const DecodeParams
         }
         int r0;
         bool ring;
-        const int nr = chunk_rows(c, r0, ring);
+        const int nr = chunk_rows(n * WPP + wslot, r0, ring);
         const unsigned char* ks = stage_mem + stage * 2 * kStreamChunkBytes;
         const unsigned char* vs = ks + kStreamChunkBytes;
 
@@ -525,19 +537,29 @@ __global__ void __launch_bounds__(64, 9) decode_stream_kernel(const DecodeParams
             }
         }
         __syncwarp();  // every lane has read the stage: it may be filled again
-        if (lane == 0 && c + kStreamStages < n_chunks) issue(c + kStreamStages);
+        if (lane == 0 && n + kStreamStages < my_chunks) issue(n + kStreamStages);
     }
     if (failed) {
         // a copy did not arrive in time: report, give copies that may still be in flight time to land in this
-        // CTA's shared memory, and leave without touching the cache or the output
+        // CTA's shared memory, and leave the cache and the output untouched
         if (lane == 0) atomicCAS(p.status, 0, (int)TMW_ERR_DEVICE_TIMEOUT);
         const long long t0 = clock64();
         while (clock64() - t0 < 400000) __nanosleep(1000);
-        return;
+        if (WPP == 1) return;
+    }
+    if (WPP > 1) {
+        // all warps of the pair have finished scanning (also the way out after a failed wait: nobody
+        // is left behind at the barrier, and nothing is written)
+        __shared__ int any_failed;
+        if (threadIdx.x == 0) any_failed = 0;
+        __syncthreads();
+        if (failed && lane == 0) any_failed = 1;
+        __syncthreads();
+        if (any_failed) return;
     }
 
     // the new token's key and value go into their ring slot for the following steps
-    if (grp == 0) {
+    if (grp == 0 && wslot == 0) {
         float tmp[8];
         load8<T>(kn + sub * 8, tmp);
         store8<T>(kr + (long long)slot_new * DH + sub * 8, tmp);
@@ -560,20 +582,53 @@ __global__ void __launch_bounds__(64, 9) decode_stream_kernel(const DecodeParams
         }
         m = m_new;
     }
-    if (grp == 0) {
-        T* out = static_cast<T*>(p.o) + b * p.os[0] + h * p.os[1];
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        float res[8];
+    T* out = static_cast<T*>(p.o) + b * p.os[0] + h * p.os[1];
+    if (WPP == 1) {
+        if (grp == 0) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float res[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) res[e] = acc[e] * inv;
-        store8<T>(out + sub * 8, res);
+            for (int e = 0; e < 8; ++e) res[e] = acc[e] * inv;
+            store8<T>(out + sub * 8, res);
+        }
+    } else {
+        // merge the warps through shared memory
+        __shared__ float sm_m[NW], sm_l[NW];
+        __shared__ float sm_acc[NW][DH];
+        if (grp == 0) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sm_acc[warp][sub * 8 + e] = acc[e];
+            if (sub == 0) {
+                sm_m[warp] = m;
+                sm_l[warp] = l;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < LPK) {
+            float m_all = -CUDART_INF_F;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) m_all = fmaxf(m_all, sm_m[w]);
+            float l_all = 0.f;
+            float res[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                const float a = sm_m[w] > -CUDART_INF_F ? exp2f(sm_m[w] - m_all) : 0.f;
+                l_all += sm_l[w] * a;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) res[e] += sm_acc[w][threadIdx.x * 8 + e] * a;
+            }
+            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) res[e] *= inv;
+            store8<T>(out + threadIdx.x * 8, res);
+        }
     }
 }
 
-template <typename T, int DH>
+template <typename T, int DH, int WPP>
 int launch_decode_stream(const DecodeParams& p, cudaStream_t stream) {
     if constexpr (sizeof(T) == 2 && (DH == 64 || DH == 128)) {
-        auto kern = decode_stream_kernel<T, DH>;
+        auto kern = decode_stream_kernel<T, DH, WPP>;
         // nine 64-thread CTAs with 24 KB each per SM: ask for the largest shared-memory carve-out, once per
         // device (so that later calls, e.g. under stream capture, only launch)
         static bool configured[64] = {false};
@@ -581,10 +636,13 @@ int launch_decode_stream(const DecodeParams& p, cudaStream_t stream) {
         TMW_CUDA_TRY(cudaGetDevice(&dev));
         if (dev < 0 || dev >= 64 || !configured[dev]) {
             TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, 100));
+            TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              stream_smem_bytes(WPP == 1 ? 2 : WPP)));
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
         const int pairs = p.batch * p.heads;
-        kern<<<(pairs + 1) / 2, 64, kStreamSmemBytes, stream>>>(p);
+        if (WPP == 1) kern<<<(pairs + 1) / 2, 64, stream_smem_bytes(2), stream>>>(p);
+        else kern<<<pairs, WPP * 32, stream_smem_bytes(WPP), stream>>>(p);
         TMW_CUDA_TRY(cudaGetLastError());
         return TMW_OK;
     } else {
@@ -634,8 +692,10 @@ int launch_decode_shape(const DecodeParams& p, cudaStream_t stream) {
     // 16-bit caches whose rows are whole 16-byte units at 16-byte aligned addresses take the streaming variant
     constexpr bool kStreamShape = sizeof(T) == 2 && (DH == 64 || DH == 128);
     const bool aligned = (((uintptr_t)p.k_ring | (uintptr_t)p.v_ring | (uintptr_t)p.k_pers | (uintptr_t)p.v_pers) & 15) == 0;
-    if (TMW_DECODE_STREAM && kStreamShape && aligned && pairs > TMW_DECODE_STREAM_MIN_PAIRS_PER_SM * sms) {
-        return launch_decode_stream<T, DH>(p, stream);
+    if (TMW_DECODE_STREAM && kStreamShape && aligned) {
+        if (pairs > TMW_DECODE_STREAM_MIN_PAIRS_PER_SM * sms) return launch_decode_stream<T, DH, 1>(p, stream);
+        if (TMW_DECODE_STREAM_WPP == 2 && pairs > sms) return launch_decode_stream<T, DH, 2>(p, stream);
+        if (TMW_DECODE_STREAM_WPP == 4 && pairs > sms / 2) return launch_decode_stream<T, DH, 4>(p, stream);
     }
     if (pairs > 9 * sms) {
         decode_kernel<T, DH, 1><<<(pairs + 1) / 2, 64, 0, stream>>>(p);

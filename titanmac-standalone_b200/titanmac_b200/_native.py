@@ -115,6 +115,7 @@ SIGNATURES = {
          ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
          ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p],
     ),
+    "tmw_gelu": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "tmw_add_rmsnorm": (
         ctypes.c_int,
         [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
@@ -303,6 +304,23 @@ class RingCache:
                 check(lib().tmw_decode(ctypes.byref(c), q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
                                        out.data_ptr(), qs, ns, os_, pos.data_ptr(), _stream_ptr(self.device)))
         return out
+
+
+def gelu_supported(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype in _DTYPES and x.numel() % 8 == 0 and x.is_contiguous()
+
+
+def gelu(x: torch.Tensor, inplace: bool = False) -> torch.Tensor:
+    """Exact (erf) GELU of a contiguous CUDA tensor — the nn.GELU() of titans_core/blocks/mlp.py:58-65."""
+    _require_cuda(x)
+    if x.dtype not in _DTYPES or not x.is_contiguous():
+        raise TypeError("gelu: contiguous fp32 / bf16 / fp16 tensor expected")
+    y = x if inplace else torch.empty_like(x)
+    if x.numel() == 0:
+        return y
+    with torch.cuda.device(x.device):
+        check(lib().tmw_gelu(_DTYPES[x.dtype], x.numel(), x.data_ptr(), y.data_ptr(), _stream_ptr(x.device)))
+    return y
 
 
 def add_rmsnorm_supported(x: torch.Tensor) -> bool:

@@ -4,7 +4,7 @@ Mirrors titans_core/blocks/titan_block.py:41-102, blocks/norms.py:39-60 and
 blocks/mlp.py:28-67 of the reference (same submodule names, so checkpoints load
 unchanged).  The attention is this package's own code, and so is the element-wise work around
 it on a GPU: RMSNorm with the preceding residual add folded in is one kernel
-(``tmw_add_rmsnorm``); the MLP's linears and its GELU stay library calls.  The reference's
+(``tmw_add_rmsnorm``) and the exact GELU is another (``tmw_gelu``); the linears stay library calls.  The reference's
 default ``use_block_sparse=True`` selects a different attention class with different math,
 which this package does not provide: it is refused here instead of being silently replaced.
 The package is forward-only; an input that carries a gradient takes the plain PyTorch norm.
@@ -56,7 +56,12 @@ class MLPBlock(nn.Module):
         self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.dropout(self.fc2(self.activation(self.fc1(x))))
+        h = self.fc1(x)
+        if _native.gelu_supported(h) and not (torch.is_grad_enabled() and h.requires_grad):
+            h = _native.gelu(h, inplace=True)  # same exact-erf GELU in one pass bound by HBM
+        else:
+            h = self.activation(h)
+        return self.dropout(self.fc2(h))
 
 
 class TitanBlock(nn.Module):
