@@ -177,7 +177,7 @@ def run_model_cases(out: dict) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     sys.dont_write_bytecode = True
     sys.path.insert(0, args.reference)

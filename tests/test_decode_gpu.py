@@ -55,14 +55,17 @@ def test_decode_bf16_matches_fp32_oracle(dh, w, Np, B, H, L, pre):
 
 
 @pytest.mark.parametrize("dh,w,Np,B,H,steps,pre,dtype", [
-    (64, 40, 5, 80, 8, 60, 0, torch.bfloat16),    # 640 pairs: every SM gets more than four -> streaming kernel
+    (64, 40, 5, 80, 8, 60, 0, torch.bfloat16),    # 640 pairs: one pair per two-warp CTA
+    (64, 19, 3, 170, 8, 12, 25, torch.bfloat16),  # 1360 pairs: one warp per pair, two pairs per CTA
+    (64, 45, 16, 20, 5, 70, 0, torch.bfloat16),   # 100 pairs: four warps share a pair
+    (128, 30, 2, 16, 8, 40, 10, torch.float16),   # 128 pairs, head_dim 128, four warps
     (64, 37, 16, 100, 10, 30, 30, torch.bfloat16),
     (128, 21, 0, 75, 8, 50, 3, torch.float16),    # no persistent keys, ring shorter than one chunk at first
     (128, 33, 7, 160, 4, 20, 40, torch.bfloat16),
 ])
 def test_decode_streaming_kernel_many_pairs(dh, w, Np, B, H, steps, pre, dtype):
-    """Batches with more than four (sequence, head) pairs per SM run the shared-memory streaming variant:
-    same contract - first tokens, a ring that is not full yet, and several wraps of the ring."""
+    """16-bit caches with more than half a pair per SM run the shared-memory streaming variant in one of its
+    three launch shapes: same contract - first tokens, a ring that is not full yet, several wraps of the ring."""
     L = Np + pre + steps
     q, k, v = (t.to(dtype) for t in wo.qkv_inputs(B, H, L, dh, seed=dh + w + B))
     k[1:, :, :Np] = k[:1, :, :Np]

@@ -11,7 +11,7 @@
 // ONE warp (no block-level merge, all pairs resident at once, so no wave
 // quantisation); with few pairs a whole CTA of 8 warps shares one pair.
 //
-// 16-bit caches with more than four pairs per SM take decode_stream_kernel further
+// 16-bit caches with more than half a pair per SM take decode_stream_kernel further
 // down instead: the same arithmetic fed from shared memory, which bulk asynchronous
 // copies keep filled three chunks ahead (measured on B200, 2560 pairs, window 512:
 // 60 us against 68 us; 5120 pairs: 105 us against 129 us, the bandwidth of a plain copy).
@@ -23,12 +23,6 @@
 
 #ifndef TMW_DECODE_STREAM
 #define TMW_DECODE_STREAM 1
-#endif
-#ifndef TMW_DECODE_STREAM_WPP
-#define TMW_DECODE_STREAM_WPP 0
-#endif
-#ifndef TMW_DECODE_STREAM_MIN_PAIRS_PER_SM
-#define TMW_DECODE_STREAM_MIN_PAIRS_PER_SM 4
 #endif
 
 namespace tmw {
@@ -693,9 +687,12 @@ int launch_decode_shape(const DecodeParams& p, cudaStream_t stream) {
     constexpr bool kStreamShape = sizeof(T) == 2 && (DH == 64 || DH == 128);
     const bool aligned = (((uintptr_t)p.k_ring | (uintptr_t)p.v_ring | (uintptr_t)p.k_pers | (uintptr_t)p.v_pers) & 15) == 0;
     if (TMW_DECODE_STREAM && kStreamShape && aligned) {
-        if (pairs > TMW_DECODE_STREAM_MIN_PAIRS_PER_SM * sms) return launch_decode_stream<T, DH, 1>(p, stream);
-        if (TMW_DECODE_STREAM_WPP == 2 && pairs > sms) return launch_decode_stream<T, DH, 2>(p, stream);
-        if (TMW_DECODE_STREAM_WPP == 4 && pairs > sms / 2) return launch_decode_stream<T, DH, 4>(p, stream);
+        // every shape runs as a single wave: 2 pairs per CTA x 9 CTAs per SM, 1 pair per 2-warp CTA x 9, or
+        // 1 pair per 4-warp CTA x 4 (measured, us per layer at window 512: 2560 pairs 60, 800 pairs 20.8,
+        // 640 pairs 18.5, 480 pairs 14.3, 320 pairs 11.8, 160 pairs 8.9)
+        if (pairs > 9 * sms) return launch_decode_stream<T, DH, 1>(p, stream);
+        if (pairs > 4 * sms) return launch_decode_stream<T, DH, 2>(p, stream);
+        if (pairs > sms / 2) return launch_decode_stream<T, DH, 4>(p, stream);
     }
     if (pairs > 9 * sms) {
         decode_kernel<T, DH, 1><<<(pairs + 1) / 2, 64, 0, stream>>>(p);
