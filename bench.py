@@ -394,7 +394,8 @@ def run_decode(args, wl_name: str, wl: dict) -> None:
         raise SystemExit("the batch must divide by the number of GPUs")
     B = wl["batch"] // world
     cfg = TitanMACConfig(vocab_size=wl["vocab"], d_model=wl["d_model"], n_heads=wl["heads"], n_layers=wl["layers"],
-                         d_ff=wl["d_ff"], max_seq_len=4096, window_size=wl["window"], n_persistent=wl["n_persistent"])
+                         d_ff=wl["d_ff"], max_seq_len=4096, window_size=wl["window"], n_persistent=wl["n_persistent"],
+                         use_block_sparse=False)
     g = torch.Generator(device="cpu").manual_seed(0)
     model = TitanMAC(cfg).eval()
     with torch.no_grad():  # every weight N(0, 0.02), biases 0, norm scales 1
@@ -524,7 +525,7 @@ def run_model_prefill(args, wl_name: str, wl: dict) -> None:
     B, T, D, H, w, Np = wl["batch"], wl["T"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
     L, V, F_, NL = Np + T, wl["vocab"], wl["d_ff"], wl["layers"]
     cfg = TitanMACConfig(vocab_size=V, d_model=D, n_heads=H, n_layers=NL, d_ff=F_, max_seq_len=T, window_size=w,
-                         n_persistent=Np)
+                         n_persistent=Np, use_block_sparse=False)
     g = torch.Generator(device="cpu").manual_seed(0)
     model = TitanMAC(cfg).eval()
     with torch.no_grad():  # every weight N(0, 0.02), biases 0, norm scales 1

@@ -91,6 +91,30 @@ TMW_API int tmw_prefill(const tmw_prefill_desc* desc, const void* q, const void*
                 void* stream);
 
 /*
+ * Prefill with the mask of the reference's BlockSparseAttention (its default attention class,
+ * titans_core/attn/block_sparse_attention.py:258-343), for whole sequences (q_pos0 = 0,
+ * k_pos0 = n_persistent, q_rows = k_rows = L; desc->window is its window_size):
+ *   - the sequence row with sequence index t sees the persistent keys and the sequence keys
+ *     max(0, floor(t / block_size) * block_size - window) .. t   (:299-311, :147-156);
+ *   - the n_persistent persistent query rows see every key, later rows included (:283-291).
+ * q, k, v are the tensors after that class's depthwise convolutions (tmw_causal_dwconv).
+ * Replaces its Python loop over query blocks with per-block concatenation, mask and softmax.
+ */
+TMW_API int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block_size, const void* q, const void* k,
+                                     const void* v, void* o, void* stream);
+
+/*
+ * Causal depthwise convolution along the rows: y[b, t, c] = sum_j weight[c, j] * x[b, t - (taps-1) + j, c],
+ * rows before the first count as zero.  x, y: [batch, rows, channels] contiguous (channels a multiple of 8,
+ * 16-byte aligned); weight: [channels, taps] contiguous, same dtype, 1 <= taps <= 8; y must not overlap x.
+ * Replaces the three Conv1d(groups=d_model, padding=taps-1) calls with their transposes and trimming in
+ * BlockSparseAttention.forward (block_sparse_attention.py:241-256) - with channels = 3 * d_model and the
+ * three filters stacked it is one pass over the QKV projection output.
+ */
+TMW_API int tmw_causal_dwconv(int32_t dtype, int32_t batch, int32_t rows, int32_t channels, int32_t taps,
+                              const void* x, const void* weight, void* y, void* stream);
+
+/*
  * Decode: one new token per sequence against a ring cache of the last window+1
  * keys.  The reference has no incremental decode (its generation helper re-runs
  * the full forward per token, examples/train_math.py:146-161); this entry point

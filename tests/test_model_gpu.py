@@ -18,13 +18,13 @@ def load_sd(golden_model, prefix):
 def block_cfg(g):
     d_model, n_heads, d_ff, w, Np = (int(v) for v in g.np("block", "cfg"))
     return TitanMACConfig(vocab_size=97, d_model=d_model, n_heads=n_heads, n_layers=1, d_ff=d_ff, max_seq_len=256,
-                          window_size=w, n_persistent=Np)
+                          window_size=w, n_persistent=Np, use_block_sparse=False)
 
 
 def model_cfg(g):
     V, d_model, n_heads, n_layers, d_ff, max_len, w, Np = (int(v) for v in g.np("model", "cfg"))
     return TitanMACConfig(vocab_size=V, d_model=d_model, n_heads=n_heads, n_layers=n_layers, d_ff=d_ff,
-                          max_seq_len=max_len, window_size=w, n_persistent=Np)
+                          max_seq_len=max_len, window_size=w, n_persistent=Np, use_block_sparse=False)
 
 
 def test_block_matches_reference(golden_model):
@@ -36,10 +36,15 @@ def test_block_matches_reference(golden_model):
     assert (y - golden_model["block", "y"]).abs().max().item() <= 2e-5
 
 
-def test_block_refuses_block_sparse():
-    cfg = TitanMACConfig(use_block_sparse=True)
-    with pytest.raises(NotImplementedError):
-        TitanBlock(cfg)
+def test_config_selects_the_attention_class_like_the_reference():
+    from titanmac_b200 import BlockSparseAttention, WindowedAttention
+
+    assert isinstance(TitanBlock(TitanMACConfig(d_model=128, n_heads=2, d_ff=128)).attention, BlockSparseAttention)
+    assert isinstance(TitanBlock(TitanMACConfig(d_model=128, n_heads=2, d_ff=128, use_block_sparse=False)).attention,
+                      WindowedAttention)
+    model = TitanMAC(TitanMACConfig(vocab_size=50, d_model=128, n_heads=2, n_layers=1, d_ff=128, max_seq_len=64))
+    with pytest.raises(NotImplementedError):  # the ring-cache path belongs to the windowed class
+        model.new_caches(1, DEV, torch.bfloat16)
 
 
 def test_model_forward_matches_reference_logits(golden_model):

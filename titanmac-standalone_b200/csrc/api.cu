@@ -151,6 +151,32 @@ int tmw_prefill(const tmw_prefill_desc* desc, const void* q, const void* k, cons
     return tmw::launch_prefill_simt(*desc, q, k, v, o, s);
 }
 
+int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block_size, const void* q, const void* k,
+                             const void* v, void* o, void* stream) {
+    const int rc = tmw::validate_prefill(desc, q, k, v, o);
+    if (rc != TMW_OK) return rc;
+    if (block_size <= 0 || block_size > (1 << 20)) {
+        tmw::set_error_text("tmw_prefill_block_sparse: block_size must be positive (at most 2^20)");
+        return TMW_ERR_INVALID_ARGUMENT;
+    }
+    if (desc->q_pos0 != 0 || desc->k_pos0 != desc->n_persistent || desc->q_rows != desc->k_rows) {
+        tmw::set_error_text("tmw_prefill_block_sparse: whole sequences only (q_pos0 = 0, k_pos0 = n_persistent, q_rows = k_rows)");
+        return TMW_ERR_UNSUPPORTED;
+    }
+    if (desc->batch == 0 || desc->heads == 0 || desc->q_rows == 0) return TMW_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    tmw_prefill_desc d = *desc;
+    const bool tc_ok = tmw::prefill_tc_supports(d, q, k, v, o) && (int64_t)d.q_rows + d.window + block_size < ((int64_t)1 << 29);
+    if (d.algo == TMW_ALGO_TCGEN05 && !tc_ok) return TMW_ERR_UNSUPPORTED;
+    // every row with the block-granular window and the persistent keys ...
+    int st = (d.algo != TMW_ALGO_SIMT && tc_ok) ? tmw::launch_prefill_tc(d, q, k, v, o, s, block_size)
+                                                : tmw::launch_prefill_simt(d, q, k, v, o, s, block_size, false);
+    if (st != TMW_OK || d.n_persistent == 0) return st;
+    // ... then the persistent query rows again, this time seeing every key (a few rows: CUDA-core kernel)
+    d.q_rows = d.n_persistent;
+    return tmw::launch_prefill_simt(d, q, k, v, o, s, block_size, true);
+}
+
 size_t tmw_cache_ring_bytes(int32_t dtype, int32_t batch, int32_t heads, int32_t head_dim, int32_t window) {
     if (!tmw::dtype_ok(dtype) || batch < 0 || heads < 0 || head_dim <= 0 || window < 0) return 0;
     return (size_t)batch * (size_t)heads * ((size_t)window + 1) * (size_t)head_dim * tmw::dtype_size(dtype);

@@ -1,3 +1,5 @@
+// Element-wise kernels around the attention call (all HBM-bound, 16-byte accesses).
+//
 // Residual add + RMSNorm in one pass over the rows: the element-wise work that surrounds the
 // attention module in a TitanBlock (titans_core/blocks/titan_block.py:92-100 of the reference,
 // norm formula titans_core/blocks/norms.py:55-58).  In PyTorch the residual add and the norm are
@@ -154,8 +156,108 @@ int launch_gelu(long long n, const void* x, void* y, cudaStream_t stream) {
     return TMW_OK;
 }
 
+// ---- causal depthwise convolution along the rows ---------------------------------------------------------
+// y[b, t, c] = sum_j w[c, j] * x[b, t - (TAPS-1) + j, c]: the Conv1d(groups = channels, padding = TAPS-1),
+// trimmed to the input length, that the reference's block-sparse attention applies to Q, K and V
+// (titans_core/attn/block_sparse_attention.py:77-92, 241-256).  One thread owns 8 adjacent channels and
+// walks down a strip of rows with the last TAPS rows in registers: x is read once (plus TAPS-1 rows per
+// strip), y written once.
+constexpr int kConvStrip = 64;
+constexpr int kConvThreads = 128;
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(kConvThreads)
+dwconv_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, int rows, int channels) {
+    const int vec = blockIdx.x * kConvThreads + threadIdx.x;  // which group of 8 channels
+    if (vec * 8 >= channels) return;
+    const int t0 = blockIdx.y * kConvStrip;
+    const int t1 = min(rows, t0 + kConvStrip);
+    const long long base = (long long)blockIdx.z * rows * channels + vec * 8;
+    float wr[TAPS][8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wr[j][c] = to_f32<T>(w[(long long)(vec * 8 + c) * TAPS + j]);
+    float hist[TAPS][8];  // hist[j] = x[t - (TAPS-1) + j]
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) {
+        const int t = t0 - (TAPS - 1) + j;
+        if (t >= 0) {
+            load8<T>(x + base + (long long)t * channels, hist[j + 1]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) hist[j + 1][c] = 0.f;
+        }
+    }
+    for (int t = t0; t < t1; ++t) {
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; ++j)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) hist[j][c] = hist[j + 1][c];
+        load8<T>(x + base + (long long)t * channels, hist[TAPS - 1]);
+        float out[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            float a = 0.f;
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) a = fmaf(wr[j][c], hist[j][c], a);
+            out[c] = a;
+        }
+        store8<T>(y + base + (long long)t * channels, out);
+    }
+}
+
+template <typename T, int TAPS>
+int launch_dwconv_taps(int batch, int rows, int channels, const void* x, const void* w, void* y, cudaStream_t stream) {
+    const dim3 grid((channels / 8 + kConvThreads - 1) / kConvThreads, (rows + kConvStrip - 1) / kConvStrip, batch);
+    dwconv_kernel<T, TAPS><<<grid, kConvThreads, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(w),
+                                                              static_cast<T*>(y), rows, channels);
+    TMW_CUDA_TRY(cudaGetLastError());
+    return TMW_OK;
+}
+
+template <typename T>
+int launch_dwconv(int batch, int rows, int channels, int taps, const void* x, const void* w, void* y,
+                  cudaStream_t stream) {
+    switch (taps) {
+        case 1: return launch_dwconv_taps<T, 1>(batch, rows, channels, x, w, y, stream);
+        case 2: return launch_dwconv_taps<T, 2>(batch, rows, channels, x, w, y, stream);
+        case 3: return launch_dwconv_taps<T, 3>(batch, rows, channels, x, w, y, stream);
+        case 4: return launch_dwconv_taps<T, 4>(batch, rows, channels, x, w, y, stream);
+        case 5: return launch_dwconv_taps<T, 5>(batch, rows, channels, x, w, y, stream);
+        case 6: return launch_dwconv_taps<T, 6>(batch, rows, channels, x, w, y, stream);
+        case 7: return launch_dwconv_taps<T, 7>(batch, rows, channels, x, w, y, stream);
+        case 8: return launch_dwconv_taps<T, 8>(batch, rows, channels, x, w, y, stream);
+        default: return TMW_ERR_UNSUPPORTED;
+    }
+}
+
 }  // namespace
 }  // namespace tmw
+
+extern "C" int tmw_causal_dwconv(int32_t dtype, int32_t batch, int32_t rows, int32_t channels, int32_t taps,
+                                 const void* x, const void* weight, void* y, void* stream) {
+    using namespace tmw;
+    if (batch < 0 || rows < 0 || channels <= 0) return TMW_ERR_INVALID_ARGUMENT;
+    if (dtype != TMW_F32 && dtype != TMW_BF16 && dtype != TMW_F16) return TMW_ERR_INVALID_ARGUMENT;
+    if (taps < 1 || taps > 8 || channels % 8 != 0) {
+        set_error_text("tmw_causal_dwconv: 1 to 8 taps and a multiple of 8 channels");
+        return TMW_ERR_UNSUPPORTED;
+    }
+    if (batch == 0 || rows == 0) return TMW_OK;
+    if (x == nullptr || weight == nullptr || y == nullptr || x == y) return TMW_ERR_INVALID_ARGUMENT;
+    if ((((uintptr_t)x | (uintptr_t)y) & 15) != 0) {
+        set_error_text("tmw_causal_dwconv: x and y must be 16-byte aligned");
+        return TMW_ERR_INVALID_ARGUMENT;
+    }
+    if (batch > 65535 || (rows + kConvStrip - 1) / kConvStrip > 65535) return TMW_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case TMW_F32: return launch_dwconv<float>(batch, rows, channels, taps, x, weight, y, s);
+        case TMW_BF16: return launch_dwconv<__nv_bfloat16>(batch, rows, channels, taps, x, weight, y, s);
+        default: return launch_dwconv<__half>(batch, rows, channels, taps, x, weight, y, s);
+    }
+}
 
 extern "C" int tmw_gelu(int32_t dtype, int64_t n, const void* x, void* y, void* stream) {
     using namespace tmw;

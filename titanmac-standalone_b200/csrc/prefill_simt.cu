@@ -36,6 +36,8 @@ struct SimtParams {
     const void* v;
     void* o;
     int q_rows, k_rows, window, np, q_pos0, k_pos0;
+    int block;     // 0 or the block size of the block-granular window
+    int all_keys;  // 1: no mask at all, every key row is visible to every query row of the call
     long long qs[3], ks[3], vs[3], os[3];
     float scale_log2;  // scale * log2(e)
 };
@@ -78,9 +80,10 @@ __global__ void __launch_bounds__(kThreads) prefill_simt_kernel(const SimtParams
     const int p_first = p.q_pos0 + r0;
     const int p_last = p.q_pos0 + min(r0 + S::ROWS, p.q_rows) - 1;
     // window keys this CTA can need: positions [glo, ghi]
-    const int glo = max(p.np, p_first - p.window);
-    const int ghi = p_last;
-    const int n_win = (p_last >= p.np && ghi >= glo) ? ghi - glo + 1 : 0;
+    const int glo = p.all_keys ? p.k_pos0 : first_visible_pos(max(p_first, p.np), p.np, p.window, p.block);
+    const int ghi = p.all_keys ? p.k_pos0 + (p.k_rows - p.np) - 1 : p_last;
+    const int n_win = (p.all_keys || p_last >= p.np) && ghi >= glo ? ghi - glo + 1 : 0;
+    const int my_lo = pos >= p.np ? first_visible_pos(pos, p.np, p.window, p.block) : 0;
     const int n_keys = p.np + n_win;  // virtual key index u: [0,np) persistent, then the window
 
     for (int u0 = 0; u0 < n_keys; u0 += S::BN) {
@@ -133,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) prefill_simt_kernel(const SimtParams
                 const int u = u0 + j;
                 const int g = u < p.np ? u : glo + (u - p.np);
                 const bool vis = valid && u < n_keys &&
-                                 (u < p.np || (pos >= p.np && g <= pos && pos - g <= p.window));
+                                 (p.all_keys || u < p.np || (pos >= p.np && g <= pos && g >= my_lo));
                 s[jj] = vis ? part * p.scale_log2 : -CUDART_INF_F;
                 tmax = fmaxf(tmax, s[jj]);
             }
@@ -206,8 +209,10 @@ int launch_dh(const SimtParams& p, int batch, int heads, int dh, cudaStream_t st
 }  // namespace
 
 int launch_prefill_simt(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, int window_block, bool all_keys) {
     SimtParams p;
+    p.block = window_block;
+    p.all_keys = all_keys ? 1 : 0;
     p.q = q; p.k = k; p.v = v; p.o = o;
     p.q_rows = d.q_rows; p.k_rows = d.k_rows; p.window = d.window; p.np = d.n_persistent;
     p.q_pos0 = d.q_pos0; p.k_pos0 = d.k_pos0;

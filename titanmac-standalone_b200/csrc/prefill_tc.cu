@@ -97,6 +97,8 @@ __device__ long long g_trace[4096];
 
 struct TcParams {
     int q_rows, k_rows, window, np, np_pad, q_pos0, k_pos0;
+    int block;        // 0 or the block size of the block-granular window (first_visible_pos)
+    int window_plan;  // window + block - 1: the widest window any row can have, used to lay out the key tiles
     int dim_order;  // bit i set: tensor i (0=q,1=k,2=v,3=o) has its head axis before its row axis in the map
     float scale_log2;
     int* status;
@@ -321,7 +323,7 @@ __device__ __forceinline__ int floor_div(int a, int b) { return (a >= 0) ? a / b
 __device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block, int tiles) {
     CtaPlan c;
     const int r0 = block * tiles * BM;
-    c.anchor = p.q_pos0 + r0 - p.window;
+    c.anchor = p.q_pos0 + r0 - p.window_plan;
     c.x_begin = 1 << 30;
     c.x_end = 0;
 #pragma unroll
@@ -332,7 +334,7 @@ __device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block, int t
         q.has_pers = (q.rows > 0 && p.np > 0) ? 1 : 0;
         const int p_hi = q.p_lo + q.rows - 1;
         if (q.rows > 0 && p_hi >= p.np) {
-            const int g_lo = max(p.np, q.p_lo - p.window);
+            const int g_lo = first_visible_pos(max(q.p_lo, p.np), p.np, p.window, p.block);
             q.a = floor_div(g_lo - c.anchor, BN);
             q.n_win = floor_div(p_hi - c.anchor, BN) - q.a + 1;
             c.x_begin = min(c.x_begin, q.a);
@@ -686,7 +688,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             } else {
                 const int g0 = plan.anchor + (q.a + item - q.has_pers) * BN;
                 if (pos >= p.np) {
-                    j_lo = max(p.np, pos - p.window) - g0;
+                    j_lo = first_visible_pos(pos, p.np, p.window, p.block) - g0;
                     j_hi = pos - g0;
                 } else {
                     j_lo = 1;
@@ -694,7 +696,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 ncols = BN;
                 // every row of the tile sees every key of the tile (decided per tile, not per row)
-                full = q.p_lo >= p.np && g0 >= p.np && g0 + BN - 1 <= q.p_lo && q.p_lo + BM - 1 - g0 <= p.window;
+                full = q.p_lo >= p.np && g0 >= p.np && g0 + BN - 1 <= q.p_lo &&
+                       g0 >= first_visible_pos(q.p_lo + BM - 1, p.np, p.window, p.block);
             }
             const int nchunks = (ncols + 31) / 32;
             // 32-column chunks in which no row of this warp sees a key (beyond the diagonal, or before the
@@ -974,7 +977,8 @@ bool make_map(CUtensorMap* map, const void* base, int dtype, int batch, int head
 int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
 
 template <int DH, int KS, int VS, int TILES>
-int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream) {
+int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream,
+              int window_block) {
     using L = TcSmem<DH, KS, VS, TILES>;
     const int np_pad = np_pad_of(d.n_persistent);
     CUtensorMap mq, mk, mv, mo, mkp, mvp;
@@ -988,6 +992,8 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
         return TMW_ERR_CUDA;
     TcParams p;
     p.q_rows = d.q_rows; p.k_rows = d.k_rows; p.window = d.window; p.np = d.n_persistent; p.np_pad = np_pad;
+    p.block = window_block;
+    p.window_plan = d.window + (window_block > 0 ? window_block - 1 : 0);
     p.q_pos0 = d.q_pos0; p.k_pos0 = d.k_pos0;
     p.dim_order = (hf[0] ? 1 : 0) | (hf[1] ? 2 : 0) | (hf[2] ? 4 : 0) | (hf[3] ? 8 : 0);
     const float scale = d.scale != 0.f ? d.scale : 1.0f / sqrtf((float)DH);
@@ -1038,16 +1044,16 @@ bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, co
 }
 
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, int window_block) {
     if (d.head_dim == 64) {
         // One query tile per CTA and two CTAs per SM when two such CTAs fit into shared memory (they do
         // unless there are many persistent keys): independent CTAs drift apart, so one CTA's exponentials,
         // start-up and output phase overlap the other's matrix products.
         if (TMW_TILES64 == 1 && TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem)
-            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream);
-        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream);
+            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block);
+        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block);
     }
-    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream);
+    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream, window_block);
 }
 
 }  // namespace tmw

@@ -88,6 +88,19 @@ __device__ __forceinline__ void store8<__half>(__half* p, const float (&in)[8]) 
 
 __host__ __device__ inline size_t dtype_size(int dtype) { return dtype == TMW_F32 ? 4 : 2; }
 
+// Position of the first sequence key that the sequence query at position `pos` (>= np) sees.
+// block == 0: the query and its `window` predecessors (WindowedAttention, windowed_attention.py:136-150).
+// block  > 0: the left edge moves in steps of `block` rows - the query in block b of the sequence sees the
+//             keys from b * block - window on (BlockSparseAttention, block_sparse_attention.py:299-311).
+__host__ __device__ inline int first_visible_pos(int pos, int np, int window, int block) {
+    if (block > 0) {
+        const int lo = ((pos - np) / block) * block - window;
+        return np + (lo > 0 ? lo : 0);
+    }
+    const int lo = pos - window;
+    return lo > np ? lo : np;
+}
+
 // ---- host-side plumbing shared by the entry points ---------------------------------
 void set_cuda_error(cudaError_t e, const char* where);
 void set_error_text(const char* text);
@@ -108,10 +121,12 @@ int validate_decode_call(const tmw_cache_desc* cache, const void* q, const void*
                          const int64_t o_stride[2], const int32_t* pos);
 
 // Kernel launchers (one per translation unit).
+// window_block: 0 = per-token window, > 0 = block-granular left edge (see first_visible_pos);
+// all_keys: every query row of the call sees every key, unmasked (the persistent rows of the block-sparse class)
 int launch_prefill_simt(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                        cudaStream_t stream);
+                        cudaStream_t stream, int window_block = 0, bool all_keys = false);
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                      cudaStream_t stream);
+                      cudaStream_t stream, int window_block = 0);
 bool prefill_tc_supports(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o);
 int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, const void* v_new, void* o,
                   const int64_t qs[2], const int64_t ns[2], const int64_t os[2], const int32_t* pos,

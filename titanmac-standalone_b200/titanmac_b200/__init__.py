@@ -2,10 +2,12 @@
 
 from .config import TitanMACConfig, WindowConfig
 from .attn.windowed_attention import WindowedAttention
+from .attn.block_sparse_attention import BlockSparseAttention, create_block_sparse_attention
 from .blocks.titan_block import MLPBlock, RMSNorm, TitanBlock
 from .models.titanmac import TitanMAC
 from .host_pipeline import HostPipeline
 from . import _native
 
-__all__ = ["TitanMACConfig", "WindowConfig", "WindowedAttention", "TitanBlock", "RMSNorm", "MLPBlock", "TitanMAC",
+__all__ = ["TitanMACConfig", "WindowConfig", "WindowedAttention", "BlockSparseAttention",
+           "create_block_sparse_attention", "TitanBlock", "RMSNorm", "MLPBlock", "TitanMAC",
            "HostPipeline", "_native"]

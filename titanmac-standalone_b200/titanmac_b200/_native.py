@@ -90,6 +90,15 @@ SIGNATURES = {
         [ctypes.POINTER(PrefillDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
          ctypes.c_void_p],
     ),
+    "tmw_prefill_block_sparse": (
+        ctypes.c_int,
+        [ctypes.POINTER(PrefillDesc), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+         ctypes.c_void_p, ctypes.c_void_p],
+    ),
+    "tmw_causal_dwconv": (
+        ctypes.c_int,
+        [ctypes.c_int32] * 5 + [ctypes.c_void_p] * 4,
+    ),
     "tmw_cache_ring_bytes": (ctypes.c_size_t, [ctypes.c_int32] * 5),
     "tmw_cache_fill": (
         ctypes.c_int,
@@ -185,8 +194,12 @@ def prefill(
     k_pos0: Optional[int] = None,
     scale: float = 0.0,
     algo: int = ALGO_AUTO,
+    window_block: int = 0,
 ) -> torch.Tensor:
-    """``tmw_prefill`` on ``[B, H, rows, dh]`` tensors (any strides with a contiguous last axis)."""
+    """``tmw_prefill`` on ``[B, H, rows, dh]`` tensors (any strides with a contiguous last axis).
+
+    ``window_block > 0`` selects ``tmw_prefill_block_sparse``: the mask of the reference's
+    BlockSparseAttention with that block size (whole sequences only)."""
     _require_cuda(q, k, v)
     if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
         raise TypeError("q, k, v must share one dtype out of float32, bfloat16, float16")
@@ -208,9 +221,34 @@ def prefill(
     d.v_stride[:] = _bhrd_strides(v)
     d.o_stride[:] = _bhrd_strides(out)
     with torch.cuda.device(q.device):
-        check(lib().tmw_prefill(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                _stream_ptr(q.device)))
+        if window_block > 0:
+            check(lib().tmw_prefill_block_sparse(ctypes.byref(d), window_block, q.data_ptr(), k.data_ptr(),
+                                                 v.data_ptr(), out.data_ptr(), _stream_ptr(q.device)))
+        else:
+            check(lib().tmw_prefill(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                    _stream_ptr(q.device)))
     return out
+
+
+def causal_dwconv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``y[b, t, c] = sum_j weight[c, j] * x[b, t - (taps-1) + j, c]`` for ``x [B, T, C]`` contiguous and
+    ``weight [C, taps]`` — the causal depthwise Conv1d of block_sparse_attention.py:241-256 without the
+    transposes."""
+    _require_cuda(x, weight)
+    if x.dtype not in _DTYPES or weight.dtype != x.dtype or x.dim() != 3 or weight.dim() != 2:
+        raise TypeError("causal_dwconv: x [B, T, C] and weight [C, taps] of one dtype out of fp32 / bf16 / fp16")
+    if weight.shape[0] != x.shape[2]:
+        raise ValueError("causal_dwconv: one filter per channel")
+    x = x if x.is_contiguous() else x.contiguous()
+    weight = weight if weight.is_contiguous() else weight.contiguous()
+    y = torch.empty_like(x)
+    B, T, C = x.shape
+    if B == 0 or T == 0:
+        return y
+    with torch.cuda.device(x.device):
+        check(lib().tmw_causal_dwconv(_DTYPES[x.dtype], B, T, C, weight.shape[1], x.data_ptr(), weight.data_ptr(),
+                                      y.data_ptr(), _stream_ptr(x.device)))
+    return y
 
 
 class RingCache:

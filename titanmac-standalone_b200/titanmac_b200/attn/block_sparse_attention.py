@@ -1,0 +1,90 @@
+"""Drop-in for the reference's ``BlockSparseAttention`` (its default attention class) on B200.
+
+Same constructor arguments, attributes and ``state_dict`` keys (``qkv_proj.weight``,
+``conv_q.weight``, ``conv_k.weight``, ``conv_v.weight`` of shape ``[d_model, 1, taps]``,
+``out_proj.weight``) and ``forward(x, attn_mask=None)`` as
+titans_core/attn/block_sparse_attention.py:27-343, and the same factory
+``create_block_sparse_attention(config)`` (:346-368), so ``TitanBlock`` can pick it for
+``use_block_sparse=True`` like the reference does (titans_core/blocks/titan_block.py:51-64).
+
+What the reference does in Python — three transposed Conv1d calls, then a loop over query blocks
+that concatenates each block's keys, builds a mask and runs a softmax — is two launches here:
+``tmw_causal_dwconv`` over the whole QKV projection output (the three filters stacked) and
+``tmw_prefill_block_sparse`` reading Q, K, V as strided views of the result.
+
+Not supported (raises ``NotImplementedError``): ``causal=False``, dropout in training mode, autograd
+through the module.  Like the reference, a caller-supplied ``attn_mask`` is ignored (:218-219).
+The ring-cache generation path of ``TitanMAC`` belongs to ``WindowedAttention`` only.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import _native
+
+
+class BlockSparseAttention(nn.Module):
+    def __init__(self, d_model: int, n_heads: int, window_size: int = 512, block_size: int = 64,
+                 n_persistent: int = 0, dropout: float = 0.0, causal: bool = True, use_conv: bool = True,
+                 conv_kernel: int = 4):
+        super().__init__()
+        if d_model % n_heads != 0:
+            raise ValueError(f"d_model ({d_model}) must be divisible by n_heads ({n_heads})")
+        self.d_model, self.n_heads, self.d_head = d_model, n_heads, d_model // n_heads
+        self.window_size, self.block_size, self.n_persistent = window_size, block_size, n_persistent
+        self.dropout_p, self.causal, self.use_conv = dropout, causal, use_conv
+        self.qkv_proj = nn.Linear(d_model, 3 * d_model, bias=False)
+        if use_conv:
+            mk = lambda: nn.Conv1d(d_model, d_model, kernel_size=conv_kernel, padding=conv_kernel - 1,  # noqa: E731
+                                   groups=d_model, bias=False)
+            self.conv_q, self.conv_k, self.conv_v = mk(), mk(), mk()
+        self.out_proj = nn.Linear(d_model, d_model, bias=False)
+        self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
+        self.scale = 1.0 / math.sqrt(self.d_head)
+        self.algo = _native.ALGO_AUTO   # tmw_algo passed to the library (tests pin a kernel)
+        self.core_events = None         # see WindowedAttention.core_events
+
+    def stacked_conv_weight(self) -> torch.Tensor:
+        """``[3 * d_model, taps]``: the three depthwise filters in the channel order of the QKV projection."""
+        return torch.cat([self.conv_q.weight[:, 0], self.conv_k.weight[:, 0], self.conv_v.weight[:, 0]], dim=0)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if not self.causal:
+            raise NotImplementedError("causal=False is not supported")
+        if self.training and self.dropout_p > 0:
+            raise NotImplementedError("attention dropout in training mode is not supported")
+        if not x.is_cuda:
+            raise RuntimeError("BlockSparseAttention (B200) needs CUDA tensors; there is no CPU path")
+        B, L, D = x.shape
+        if self.n_persistent >= L:
+            raise ValueError(f"n_persistent ({self.n_persistent}) must be < seq_len ({L})")
+        qkv = self.qkv_proj(x)
+        if self.use_conv:
+            qkv = _native.causal_dwconv(qkv, self.stacked_conv_weight())
+        v5 = qkv.view(B, L, 3, self.n_heads, self.d_head)
+        q, k, v = (v5[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        o = torch.empty((B, L, self.n_heads, self.d_head), dtype=qkv.dtype, device=qkv.device)
+        if self.core_events is not None:
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+        _native.prefill(q, k, v, self.window_size, self.n_persistent, out=o.permute(0, 2, 1, 3), scale=self.scale,
+                        algo=self.algo, window_block=self.block_size)
+        if self.core_events is not None:
+            end.record()
+            self.core_events.append((start, end))
+        return self.dropout(self.out_proj(o.view(B, L, D)))
+
+
+def create_block_sparse_attention(config) -> BlockSparseAttention:
+    """From a ``TitanMACConfig``; block size ``config.block_size`` if present, else ``max(64, window_size // 8)``
+    (block_sparse_attention.py:356-368)."""
+    block_size = getattr(config, "block_size", max(64, config.window_size // 8))
+    return BlockSparseAttention(d_model=config.d_model, n_heads=config.n_heads, window_size=config.window_size,
+                                block_size=block_size, n_persistent=config.n_persistent,
+                                dropout=config.attention_dropout, causal=config.causal)

@@ -4,9 +4,8 @@ Mirrors titans_core/blocks/titan_block.py:41-102, blocks/norms.py:39-60 and
 blocks/mlp.py:28-67 of the reference (same submodule names, so checkpoints load
 unchanged).  The attention is this package's own code, and so is the element-wise work around
 it on a GPU: RMSNorm with the preceding residual add folded in is one kernel
-(``tmw_add_rmsnorm``) and the exact GELU is another (``tmw_gelu``); the linears stay library calls.  The reference's
-default ``use_block_sparse=True`` selects a different attention class with different math,
-which this package does not provide: it is refused here instead of being silently replaced.
+(``tmw_add_rmsnorm``) and the exact GELU is another (``tmw_gelu``); the linears stay library calls.
+``use_block_sparse`` selects the attention class exactly as in the reference.
 The package is forward-only; an input that carries a gradient takes the plain PyTorch norm.
 """
 
@@ -18,6 +17,7 @@ import torch
 import torch.nn as nn
 
 from .. import _native
+from ..attn.block_sparse_attention import BlockSparseAttention
 from ..attn.windowed_attention import WindowedAttention
 
 
@@ -69,15 +69,16 @@ class TitanBlock(nn.Module):
 
     def __init__(self, config):
         super().__init__()
-        if getattr(config, "use_block_sparse", False):
-            raise NotImplementedError(
-                "use_block_sparse=True selects the reference's BlockSparseAttention, which is different math "
-                "and not part of this package; build the config with use_block_sparse=False"
-            )
         self.config = config
         self.norm_attn = RMSNorm(config.d_model, eps=config.norm_eps)
         self.norm_mlp = RMSNorm(config.d_model, eps=config.norm_eps)
-        self.attention = WindowedAttention(config)
+        if getattr(config, "use_block_sparse", False):  # same switch as titan_block.py:51-64
+            self.attention = BlockSparseAttention(
+                d_model=config.d_model, n_heads=config.n_heads, window_size=config.window_size,
+                block_size=getattr(config, "block_size", 64), n_persistent=config.n_persistent,
+                dropout=config.attention_dropout, causal=config.causal)
+        else:
+            self.attention = WindowedAttention(config)
         self.mlp = MLPBlock(d_model=config.d_model, d_ff=config.d_ff, dropout=config.dropout)
 
     def forward(self, x: torch.Tensor, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:

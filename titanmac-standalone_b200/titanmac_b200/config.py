@@ -35,10 +35,10 @@ class TitanMACConfig:
     max_seq_len: int = 4096
     window_size: int = 512
     n_persistent: int = 16
-    # The reference defaults this to True, which selects a different attention class
-    # (block-sparse, other math).  This package implements the windowed module only,
-    # so the default here is False and True is refused where the block is built.
-    use_block_sparse: bool = False
+    # As in the reference (titans_core/config.py:91-92): True selects BlockSparseAttention (depthwise
+    # convolutions on Q/K/V, block-granular window, global persistent rows), False WindowedAttention.
+    # The ring-cache generation path (TitanMAC.prefill / decode_step / generate) needs False.
+    use_block_sparse: bool = True
     block_size: int = 64
     dropout: float = 0.0
     tie_weights: bool = True

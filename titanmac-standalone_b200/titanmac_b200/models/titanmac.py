@@ -96,7 +96,14 @@ class TitanMAC(nn.Module):
         return out
 
     # --------------------------------------------------------------- generation --
+    def _need_windowed(self) -> None:
+        if getattr(self.config, "use_block_sparse", False):
+            raise NotImplementedError(
+                "the ring-cache generation path (prefill / decode_step / generate) is built for WindowedAttention; "
+                "build the config with use_block_sparse=False (forward() works with either attention class)")
+
     def new_caches(self, batch: int, device, dtype) -> List[_native.RingCache]:
+        self._need_windowed()
         c = self.config
         return [_native.RingCache(batch, c.n_heads, c.d_head, c.window_size, c.n_persistent, dtype, device)
                 for _ in self.layers]
@@ -104,6 +111,7 @@ class TitanMAC(nn.Module):
     @torch.no_grad()
     def prefill(self, input_ids: torch.Tensor, caches: Optional[List[_native.RingCache]] = None):
         """Run the prompt ``[B, T]`` once; returns (logits of the last prompt token ``[B, V]``, caches)."""
+        self._need_windowed()
         B, T = input_ids.shape
         Np = self.config.n_persistent
         x = self._embed(input_ids)
@@ -137,6 +145,7 @@ class TitanMAC(nn.Module):
     def decode_step(self, token_ids: torch.Tensor, pos: torch.Tensor, caches: List[_native.RingCache]) -> torch.Tensor:
         """One new token per sequence.  ``token_ids [B]``, ``pos [B] int32`` = its index in the sequence
         (the prompt occupied 0..T-1).  Returns logits ``[B, V]``; ``pos`` is not modified."""
+        self._need_windowed()
         c = self.config
         B = token_ids.shape[0]
         x = self.embed_tokens(token_ids) + self.embed_positions(pos.long())
