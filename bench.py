@@ -50,6 +50,10 @@ WORKLOADS = {
     # (256 sequences sharded over the GPUs), prompt 2048 tokens, then `--steps` single-token steps
     "config4_decode": dict(batch=256, T=2048, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
                            layers=16, d_ff=2560, vocab=50000),
+    # config 2's layer with the reference's DEFAULT attention class (block-sparse: depthwise convolutions on
+    # Q/K/V, block-granular window, global persistent rows), block = max(64, window // 8) = 64
+    "config2_block_sparse_layer_prefill": dict(batch=8, T=4096, d_model=640, heads=10, window=512, n_persistent=16,
+                                               dtype="bf16", block_size=64, conv_taps=4),
     # BASELINE config 3: whole 16-layer model forward (prefill), 2 sequences of 8192 tokens per GPU
     "config3_model_prefill": dict(batch=2, T=8192, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
                                   layers=16, d_ff=2560, vocab=50000),
@@ -73,9 +77,15 @@ def layer_flops(wl: dict) -> dict:
     B, D, H = wl["batch"], wl["d_model"], wl["heads"]
     L = wl["n_persistent"] + wl["T"]
     dh = D // H
-    core = B * H * live_pairs(L, wl["window"], wl["n_persistent"]) * 4 * dh
     qkv = 2 * B * L * D * 3 * D
     out = 2 * B * L * D * D
+    if "block_size" in wl:
+        from oracle import block_sparse_oracle as bo  # pair count only
+
+        core = B * H * bo.live_pairs(L, wl["window"], wl["block_size"], wl["n_persistent"]) * 4 * dh
+        conv = 2 * wl["conv_taps"] * B * L * 3 * D
+        return dict(core=core, qkv=qkv, out=out, conv=conv, total=core + qkv + out + conv)
+    core = B * H * live_pairs(L, wl["window"], wl["n_persistent"]) * 4 * dh
     return dict(core=core, qkv=qkv, out=out, total=core + qkv + out)
 
 
@@ -164,6 +174,12 @@ def physical_gpu_index(local_index: int) -> int:
 # --------------------------------------------------------------------------------------
 
 
+def block_sparse_conv_weights(wl: dict, seed: int):
+    """Seeded depthwise filters ``[D, taps]`` for Q, K and V (N(0, 0.3), CPU generator)."""
+    g = torch.Generator(device="cpu").manual_seed(1000 + seed)
+    return [torch.randn(wl["d_model"], wl["conv_taps"], generator=g) * 0.3 for _ in range(3)]
+
+
 def cpu_reference_sample(wl: dict, iters: int, warmup: int = 1):
     """Times the oracle port on ONE batch element of the workload, fp32 like the reference's default.
 
@@ -174,17 +190,31 @@ def cpu_reference_sample(wl: dict, iters: int, warmup: int = 1):
     torch.set_num_threads(os.cpu_count() or 1)
     one = dict(wl, batch=1)
     x, w_qkv, w_out = wo.layer_inputs(1, wl["T"], wl["d_model"], wl["n_persistent"], seed=0)
-    cache = {}
-    for _ in range(warmup):  # builds and caches the dense boolean mask like the reference's first call
-        wo.module_forward_reference_cost(x, w_qkv, w_out, wl["heads"], wl["window"], wl["n_persistent"], cache)
+    if "block_size" in wl:
+        from oracle import block_sparse_oracle as bo
+
+        convs = block_sparse_conv_weights(wl, seed=0)
+
+        def forward():
+            bo.module_forward_reference_cost(x, w_qkv, *convs, w_out, wl["heads"], wl["window"], wl["block_size"],
+                                             wl["n_persistent"])
+        how = "library depthwise convolutions + Python loop over query blocks like the reference"
+    else:
+        cache = {}
+
+        def forward():  # builds and caches the dense boolean mask like the reference's first call
+            wo.module_forward_reference_cost(x, w_qkv, w_out, wl["heads"], wl["window"], wl["n_persistent"], cache)
+        how = "dense mask + library attention like the reference"
+    for _ in range(warmup):
+        forward()
     times = []
     for _ in range(iters):
         t0 = time.perf_counter()
-        wo.module_forward_reference_cost(x, w_qkv, w_out, wl["heads"], wl["window"], wl["n_persistent"], cache)
+        forward()
         times.append(time.perf_counter() - t0)
     sec = statistics.median(times)
-    desc = (f"1 of {wl['batch']} batch elements (L={wl['n_persistent'] + wl['T']}), fp32, dense mask + library "
-            f"attention like the reference, median of {iters} after {warmup} warm-up (mask build excluded)")
+    desc = (f"1 of {wl['batch']} batch elements (L={wl['n_persistent'] + wl['T']}), fp32, {how}, "
+            f"median of {iters} after {warmup} warm-up (mask build excluded)")
     return sec, layer_flops(one)["total"], torch.get_num_threads(), desc
 
 
@@ -233,7 +263,16 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
     B, T, D, H, w, Np = wl["batch"], wl["T"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
     L = Np + T
     x_cpu, w_qkv, w_out = wo.layer_inputs(B, T, D, Np, seed=rank)
-    mod = WindowedAttention(WindowConfig(window_size=w, num_heads=H, head_dim=D // H, n_persistent=Np)).eval()
+    if "block_size" in wl:
+        from titanmac_b200 import BlockSparseAttention
+
+        mod = BlockSparseAttention(d_model=D, n_heads=H, window_size=w, block_size=wl["block_size"], n_persistent=Np,
+                                   conv_kernel=wl["conv_taps"]).eval()
+        with torch.no_grad():
+            for conv, wt in zip((mod.conv_q, mod.conv_k, mod.conv_v), block_sparse_conv_weights(wl, seed=rank)):
+                conv.weight.copy_(wt[:, None, :])
+    else:
+        mod = WindowedAttention(WindowConfig(window_size=w, num_heads=H, head_dim=D // H, n_persistent=Np)).eval()
     with torch.no_grad():
         mod.qkv_proj.weight.copy_(w_qkv)
         mod.out_proj.weight.copy_(w_out)
@@ -316,7 +355,8 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
             "config": dict(workload=wl_name, **wl, global_batch=B * world, parallelism=f"batch-sharded x{world}",
                            l2="inputs rotate over 4 sets; x+qkv+o per step = 210 MB > 126 MB L2",
                            flops_per_step_per_gpu=flops),
-            "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill)", "achieved": achieved,
+            "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill_block_sparse)"
+                         if "block_size" in wl else "attention core (tmw_prefill)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16 burst", "avg_launch_ms": core_avg_ms,
                          "traffic": NCU_TRAFFIC_BYTES.get(wl_name),
@@ -325,7 +365,7 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
                     "d2h_bytes_per_step": y_hosts[0].numel() * y_hosts[0].element_size(), "steps": e2e_steps,
                     "ms_per_step": e2e_ms / e2e_steps,
                     "how": "HostPipeline: H2D copy, forward and D2H copy of consecutive steps overlap on 3 streams"},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * (3 if "block_size" in wl else 1),
             "clocks": clocks.report(),
         }
         if world == 1:

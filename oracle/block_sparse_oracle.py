@@ -75,3 +75,49 @@ def module_forward(x: torch.Tensor, w_qkv: torch.Tensor, conv_q: torch.Tensor, c
     o = attention_core(heads(q), heads(k), heads(v), window, block_size, n_persistent)
     y = o.transpose(1, 2).reshape(B, L, D) @ w_out.float().t()
     return (y, q, k, v, o) if return_parts else y
+
+
+def live_pairs(seq_len: int, window: int, block_size: int, n_persistent: int) -> int:
+    """Visible (query, key) pairs per (batch, head): the algorithmic work of the attention core."""
+    Np, T = n_persistent, seq_len - n_persistent
+    pairs = Np * seq_len + T * Np
+    for t0 in range(0, T, block_size):
+        lo = max(0, t0 - window)
+        n = min(block_size, T - t0)
+        pairs += n * (t0 - lo) + n * (n + 1) // 2
+    return pairs
+
+
+def module_forward_reference_cost(x: torch.Tensor, w_qkv: torch.Tensor, conv_q: torch.Tensor, conv_k: torch.Tensor,
+                                  conv_v: torch.Tensor, w_out: torch.Tensor, n_heads: int, window: int,
+                                  block_size: int, n_persistent: int) -> torch.Tensor:
+    """The forward with the same cost structure as the reference on CPU (the timed CPU baseline only):
+    library depthwise Conv1d calls on transposed tensors (block_sparse_attention.py:241-256), dense
+    attention of the persistent rows over every key (:283-291), then a Python loop over query blocks that
+    concatenates the block's keys, builds its mask and runs matmul / softmax / matmul (:294-343)."""
+    import torch.nn.functional as F
+
+    B, L, D = x.shape
+    Np, dh, K = n_persistent, D // n_heads, conv_q.shape[1]
+    qkv = F.linear(x, w_qkv)
+    parts = []
+    for t, w in zip(qkv.chunk(3, dim=-1), (conv_q, conv_k, conv_v)):
+        y = F.conv1d(t.transpose(1, 2), w[:, None, :].to(t.dtype), padding=K - 1, groups=D)[:, :, :L]
+        parts.append(y.transpose(1, 2).reshape(B, L, n_heads, dh).transpose(1, 2))
+    q, k, v = parts
+    scale = 1.0 / math.sqrt(dh)
+    out = torch.empty(B, n_heads, L, dh, dtype=x.dtype)
+    if Np > 0:
+        s = torch.matmul(q[:, :, :Np], k.transpose(-2, -1)) * scale
+        out[:, :, :Np] = torch.matmul(F.softmax(s, dim=-1), v)
+    T = L - Np
+    for b0 in range(0, T, block_size):
+        b1 = min(b0 + block_size, T)
+        c0 = max(0, b0 - window)
+        kc = torch.cat([k[:, :, :Np], k[:, :, Np + c0:Np + b1]], dim=2)
+        vc = torch.cat([v[:, :, :Np], v[:, :, Np + c0:Np + b1]], dim=2)
+        m = torch.ones(b1 - b0, Np + b1 - c0, dtype=torch.bool)
+        m[:, Np:] = torch.arange(b0, b1)[:, None] >= torch.arange(c0, b1)[None, :]
+        s = (torch.matmul(q[:, :, Np + b0:Np + b1], kc.transpose(-2, -1)) * scale).masked_fill(~m, float("-inf"))
+        out[:, :, Np + b0:Np + b1] = torch.matmul(F.softmax(s, dim=-1), vc)
+    return F.linear(out.transpose(1, 2).reshape(B, L, D), w_out)

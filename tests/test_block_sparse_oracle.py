@@ -59,3 +59,14 @@ def test_mask_properties():
     assert counts[0] == 1 and counts.max() == 16 + 8    # between w + 1 and w + block_size keys once filled
     assert (counts[24:] >= 17).all()
     assert bo.first_visible_key(23, 16, 8) == 0 and bo.first_visible_key(24, 16, 8) == 8
+
+
+def test_cost_faithful_restatement_and_pair_count_agree_with_the_oracle(bs_golden):
+    for name in cases(bs_golden):
+        c = load_case(bs_golden, name)
+        sd = c["sd"]
+        args = (c["x"], sd["qkv_proj.weight"], sd["conv_q.weight"][:, 0], sd["conv_k.weight"][:, 0],
+                sd["conv_v.weight"][:, 0], sd["out_proj.weight"], c["H"], c["w"], c["bs"], c["Np"])
+        assert (bo.module_forward_reference_cost(*args) - c["y"]).abs().max().item() <= 2e-6, name
+        L = c["Np"] + c["T"]
+        assert bo.live_pairs(L, c["w"], c["bs"], c["Np"]) == int(bo.mask(L, c["w"], c["bs"], c["Np"]).sum()), name

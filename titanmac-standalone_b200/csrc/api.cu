@@ -172,9 +172,11 @@ int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block_size, c
     int st = (d.algo != TMW_ALGO_SIMT && tc_ok) ? tmw::launch_prefill_tc(d, q, k, v, o, s, block_size)
                                                 : tmw::launch_prefill_simt(d, q, k, v, o, s, block_size, false);
     if (st != TMW_OK || d.n_persistent == 0) return st;
-    // ... then the persistent query rows again, this time seeing every key (a few rows: CUDA-core kernel)
+    // ... then the persistent query rows again, this time seeing every key: one query tile per (batch, head)
+    // that walks over all key tiles
     d.q_rows = d.n_persistent;
-    return tmw::launch_prefill_simt(d, q, k, v, o, s, block_size, true);
+    return (d.algo != TMW_ALGO_SIMT && tc_ok) ? tmw::launch_prefill_tc(d, q, k, v, o, s, block_size, true)
+                                              : tmw::launch_prefill_simt(d, q, k, v, o, s, block_size, true);
 }
 
 size_t tmw_cache_ring_bytes(int32_t dtype, int32_t batch, int32_t heads, int32_t head_dim, int32_t window) {

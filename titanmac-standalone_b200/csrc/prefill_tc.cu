@@ -99,6 +99,7 @@ struct TcParams {
     int q_rows, k_rows, window, np, np_pad, q_pos0, k_pos0;
     int block;        // 0 or the block size of the block-granular window (first_visible_pos)
     int window_plan;  // window + block - 1: the widest window any row can have, used to lay out the key tiles
+    int all_keys;     // 1: every query row of the call sees every key row, unmasked
     int dim_order;  // bit i set: tensor i (0=q,1=k,2=v,3=o) has its head axis before its row axis in the map
     float scale_log2;
     int* status;
@@ -333,7 +334,15 @@ __device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block, int t
         q.rows = t < tiles ? max(0, min(BM, p.q_rows - (r0 + t * BM))) : 0;
         q.has_pers = (q.rows > 0 && p.np > 0) ? 1 : 0;
         const int p_hi = q.p_lo + q.rows - 1;
-        if (q.rows > 0 && p_hi >= p.np) {
+        if (p.all_keys) {
+            c.anchor = p.k_pos0;  // key tile x starts at key row np + x * BN
+            q.a = 0;
+            q.n_win = q.rows > 0 ? (p.k_rows - p.np + BN - 1) / BN : 0;
+            if (q.rows > 0) {
+                c.x_begin = 0;
+                c.x_end = max(c.x_end, q.n_win);
+            }
+        } else if (q.rows > 0 && p_hi >= p.np) {
             const int g_lo = first_visible_pos(max(q.p_lo, p.np), p.np, p.window, p.block);
             q.a = floor_div(g_lo - c.anchor, BN);
             q.n_win = floor_div(p_hi - c.anchor, BN) - q.a + 1;
@@ -687,7 +696,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 full = false;
             } else {
                 const int g0 = plan.anchor + (q.a + item - q.has_pers) * BN;
-                if (pos >= p.np) {
+                if (p.all_keys) {
+                    j_lo = 0;
+                    j_hi = p.k_pos0 + (p.k_rows - p.np) - 1 - g0;  // the last key row that exists
+                } else if (pos >= p.np) {
                     j_lo = first_visible_pos(pos, p.np, p.window, p.block) - g0;
                     j_hi = pos - g0;
                 } else {
@@ -696,8 +708,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 ncols = BN;
                 // every row of the tile sees every key of the tile (decided per tile, not per row)
-                full = q.p_lo >= p.np && g0 >= p.np && g0 + BN - 1 <= q.p_lo &&
-                       g0 >= first_visible_pos(q.p_lo + BM - 1, p.np, p.window, p.block);
+                full = p.all_keys ? j_hi >= BN - 1
+                                  : q.p_lo >= p.np && g0 >= p.np && g0 + BN - 1 <= q.p_lo &&
+                                        g0 >= first_visible_pos(q.p_lo + BM - 1, p.np, p.window, p.block);
             }
             const int nchunks = (ncols + 31) / 32;
             // 32-column chunks in which no row of this warp sees a key (beyond the diagonal, or before the
@@ -978,7 +991,7 @@ int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
 
 template <int DH, int KS, int VS, int TILES>
 int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream,
-              int window_block) {
+              int window_block, bool all_keys) {
     using L = TcSmem<DH, KS, VS, TILES>;
     const int np_pad = np_pad_of(d.n_persistent);
     CUtensorMap mq, mk, mv, mo, mkp, mvp;
@@ -994,6 +1007,7 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     p.q_rows = d.q_rows; p.k_rows = d.k_rows; p.window = d.window; p.np = d.n_persistent; p.np_pad = np_pad;
     p.block = window_block;
     p.window_plan = d.window + (window_block > 0 ? window_block - 1 : 0);
+    p.all_keys = all_keys ? 1 : 0;
     p.q_pos0 = d.q_pos0; p.k_pos0 = d.k_pos0;
     p.dim_order = (hf[0] ? 1 : 0) | (hf[1] ? 2 : 0) | (hf[2] ? 4 : 0) | (hf[3] ? 8 : 0);
     const float scale = d.scale != 0.f ? d.scale : 1.0f / sqrtf((float)DH);
@@ -1044,16 +1058,16 @@ bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, co
 }
 
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                      cudaStream_t stream, int window_block) {
+                      cudaStream_t stream, int window_block, bool all_keys) {
     if (d.head_dim == 64) {
         // One query tile per CTA and two CTAs per SM when two such CTAs fit into shared memory (they do
         // unless there are many persistent keys): independent CTAs drift apart, so one CTA's exponentials,
         // start-up and output phase overlap the other's matrix products.
         if (TMW_TILES64 == 1 && TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem)
-            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block);
-        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block);
+            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block, all_keys);
+        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block, all_keys);
     }
-    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream, window_block);
+    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream, window_block, all_keys);
 }
 
 }  // namespace tmw

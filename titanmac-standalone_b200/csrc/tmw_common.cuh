@@ -126,7 +126,7 @@ int validate_decode_call(const tmw_cache_desc* cache, const void* q, const void*
 int launch_prefill_simt(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
                         cudaStream_t stream, int window_block = 0, bool all_keys = false);
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                      cudaStream_t stream, int window_block = 0);
+                      cudaStream_t stream, int window_block = 0, bool all_keys = false);
 bool prefill_tc_supports(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o);
 int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, const void* v_new, void* o,
                   const int64_t qs[2], const int64_t ns[2], const int64_t os[2], const int32_t* pos,
