@@ -1,6 +1,7 @@
 // C-ABI entry points of libtmw: argument validation, kernel selection, error text.
 // Everything that can be rejected is rejected here, on the host, before a launch.
 #include <cstdio>
+#include <mutex>
 #include <cstring>
 
 #include "tmw_common.cuh"
@@ -33,6 +34,27 @@ int* device_status_word() {
         cache[dev] = static_cast<int*>(ptr);
     }
     return cache[dev];
+}
+
+// One side stream and two events per device, made on first use and kept for the life of the process (make
+// that first use outside stream capture).  Calls that use them are serialised on the host by `mutex`.
+SideStream* side_stream_of_current_device() {
+    constexpr int kMaxDevices = 64;
+    static SideStream table[kMaxDevices];
+    static bool ready[kMaxDevices] = {false};
+    static std::mutex init;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(init);
+    if (!ready[dev]) {
+        SideStream& t = table[dev];
+        if (cudaStreamCreateWithFlags(&t.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+        if (cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&t.join, cudaEventDisableTiming) != cudaSuccess)
+            return nullptr;
+        ready[dev] = true;
+    }
+    return &table[dev];
 }
 
 namespace {
@@ -168,15 +190,38 @@ int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block_size, c
     tmw_prefill_desc d = *desc;
     const bool tc_ok = tmw::prefill_tc_supports(d, q, k, v, o) && (int64_t)d.q_rows + d.window + block_size < ((int64_t)1 << 29);
     if (d.algo == TMW_ALGO_TCGEN05 && !tc_ok) return TMW_ERR_UNSUPPORTED;
-    // every row with the block-granular window and the persistent keys ...
-    int st = (d.algo != TMW_ALGO_SIMT && tc_ok) ? tmw::launch_prefill_tc(d, q, k, v, o, s, block_size)
-                                                : tmw::launch_prefill_simt(d, q, k, v, o, s, block_size, false);
-    if (st != TMW_OK || d.n_persistent == 0) return st;
-    // ... then the persistent query rows again, this time seeing every key: one query tile per (batch, head)
-    // that walks over all key tiles
-    d.q_rows = d.n_persistent;
-    return (d.algo != TMW_ALGO_SIMT && tc_ok) ? tmw::launch_prefill_tc(d, q, k, v, o, s, block_size, true)
-                                              : tmw::launch_prefill_simt(d, q, k, v, o, s, block_size, true);
+    const bool use_tc = d.algo != TMW_ALGO_SIMT && tc_ok;
+    auto launch = [&](const tmw_prefill_desc& dd, const void* qq, void* oo, cudaStream_t st, bool all_keys) {
+        return use_tc ? tmw::launch_prefill_tc(dd, qq, k, v, oo, st, block_size, all_keys)
+                      : tmw::launch_prefill_simt(dd, qq, k, v, oo, st, block_size, all_keys);
+    };
+    const int np = d.n_persistent;
+    if (np == 0) return launch(d, q, o, s, false);
+    // Two independent launches: the sequence rows [np, L) with the block-granular window, and the np
+    // persistent query rows, which see every key (one query tile per (batch, head) walking over all key
+    // tiles - it occupies only batch x heads CTAs for a long time).  They write different rows, so the
+    // second one runs on a side stream of the library between two events (a fork / join that stream
+    // capture accepts as well).
+    tmw_prefill_desc seq = d, pers = d;
+    const size_t esz = tmw::dtype_size(d.dtype);
+    seq.q_rows = d.q_rows - np;
+    seq.q_pos0 = np;
+    const void* q_seq = static_cast<const char*>(q) + (size_t)np * d.q_stride[2] * esz;
+    void* o_seq = static_cast<char*>(o) + (size_t)np * d.o_stride[2] * esz;
+    pers.q_rows = np;
+    tmw::SideStream* side = tmw::side_stream_of_current_device();
+    if (side == nullptr) {  // no side stream: one after the other
+        const int st = launch(seq, q_seq, o_seq, s, false);
+        return st != TMW_OK ? st : launch(pers, q, o, s, true);
+    }
+    std::lock_guard<std::mutex> lock(side->mutex);
+    TMW_CUDA_TRY(cudaEventRecord(side->fork, s));
+    TMW_CUDA_TRY(cudaStreamWaitEvent(side->stream, side->fork, 0));
+    int st = launch(pers, q, o, side->stream, true);
+    TMW_CUDA_TRY(cudaEventRecord(side->join, side->stream));
+    const int st2 = launch(seq, q_seq, o_seq, s, false);
+    TMW_CUDA_TRY(cudaStreamWaitEvent(s, side->join, 0));
+    return st != TMW_OK ? st : st2;
 }
 
 size_t tmw_cache_ring_bytes(int32_t dtype, int32_t batch, int32_t heads, int32_t head_dim, int32_t window) {

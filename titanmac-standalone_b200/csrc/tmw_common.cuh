@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "tmw.h"
 
 namespace tmw {
@@ -105,6 +107,14 @@ __host__ __device__ inline int first_visible_pos(int pos, int np, int window, in
 void set_cuda_error(cudaError_t e, const char* where);
 void set_error_text(const char* text);
 int* device_status_word();  // per-device int in global memory, 0 = fine
+
+// a library-owned stream for work that may overlap the caller's stream, with the events of the fork / join
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    std::mutex mutex;
+};
+SideStream* side_stream_of_current_device();  // nullptr if it cannot be made
 
 #define TMW_CUDA_TRY(expr)                                   \
     do {                                                     \
