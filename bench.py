@@ -757,6 +757,7 @@ def main() -> None:
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="config2_layer_prefill")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1 only)")
     args = ap.parse_args()
+    torch.set_grad_enabled(False)  # inference workloads: nothing is saved for a backward pass
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

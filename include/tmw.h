@@ -91,6 +91,25 @@ TMW_API int tmw_prefill(const tmw_prefill_desc* desc, const void* q, const void*
                 void* stream);
 
 /*
+ * tmw_prefill that also returns, per query row, the log-sum-exp of its scores: lse[batch, heads, q_rows]
+ * (fp32, contiguous) holds log2(sum_j exp2(s_ij * scale * log2 e)) over the visible keys - the one number
+ * per row from which the backward pass rebuilds the probabilities.
+ */
+TMW_API int tmw_prefill_lse(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v, void* o,
+                            float* lse, void* stream);
+
+/*
+ * Backward of tmw_prefill for whole sequences (q_pos0 = 0, k_pos0 = n_persistent, q_rows = k_rows):
+ * given d_o (gradient of o, addressed like o) and the o and lse of tmw_prefill_lse, writes dq, dk, dv
+ * (addressed like q, k, v: the same strides).  Replaces what autograd does through the reference's mask
+ * conversion and scaled-dot-product call (windowed_attention.py:307-323) - there over all L x L pairs,
+ * here over the visible pairs only.  fp32 arithmetic on CUDA cores for every dtype.
+ */
+TMW_API int tmw_prefill_backward(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v,
+                                 const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
+                                 void* stream);
+
+/*
  * Prefill with the mask of the reference's BlockSparseAttention (its default attention class,
  * titans_core/attn/block_sparse_attention.py:258-343), for whole sequences (q_pos0 = 0,
  * k_pos0 = n_persistent, q_rows = k_rows = L; desc->window is its window_size):

@@ -173,6 +173,34 @@ int tmw_prefill(const tmw_prefill_desc* desc, const void* q, const void* k, cons
     return tmw::launch_prefill_simt(*desc, q, k, v, o, s);
 }
 
+int tmw_prefill_lse(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v, void* o, float* lse,
+                    void* stream) {
+    const int rc = tmw::validate_prefill(desc, q, k, v, o);
+    if (rc != TMW_OK) return rc;
+    if (desc->batch == 0 || desc->heads == 0 || desc->q_rows == 0) return TMW_OK;
+    if (lse == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool tc_ok = tmw::prefill_tc_supports(*desc, q, k, v, o);
+    if (desc->algo == TMW_ALGO_TCGEN05 && !tc_ok) return TMW_ERR_UNSUPPORTED;
+    if (desc->algo != TMW_ALGO_SIMT && tc_ok) return tmw::launch_prefill_tc(*desc, q, k, v, o, s, 0, false, lse);
+    return tmw::launch_prefill_simt(*desc, q, k, v, o, s, 0, false, lse);
+}
+
+int tmw_prefill_backward(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v, const void* o,
+                         const void* d_o, const float* lse, void* dq, void* dk, void* dv, void* stream) {
+    const int rc = tmw::validate_prefill(desc, q, k, v, o);
+    if (rc != TMW_OK) return rc;
+    if (desc->q_pos0 != 0 || desc->k_pos0 != desc->n_persistent || desc->q_rows != desc->k_rows) {
+        tmw::set_error_text("tmw_prefill_backward: whole sequences only (q_pos0 = 0, k_pos0 = n_persistent, q_rows = k_rows)");
+        return TMW_ERR_UNSUPPORTED;
+    }
+    if (desc->batch == 0 || desc->heads == 0 || desc->q_rows == 0) return TMW_OK;
+    if (d_o == nullptr || lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (!tmw::aligned16(d_o) || !tmw::aligned16(dq) || !tmw::aligned16(dk) || !tmw::aligned16(dv))
+        return TMW_ERR_INVALID_ARGUMENT;
+    return tmw::launch_prefill_backward(*desc, q, k, v, o, d_o, lse, dq, dk, dv, static_cast<cudaStream_t>(stream));
+}
+
 int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block_size, const void* q, const void* k,
                              const void* v, void* o, void* stream) {
     const int rc = tmw::validate_prefill(desc, q, k, v, o);

@@ -40,6 +40,7 @@ struct SimtParams {
     int all_keys;  // 1: no mask at all, every key row is visible to every query row of the call
     long long qs[3], ks[3], vs[3], os[3];
     float scale_log2;  // scale * log2(e)
+    float* lse;        // optional [batch, heads, q_rows]: m + log2(l) of every row (log2 domain)
 };
 
 template <typename T, int DH>
@@ -170,6 +171,8 @@ __global__ void __launch_bounds__(kThreads) prefill_simt_kernel(const SimtParams
         }
     }
 
+    if (valid && sub == 0 && p.lse != nullptr)
+        p.lse[((long long)b * gridDim.y + h) * p.q_rows + row] = m + log2f(l);
     if (valid) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -209,8 +212,9 @@ int launch_dh(const SimtParams& p, int batch, int heads, int dh, cudaStream_t st
 }  // namespace
 
 int launch_prefill_simt(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                        cudaStream_t stream, int window_block, bool all_keys) {
+                        cudaStream_t stream, int window_block, bool all_keys, float* lse) {
     SimtParams p;
+    p.lse = lse;
     p.block = window_block;
     p.all_keys = all_keys ? 1 : 0;
     p.q = q; p.k = k; p.v = v; p.o = o;

@@ -103,6 +103,7 @@ struct TcParams {
     int dim_order;  // bit i set: tensor i (0=q,1=k,2=v,3=o) has its head axis before its row axis in the map
     float scale_log2;
     int* status;
+    float* lse;  // optional [batch, heads, q_rows]: log2 of the row's softmax denominator, in the scaled-by-log2(e) domain
 };
 
 // ---------------------------------------------------------------------------------
@@ -871,6 +872,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tc_fence_after();
             TRACE(1 + t * 4 + ((warp & 3) ? 2000 : 0));
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+            if (p.lse != nullptr && row < q.rows)
+                p.lse[((long long)batch * gridDim.y + head) * p.q_rows + (blockIdx.x * TILES + t) * BM + row] =
+                    m_used + log2f(l_sum);
             uint8_t* stage = smem + L::kQ + t * L::kTileBytes;  // the Q tile is no longer needed
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
@@ -991,7 +995,7 @@ int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
 
 template <int DH, int KS, int VS, int TILES>
 int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream,
-              int window_block, bool all_keys) {
+              int window_block, bool all_keys, float* lse) {
     using L = TcSmem<DH, KS, VS, TILES>;
     const int np_pad = np_pad_of(d.n_persistent);
     CUtensorMap mq, mk, mv, mo, mkp, mvp;
@@ -1008,6 +1012,7 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     p.block = window_block;
     p.window_plan = d.window + (window_block > 0 ? window_block - 1 : 0);
     p.all_keys = all_keys ? 1 : 0;
+    p.lse = lse;
     p.q_pos0 = d.q_pos0; p.k_pos0 = d.k_pos0;
     p.dim_order = (hf[0] ? 1 : 0) | (hf[1] ? 2 : 0) | (hf[2] ? 4 : 0) | (hf[3] ? 8 : 0);
     const float scale = d.scale != 0.f ? d.scale : 1.0f / sqrtf((float)DH);
@@ -1058,16 +1063,16 @@ bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, co
 }
 
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                      cudaStream_t stream, int window_block, bool all_keys) {
+                      cudaStream_t stream, int window_block, bool all_keys, float* lse) {
     if (d.head_dim == 64) {
         // One query tile per CTA and two CTAs per SM when two such CTAs fit into shared memory (they do
         // unless there are many persistent keys): independent CTAs drift apart, so one CTA's exponentials,
         // start-up and output phase overlap the other's matrix products.
         if (TMW_TILES64 == 1 && TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem)
-            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block, all_keys);
-        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block, all_keys);
+            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block, all_keys, lse);
+        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block, all_keys, lse);
     }
-    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream, window_block, all_keys);
+    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream, window_block, all_keys, lse);
 }
 
 }  // namespace tmw

@@ -133,10 +133,14 @@ int validate_decode_call(const tmw_cache_desc* cache, const void* q, const void*
 // Kernel launchers (one per translation unit).
 // window_block: 0 = per-token window, > 0 = block-granular left edge (see first_visible_pos);
 // all_keys: every query row of the call sees every key, unmasked (the persistent rows of the block-sparse class)
+// lse (optional): [batch, heads, q_rows] fp32, log2 of every row's softmax denominator in the domain of
+// score * scale * log2(e) - what the backward pass needs to rebuild the probabilities
 int launch_prefill_simt(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                        cudaStream_t stream, int window_block = 0, bool all_keys = false);
+                        cudaStream_t stream, int window_block = 0, bool all_keys = false, float* lse = nullptr);
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                      cudaStream_t stream, int window_block = 0, bool all_keys = false);
+                      cudaStream_t stream, int window_block = 0, bool all_keys = false, float* lse = nullptr);
+int launch_prefill_backward(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
+                            const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream);
 bool prefill_tc_supports(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o);
 int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, const void* v_new, void* o,
                   const int64_t qs[2], const int64_t ns[2], const int64_t os[2], const int32_t* pos,

@@ -90,6 +90,14 @@ SIGNATURES = {
         [ctypes.POINTER(PrefillDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
          ctypes.c_void_p],
     ),
+    "tmw_prefill_lse": (
+        ctypes.c_int,
+        [ctypes.POINTER(PrefillDesc)] + [ctypes.c_void_p] * 6,
+    ),
+    "tmw_prefill_backward": (
+        ctypes.c_int,
+        [ctypes.POINTER(PrefillDesc)] + [ctypes.c_void_p] * 10,
+    ),
     "tmw_prefill_block_sparse": (
         ctypes.c_int,
         [ctypes.POINTER(PrefillDesc), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
@@ -195,11 +203,13 @@ def prefill(
     scale: float = 0.0,
     algo: int = ALGO_AUTO,
     window_block: int = 0,
+    lse: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """``tmw_prefill`` on ``[B, H, rows, dh]`` tensors (any strides with a contiguous last axis).
 
     ``window_block > 0`` selects ``tmw_prefill_block_sparse``: the mask of the reference's
-    BlockSparseAttention with that block size (whole sequences only)."""
+    BlockSparseAttention with that block size (whole sequences only).  ``lse`` (fp32 ``[B, H, rows]``,
+    contiguous) receives every row's log-sum-exp (``tmw_prefill_lse``), which ``prefill_backward`` needs."""
     _require_cuda(q, k, v)
     if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
         raise TypeError("q, k, v must share one dtype out of float32, bfloat16, float16")
@@ -221,13 +231,49 @@ def prefill(
     d.v_stride[:] = _bhrd_strides(v)
     d.o_stride[:] = _bhrd_strides(out)
     with torch.cuda.device(q.device):
-        if window_block > 0:
+        if lse is not None:
+            if window_block > 0:
+                raise NotImplementedError("the log-sum-exp output exists for the windowed mask only")
+            if lse.dtype != torch.float32 or lse.shape != (B, H, rq) or not lse.is_contiguous() or lse.device != q.device:
+                raise ValueError("lse must be a contiguous fp32 [B, H, rows] tensor on the same device")
+            check(lib().tmw_prefill_lse(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                        lse.data_ptr(), _stream_ptr(q.device)))
+        elif window_block > 0:
             check(lib().tmw_prefill_block_sparse(ctypes.byref(d), window_block, q.data_ptr(), k.data_ptr(),
                                                  v.data_ptr(), out.data_ptr(), _stream_ptr(q.device)))
         else:
             check(lib().tmw_prefill(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                                     _stream_ptr(q.device)))
     return out
+
+
+def prefill_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor,
+                     lse: torch.Tensor, dq: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor, window: int,
+                     n_persistent: int, scale: float = 0.0) -> None:
+    """``tmw_prefill_backward``: fills ``dq, dk, dv`` (same strides as ``q, k, v``) from ``d_o`` (same strides as
+    ``o``), the saved output and the log-sum-exp of ``prefill(..., lse=...)``.  Whole sequences only."""
+    _require_cuda(q, k, v, o, d_o, lse, dq, dk, dv)
+    B, H, L, dh = q.shape
+    for a, b_ in ((dq, q), (dk, k), (dv, v), (d_o, o)):
+        if a.shape != b_.shape or a.stride() != b_.stride() or a.dtype != q.dtype:
+            raise ValueError("dq, dk, dv, d_o must match q, k, v, o in shape, strides and dtype")
+    if lse.dtype != torch.float32 or lse.shape != (B, H, L) or not lse.is_contiguous():
+        raise ValueError("lse must be a contiguous fp32 [B, H, rows] tensor")
+    d = PrefillDesc()
+    d.dtype = _DTYPES[q.dtype]
+    d.algo = ALGO_AUTO
+    d.batch, d.heads, d.head_dim = B, H, dh
+    d.q_rows, d.k_rows = L, k.shape[2]
+    d.window, d.n_persistent = window, n_persistent
+    d.q_pos0, d.k_pos0, d.scale = 0, n_persistent, scale
+    d.q_stride[:] = _bhrd_strides(q)
+    d.k_stride[:] = _bhrd_strides(k)
+    d.v_stride[:] = _bhrd_strides(v)
+    d.o_stride[:] = _bhrd_strides(o)
+    with torch.cuda.device(q.device):
+        check(lib().tmw_prefill_backward(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                         d_o.data_ptr(), lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                         _stream_ptr(q.device)))
 
 
 def causal_dwconv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -9,8 +9,10 @@ attention core is ``tmw_prefill`` from libtmw reading Q, K, V as strided views o
 the projection output and writing straight into the head-concatenated layout.
 
 Not supported (raises ``NotImplementedError``): a caller-supplied ``attn_mask``
-(every caller in the reference passes ``None``), ``causal=False``, dropout in
-training mode, and autograd through the attention core.
+(every caller in the reference passes ``None``), ``causal=False`` and dropout in
+training mode.  When a gradient is wanted (grad mode on and the input or a weight
+requires one) the attention core runs as an autograd function whose backward is
+``tmw_prefill_backward``; otherwise nothing is saved.
 """
 
 from __future__ import annotations
@@ -22,6 +24,33 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import _native
+
+
+class _WindowedCore(torch.autograd.Function):
+    """``qkv [B, L, 3, H, dh]`` → ``o [B, L, H, dh]`` with ``tmw_prefill_lse`` / ``tmw_prefill_backward``."""
+
+    @staticmethod
+    def forward(ctx, qkv: torch.Tensor, window: int, n_persistent: int, algo: int) -> torch.Tensor:
+        qkv = qkv.contiguous()
+        B, L, _, H, dh = qkv.shape
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        o = torch.empty((B, L, H, dh), dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty((B, H, L), dtype=torch.float32, device=qkv.device)
+        _native.prefill(q, k, v, window, n_persistent, out=o.permute(0, 2, 1, 3), algo=algo, lse=lse)
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.window, ctx.n_persistent = window, n_persistent
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o: torch.Tensor):
+        qkv, o, lse = ctx.saved_tensors
+        d_o = d_o.contiguous()
+        dqkv = torch.empty_like(qkv)
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        dq, dk, dv = (dqkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        _native.prefill_backward(q, k, v, o.permute(0, 2, 1, 3), d_o.permute(0, 2, 1, 3), lse, dq, dk, dv,
+                                 ctx.window, ctx.n_persistent)
+        return dqkv, None, None, None
 
 
 class WindowedAttention(nn.Module):
@@ -71,8 +100,6 @@ class WindowedAttention(nn.Module):
             raise NotImplementedError("causal=False is not supported")
         if self.training and self.dropout_p > 0:
             raise NotImplementedError("attention dropout in training mode is not supported")
-        if torch.is_grad_enabled() and x.requires_grad:
-            raise NotImplementedError("this module is forward-only; call it under torch.no_grad()")
         if not x.is_cuda:
             raise RuntimeError("WindowedAttention (B200) needs CUDA tensors; there is no CPU path")
 
@@ -91,11 +118,20 @@ class WindowedAttention(nn.Module):
         v5 = qkv.view(B, L, 3, self.n_heads, self.d_head)
         return tuple(v5[:, :, i].permute(0, 2, 1, 3) for i in range(3))
 
-    @torch.no_grad()
     def forward(self, x: torch.Tensor, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, L, D = x.shape
         self._check_lengths(L)
         self._check_supported(x, attn_mask)
+        if torch.is_grad_enabled() and (x.requires_grad or self.qkv_proj.weight.requires_grad
+                                        or self.out_proj.weight.requires_grad):
+            qkv = self.qkv_proj(x).view(B, L, 3, self.n_heads, self.d_head)
+            o = _WindowedCore.apply(qkv, self.window_size, self.num_persistent, self.algo)
+            return self.dropout(self.out_proj(o.view(B, L, D)))
+        with torch.no_grad():
+            return self._forward_no_grad(x)
+
+    def _forward_no_grad(self, x: torch.Tensor) -> torch.Tensor:
+        B, L, D = x.shape
         qkv = self.qkv_proj(x)
         q, k, v = self.split_qkv(qkv)
         # the output is allocated as [B, L, H, dh] so that "concat heads" is a view

@@ -6,7 +6,8 @@ unchanged).  The attention is this package's own code, and so is the element-wis
 it on a GPU: RMSNorm with the preceding residual add folded in is one kernel
 (``tmw_add_rmsnorm``) and the exact GELU is another (``tmw_gelu``); the linears stay library calls.
 ``use_block_sparse`` selects the attention class exactly as in the reference.
-The package is forward-only; an input that carries a gradient takes the plain PyTorch norm.
+Under ``torch.no_grad()`` the fused kernels run; with grad mode on, norm and GELU fall back to the
+differentiable PyTorch formulas and the windowed attention core uses its own backward kernel.
 """
 
 from __future__ import annotations
@@ -30,15 +31,19 @@ class RMSNorm(nn.Module):
         self.scale = nn.Parameter(torch.ones(dim))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if _native.add_rmsnorm_supported(x) and not (torch.is_grad_enabled() and x.requires_grad):
+        if _native.add_rmsnorm_supported(x) and not self._wants_grad(x):
             return _native.add_rmsnorm(x, None, self.scale, self.eps)[1]
         rms = torch.sqrt(torch.mean(x ** 2, dim=-1, keepdim=True) + self.eps)
         return x / rms * self.scale
 
+    def _wants_grad(self, *tensors: torch.Tensor) -> bool:
+        """The fused kernel has no backward: with grad mode on and a gradient due to an input or to the scale,
+        the plain PyTorch formula runs instead (inference callers use ``torch.no_grad()``)."""
+        return torch.is_grad_enabled() and (self.scale.requires_grad or any(t.requires_grad for t in tensors))
+
     def add_forward(self, x: torch.Tensor, residual: torch.Tensor, inplace: bool = False):
         """``h = x + residual`` and ``RMSNorm(h)`` together: returns ``(h, normed)``."""
-        if _native.add_rmsnorm_supported(x) and not (
-                torch.is_grad_enabled() and (x.requires_grad or residual.requires_grad)):
+        if _native.add_rmsnorm_supported(x) and not self._wants_grad(x, residual):
             return _native.add_rmsnorm(x, residual, self.scale, self.eps, inplace_sum=inplace)
         h = x + residual
         return h, self.forward(h)
