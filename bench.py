@@ -54,6 +54,8 @@ WORKLOADS = {
     # Q/K/V, block-granular window, global persistent rows), block = max(64, window // 8) = 64
     "config2_block_sparse_layer_prefill": dict(batch=8, T=4096, d_model=640, heads=10, window=512, n_persistent=16,
                                                dtype="bf16", block_size=64, conv_taps=4),
+    # config 2's layer, forward + backward (gradients of the input and of both weights)
+    "config2_layer_train": dict(batch=8, T=4096, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16"),
     # BASELINE config 3: whole 16-layer model forward (prefill), 2 sequences of 8192 tokens per GPU
     "config3_model_prefill": dict(batch=2, T=8192, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
                                   layers=16, d_ff=2560, vocab=50000),
@@ -653,6 +655,136 @@ def run_model_prefill(args, wl_name: str, wl: dict) -> None:
         dist.destroy_process_group()
 
 
+def train_flops(wl: dict) -> dict:
+    """Forward + backward of the layer: every GEMM three times, the core 3.5 times (forward 4 dh per live pair;
+    backward recomputes S and forms dP, dV, dQ, dK: 10 dh per live pair)."""
+    f = layer_flops(wl)
+    return dict(core_fwd=f["core"], core_bwd=f["core"] * 5 // 2, gemm=3 * (f["qkv"] + f["out"]),
+                total=f["core"] * 7 // 2 + 3 * (f["qkv"] + f["out"]))
+
+
+def run_train(args, wl_name: str, wl: dict) -> None:
+    """Forward + backward of one attention layer per step (weak scaling, no gradient exchange: the layer is
+    timed in isolation).  The backward of the attention core is `tmw_prefill_backward`."""
+    from oracle import windowed_oracle as wo
+    from titanmac_b200 import WindowConfig, WindowedAttention, _native
+
+    dist, world, rank, local, dev = _dist_setup(args)
+    torch.set_grad_enabled(True)
+    B, T, D, H, w, Np = wl["batch"], wl["T"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
+    L = Np + T
+    x_cpu, w_qkv, w_out = wo.layer_inputs(B, T, D, Np, seed=rank)
+    mod = WindowedAttention(WindowConfig(window_size=w, num_heads=H, head_dim=D // H, n_persistent=Np))
+    with torch.no_grad():
+        mod.qkv_proj.weight.copy_(w_qkv)
+        mod.out_proj.weight.copy_(w_out)
+    mod = mod.to(device=dev, dtype=torch.bfloat16)
+    xs = [(x_cpu.to(torch.bfloat16) + 0.001 * i).to(dev).requires_grad_(True) for i in range(4)]
+    g = torch.randn(B, L, D, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).to(dev)
+    flops = train_flops(wl)
+
+    def step(i):
+        x = xs[i % 4]
+        x.grad = None
+        mod.zero_grad(set_to_none=True)
+        mod(x).backward(g)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        barrier()
+        a.record()
+        for i in range(args.steps):
+            step(i)
+        b.record()
+        barrier()
+    ms = a.elapsed_time(b)
+    _native.poll_status(dev)
+
+    # the backward kernels alone (saved tensors of one forward)
+    qkv = torch.randn(B, L, 3, H, D // H, device=dev).to(torch.bfloat16)
+    q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    lse = torch.empty(B, H, L, dtype=torch.float32, device=dev)
+    o = _native.prefill(q, k, v, w, Np, lse=lse)
+    d_o = torch.empty_like(o)
+    d_o.normal_()
+    dqkv = torch.empty_like(qkv)
+    dq, dk, dv = (dqkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    for _ in range(2):
+        _native.prefill_backward(q, k, v, o, d_o, lse, dq, dk, dv, w, Np)
+    c, d_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n_core = 5
+    c.record()
+    for _ in range(n_core):
+        _native.prefill_backward(q, k, v, o, d_o, lse, dq, dk, dv, w, Np)
+    d_.record()
+    torch.cuda.synchronize()
+    core_ms = c.elapsed_time(d_) / n_core
+
+    # end to end: input and output gradient from pinned host memory, input gradient back
+    x_host = x_cpu.to(torch.bfloat16).pin_memory()
+    g_host = g.cpu().pin_memory()
+    dx_host = torch.empty((B, L, D), dtype=torch.bfloat16).pin_memory()
+    x_dev = torch.empty((B, L, D), dtype=torch.bfloat16, device=dev, requires_grad=True)
+    g_dev = torch.empty_like(g)
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        with torch.no_grad():
+            x_dev.copy_(x_host, non_blocking=True)
+            g_dev.copy_(g_host, non_blocking=True)
+        x_dev.grad = None
+        mod.zero_grad(set_to_none=True)
+        mod(x_dev).backward(g_dev)
+        dx_host.copy_(x_dev.grad, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2.record()
+    barrier()
+    e2e_ms = s2.elapsed_time(e2)
+
+    t = torch.tensor([ms, core_ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, core_ms, e2e_ms = (float(x) for x in t.cpu())
+    if rank == 0:
+        peaks = load_peaks()
+        achieved = flops["core_bwd"] / (core_ms * 1e-3) / 1e12
+        line = {
+            "metric": "windowed_attn_layer_train_tflops", "value": flops["total"] * world * args.steps / (ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload=wl_name, **wl, global_batch=B * world, parallelism=f"batch-sharded x{world}",
+                           l2="inputs rotate over 4 sets; activations + gradients per step > 126 MB L2",
+                           flops_per_step_per_gpu=flops),
+            "roofline": {"bound": "tensor", "kernel": "attention-core backward (tmw_prefill_backward: dQ and dK/dV "
+                         "kernels on CUDA cores, fp32)", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                         "peak_source": f"{peaks['source']} bf16 burst", "avg_launch_ms": core_ms, "traffic": None,
+                         "algorithmic_flops_per_launch": flops["core_bwd"]},
+            "e2e": {"value": flops["total"] * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": 2 * x_host.numel() * 2, "d2h_bytes_per_step": dx_host.numel() * 2,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": args.steps * 3,
+            "clocks": clocks.report(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_long(args, wl_name: str, wl: dict) -> None:
     """BASELINE config 5: attention core over one long sequence, rows sharded over the GPUs with a K/V halo."""
     from oracle import windowed_oracle as wo
@@ -761,12 +893,14 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
-        if "layer_prefill" not in args.workload:
+        if "layer_prefill" not in args.workload:  # (the train, model, decode and long-context workloads)
             if int(os.environ.get("RANK", "0")) == 0:
                 print(json.dumps({"impl": "reference", "unavailable":
                                   "the CPU reference arm is timed on the layer workloads only"}), flush=True)
             return
         run_reference_arm(args, args.workload, wl)
+    elif args.workload == "config2_layer_train":
+        run_train(args, args.workload, wl)
     elif args.workload == "config3_model_prefill":
         run_model_prefill(args, args.workload, wl)
     elif args.workload == "config4_decode":

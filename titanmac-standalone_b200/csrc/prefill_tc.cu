@@ -57,8 +57,11 @@ constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per tile
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 #ifndef TMW_POLY_OF4
-#define TMW_POLY_OF4 1
+#define TMW_POLY_OF4 0
 #endif
+// Of every 4 column pairs, how many take the polynomial exp2 on the FMA pipe instead of the MUFU unit.
+// Measured on config 2's core: 0 -> 146 us, 1 -> 152 us, 2 -> 166 us (the polynomial costs 14 instructions per
+// pair against 2, and with two CTAs per SM the MUFU unit is not the limit), so it is off.
 constexpr int kPolyOf4 = TMW_POLY_OF4;
 #ifndef TMW_ALTERNATE
 #define TMW_ALTERNATE 2
@@ -322,10 +325,12 @@ struct CtaPlan {
 
 __device__ __forceinline__ int floor_div(int a, int b) { return (a >= 0) ? a / b : -((-a + b - 1) / b); }
 
-__device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block, int tiles) {
+// `wblock` / `all_keys`: the block-granular window and the unmasked mode; the kernel instantiated for the
+// plain windowed mask passes constants, so that none of this costs it an instruction
+__device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block, int tiles, int wblock, bool all_keys) {
     CtaPlan c;
     const int r0 = block * tiles * BM;
-    c.anchor = p.q_pos0 + r0 - p.window_plan;
+    c.anchor = p.q_pos0 + r0 - (wblock > 0 ? p.window_plan : p.window);
     c.x_begin = 1 << 30;
     c.x_end = 0;
 #pragma unroll
@@ -335,7 +340,7 @@ __device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block, int t
         q.rows = t < tiles ? max(0, min(BM, p.q_rows - (r0 + t * BM))) : 0;
         q.has_pers = (q.rows > 0 && p.np > 0) ? 1 : 0;
         const int p_hi = q.p_lo + q.rows - 1;
-        if (p.all_keys) {
+        if (all_keys) {
             c.anchor = p.k_pos0;  // key tile x starts at key row np + x * BN
             q.a = 0;
             q.n_win = q.rows > 0 ? (p.k_rows - p.np + BN - 1) / BN : 0;
@@ -344,7 +349,7 @@ __device__ __forceinline__ CtaPlan make_plan(const TcParams& p, int block, int t
                 c.x_end = max(c.x_end, q.n_win);
             }
         } else if (q.rows > 0 && p_hi >= p.np) {
-            const int g_lo = first_visible_pos(max(q.p_lo, p.np), p.np, p.window, p.block);
+            const int g_lo = first_visible_pos(max(q.p_lo, p.np), p.np, p.window, wblock);
             q.a = floor_div(g_lo - c.anchor, BN);
             q.n_win = floor_div(p_hi - c.anchor, BN) - q.a + 1;
             c.x_begin = min(c.x_begin, q.a);
@@ -390,7 +395,9 @@ enum BarSlot {
     BAR_COUNT = 31
 };
 
-template <int DH, int KS, int VS, bool BF16, int TILES>
+// GENERAL = false: the plain windowed mask (every mode parameter a compile-time constant);
+// GENERAL = true: block-granular window and / or the unmasked "all keys" mode, read from the parameters.
+template <int DH, int KS, int VS, bool BF16, int TILES, bool GENERAL>
 __global__ void __launch_bounds__(Budget<TILES>::kThreads, TILES == 2 ? 1 : 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -412,7 +419,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y, batch = blockIdx.z;
-    const CtaPlan plan = make_plan(p, blockIdx.x, TILES);
+    const int wblock = GENERAL ? p.block : 0;
+    const bool all_keys = GENERAL && p.all_keys != 0;
+    const CtaPlan plan = make_plan(p, blockIdx.x, TILES, wblock, all_keys);
 #ifdef TMW_TRACE
     const bool trace_on = blockIdx.x == 8 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
     if (trace_on && threadIdx.x == 0) g_trace[0] = clock64();
@@ -697,11 +706,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 full = false;
             } else {
                 const int g0 = plan.anchor + (q.a + item - q.has_pers) * BN;
-                if (p.all_keys) {
+                if (all_keys) {
                     j_lo = 0;
                     j_hi = p.k_pos0 + (p.k_rows - p.np) - 1 - g0;  // the last key row that exists
                 } else if (pos >= p.np) {
-                    j_lo = first_visible_pos(pos, p.np, p.window, p.block) - g0;
+                    j_lo = first_visible_pos(pos, p.np, p.window, wblock) - g0;
                     j_hi = pos - g0;
                 } else {
                     j_lo = 1;
@@ -709,9 +718,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
                 ncols = BN;
                 // every row of the tile sees every key of the tile (decided per tile, not per row)
-                full = p.all_keys ? j_hi >= BN - 1
-                                  : q.p_lo >= p.np && g0 >= p.np && g0 + BN - 1 <= q.p_lo &&
-                                        g0 >= first_visible_pos(q.p_lo + BM - 1, p.np, p.window, p.block);
+                full = all_keys ? j_hi >= BN - 1
+                                : q.p_lo >= p.np && g0 >= p.np && g0 + BN - 1 <= q.p_lo &&
+                                      g0 >= first_visible_pos(q.p_lo + BM - 1, p.np, p.window, wblock);
             }
             const int nchunks = (ncols + 31) / 32;
             // 32-column chunks in which no row of this warp sees a key (beyond the diagonal, or before the
@@ -1022,15 +1031,18 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     const int smem_bytes = L::total_bytes(np_pad);
     dim3 grid((d.q_rows + TILES * BM - 1) / (TILES * BM), d.heads, d.batch);
     constexpr int kThreadsTc = Budget<TILES>::kThreads;
-    if (d.dtype == TMW_BF16) {
-        auto kern = prefill_tc_kernel<DH, KS, VS, true, TILES>;
+    const bool general = window_block > 0 || all_keys;
+    auto run = [&](auto kern) -> int {
         TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         kern<<<grid, kThreadsTc, smem_bytes, stream>>>(mq, mk, mv, mo, mkp, mvp, p);
-    } else {
-        auto kern = prefill_tc_kernel<DH, KS, VS, false, TILES>;
-        TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-        kern<<<grid, kThreadsTc, smem_bytes, stream>>>(mq, mk, mv, mo, mkp, mvp, p);
-    }
+        return TMW_OK;
+    };
+    int st;
+    if (d.dtype == TMW_BF16)
+        st = general ? run(prefill_tc_kernel<DH, KS, VS, true, TILES, true>) : run(prefill_tc_kernel<DH, KS, VS, true, TILES, false>);
+    else
+        st = general ? run(prefill_tc_kernel<DH, KS, VS, false, TILES, true>) : run(prefill_tc_kernel<DH, KS, VS, false, TILES, false>);
+    if (st != TMW_OK) return st;
     TMW_CUDA_TRY(cudaGetLastError());
     return TMW_OK;
 }
