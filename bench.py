@@ -811,7 +811,7 @@ def run_long(args, wl_name: str, wl: dict) -> None:
     def step():
         if world == 1:
             return _native.prefill(q, k, v, w, Np)
-        return shard.sharded_prefill(q, None, None, Ltot, w, Np, kv=kv)
+        return shard.sharded_prefill(q, None, None, Ltot, w, Np, kv=kv, overlap=bool(args.shard_overlap))
 
     def barrier():
         if world > 1:
@@ -864,6 +864,7 @@ def run_long(args, wl_name: str, wl: dict) -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": dict(workload=wl_name, **wl, parallelism=f"sequence-sharded x{world}, halo {w} rows",
+                           shard_overlap=bool(args.shard_overlap),
                            l2="Q+K+V+O = 2.1 GB per step > 126 MB L2", algorithmic_flops_per_step=flops),
             "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill)", "achieved": value / world,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
@@ -888,6 +889,9 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="config2_layer_prefill")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1 only)")
+    ap.add_argument("--shard-overlap", type=int, choices=[0, 1], default=0,
+                    help="config5_long_prefill on several GPUs: 1 = rows that need no halo are launched before the "
+                         "halo exchange (two launches), 0 = one exchange, then one launch")
     args = ap.parse_args()
     torch.set_grad_enabled(False)  # inference workloads: nothing is saved for a backward pass
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -11,9 +11,11 @@ before its first row, plus the persistent K/V from rank 0.
 
 Everything lands in the rank's own HBM first — a K and a V buffer laid out as
 ``[persistent | halo | own rows]`` — and is then read by ordinary per-CTA TMA loads;
-nothing is read from a peer's memory by the attention kernel.  The rows whose window
-lies inside the rank's own block are launched before the halo arrives (on a side
-stream), the first ``w`` rows after it.
+nothing is read from a peer's memory by the attention kernel.  The buffers are stored
+row-major (``[B, rows, H, dh]``, the layout of the projection output), so a halo is a
+contiguous range that is sent and received in place, all transfers of a step in one batch.
+Optionally (``overlap=True``) the rows whose window lies inside the rank's own block are
+launched before the halo arrives (on a side stream), the first ``w`` rows after it.
 
 The planning and the exchange work on CPU tensors with the ``gloo`` backend as well
 (that is how they are tested without GPUs); the attention calls need CUDA.
@@ -76,7 +78,8 @@ def halo_rows(bounds: Sequence[Tuple[int, int]], rank: int, window: int, n_persi
 
 
 class ShardedKV:
-    """This rank's K/V buffers ``[B, H, Np + halo + own, dh]`` and the positions that go with them.
+    """This rank's K/V buffers ``[B, H, Np + halo + own, dh]`` (views of row-major storage, so that every
+    transfer is in place) and the positions that go with them.
 
     ``ShardedKV(k_own, v_own, ...)`` copies the rank's rows into fresh buffers.  ``ShardedKV.allocate(...)``
     only makes the buffers: the producer of K and V (the QKV projection) then writes this rank's rows straight
@@ -90,13 +93,9 @@ class ShardedKV:
         self._layout(total_rows, window, n_persistent, group)
         if k_own.shape[2] != self.r1 - self.r0 or v_own.shape != k_own.shape:
             raise ValueError(f"rank {self.rank} must hold rows [{self.r0}, {self.r1}) of K and V")
-        if self.rank == 0:
-            # rank 0's own block already starts with the persistent rows
-            self.k, self.v = k_own.contiguous(), v_own.contiguous()
-        else:
-            self._buffers(B, H, dh, k_own.dtype, k_own.device)
-            self.k[:, :, self.own_offset:] = k_own
-            self.v[:, :, self.own_offset:] = v_own
+        self._buffers(B, H, dh, k_own.dtype, k_own.device)
+        self.k[:, :, self.own_offset:] = k_own
+        self.v[:, :, self.own_offset:] = v_own
 
     @classmethod
     def allocate(cls, batch: int, heads: int, head_dim: int, total_rows: int, window: int, n_persistent: int,
@@ -120,9 +119,18 @@ class ShardedKV:
         self.q_pos0 = self.r0
 
     def _buffers(self, B: int, H: int, dh: int, dtype: torch.dtype, device) -> None:
-        shape = (B, H, self.own_offset + (self.r1 - self.r0), dh)
-        self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        # Stored row-major, [B, rows, H, dh], like the output of the QKV projection: a range of rows of one
+        # batch element is then one contiguous piece of memory that can be sent and received in place.
+        # self.k / self.v are the [B, H, rows, dh] views the attention kernel takes.
+        rows = self.own_offset + (self.r1 - self.r0)
+        self._k_rows = torch.empty((B, rows, H, dh), dtype=dtype, device=device)
+        self._v_rows = torch.empty((B, rows, H, dh), dtype=dtype, device=device)
+        self.k = self._k_rows.permute(0, 2, 1, 3)
+        self.v = self._v_rows.permute(0, 2, 1, 3)
+
+    def _pieces(self, a: int, rows: int):
+        """Contiguous views of buffer rows ``[a, a + rows)``: K then V of every batch element."""
+        return [t[b, a:a + rows] for t in (self._k_rows, self._v_rows) for b in range(t.shape[0])]
 
     @property
     def k_own(self) -> torch.Tensor:
@@ -133,42 +141,44 @@ class ShardedKV:
         return self.v[:, :, self.own_offset:]
 
     def exchange(self) -> None:
-        """Persistent K/V from rank 0 and the halo rows from the left neighbours, into this rank's buffers."""
-        self.exchange_persistent()
-        self.exchange_halo()
+        """Persistent K/V from rank 0 and the halo rows from the left neighbours, into this rank's buffers:
+        one batch of in-place sends and receives."""
+        self._run(self._persistent_ops() + self._halo_ops())
 
     def exchange_persistent(self) -> None:
-        Np = self.n_persistent
-        B, H, _, dh = self.k.shape
-        if Np > 0 and self.world > 1:
-            pers = torch.empty((2, B, H, Np, dh), dtype=self.k.dtype, device=self.k.device)
-            if self.rank == 0:
-                pers[0], pers[1] = self.k[:, :, :Np], self.v[:, :, :Np]
-            dist.broadcast(pers, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0,
-                           group=self.group)
-            if self.rank != 0:
-                self.k[:, :, :Np], self.v[:, :, :Np] = pers[0], pers[1]
+        self._run(self._persistent_ops())
 
     def exchange_halo(self) -> None:
-        Np = self.n_persistent
-        B, H, _, dh = self.k.shape
-        ops, landing = [], []
-        for tr in plan_halo(self.bounds, self.window, Np):
-            if tr.src == self.rank:
-                a = self.own_offset + (tr.src_row0 - self.r0)
-                # one message per transfer: K and V rows stacked
-                msg = torch.stack([self.k[:, :, a:a + tr.rows], self.v[:, :, a:a + tr.rows]]).contiguous()
-                ops.append(dist.P2POp(dist.isend, msg, self._global(tr.dst), group=self.group))
-            elif tr.dst == self.rank:
-                buf = torch.empty((2, B, H, tr.rows, dh), dtype=self.k.dtype, device=self.k.device)
-                ops.append(dist.P2POp(dist.irecv, buf, self._global(tr.src), group=self.group))
-                landing.append((tr, buf))
+        self._run(self._halo_ops())
+
+    def _run(self, ops) -> None:
         if ops:
             for req in dist.batch_isend_irecv(ops):
                 req.wait()
-        for tr, buf in landing:
-            a = Np + tr.dst_offset
-            self.k[:, :, a:a + tr.rows], self.v[:, :, a:a + tr.rows] = buf[0], buf[1]
+
+    def _persistent_ops(self):
+        """Rank 0 sends its first ``Np`` rows to every other rank (they land in rows ``[0, Np)`` there)."""
+        Np, ops = self.n_persistent, []
+        if Np == 0 or self.world == 1:
+            return ops
+        if self.rank == 0:
+            for dst in range(1, self.world):
+                ops += [dist.P2POp(dist.isend, t, self._global(dst), group=self.group) for t in self._pieces(0, Np)]
+        else:
+            ops += [dist.P2POp(dist.irecv, t, self._global(0), group=self.group) for t in self._pieces(0, Np)]
+        return ops
+
+    def _halo_ops(self):
+        Np, ops = self.n_persistent, []
+        for tr in plan_halo(self.bounds, self.window, Np):
+            if tr.src == self.rank:
+                a = self.own_offset + (tr.src_row0 - self.r0)
+                ops += [dist.P2POp(dist.isend, t, self._global(tr.dst), group=self.group)
+                        for t in self._pieces(a, tr.rows)]
+            elif tr.dst == self.rank:
+                ops += [dist.P2POp(dist.irecv, t, self._global(tr.src), group=self.group)
+                        for t in self._pieces(Np + tr.dst_offset, tr.rows)]
+        return ops
 
     def _global(self, group_rank: int) -> int:
         return dist.get_global_rank(self.group, group_rank) if self.group is not None else group_rank
@@ -186,12 +196,17 @@ def _side_stream(device: torch.device) -> "torch.cuda.Stream":
 
 def sharded_prefill(q_own: torch.Tensor, k_own: Optional[torch.Tensor], v_own: Optional[torch.Tensor],
                     total_rows: int, window: int, n_persistent: int, group: Optional[dist.ProcessGroup] = None,
-                    overlap: bool = True, algo: int = 0, kv: Optional[ShardedKV] = None) -> torch.Tensor:
+                    overlap: bool = False, algo: int = 0, kv: Optional[ShardedKV] = None) -> torch.Tensor:
     """Attention output for this rank's rows (``[B, H, own, dh]``), CUDA only.
 
     ``q_own, k_own, v_own``: ``[B, H, r1 - r0, dh]`` — this rank's rows of the whole-length tensors
     (rank 0's block starts with the persistent rows).  With ``kv`` (from :meth:`ShardedKV.allocate`, its
     ``k_own`` / ``v_own`` views already filled) ``k_own`` and ``v_own`` are ignored and nothing is copied.
+
+    ``overlap=False``: one batch of sends / receives, then one launch (measured best for halos of a few MB:
+    0.915 ms against 0.927 ms per step on two GPUs at 131 072 rows).  ``overlap=True``: the persistent rows
+    first, then the rows that need no halo on a side stream while the halo travels, then the first
+    ``window`` rows - for halos large enough that the transfer shows.
     """
     from . import _native
 
