@@ -46,7 +46,7 @@ WORKLOADS = {
                                   dtype="bf16"),
     "config1_layer_prefill_fp32": dict(batch=2, T=512, d_model=512, heads=8, window=256, n_persistent=16,
                                        dtype="fp32"),
-    # BASELINE config 4: 16-layer default model, ring-cache decode; `batch` is the WHOLE-job batch here
+    # benchmark configuration 4: 16-layer default model, ring-cache decode; `batch` is the WHOLE-job batch here
     # (256 sequences sharded over the GPUs), prompt 2048 tokens, then `--steps` single-token steps
     "config4_decode": dict(batch=256, T=2048, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
                            layers=16, d_ff=2560, vocab=50000),
@@ -56,10 +56,10 @@ WORKLOADS = {
                                                dtype="bf16", block_size=64, conv_taps=4),
     # config 2's layer, forward + backward (gradients of the input and of both weights)
     "config2_layer_train": dict(batch=8, T=4096, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16"),
-    # BASELINE config 3: whole 16-layer model forward (prefill), 2 sequences of 8192 tokens per GPU
+    # benchmark configuration 3: whole 16-layer model forward (prefill), 2 sequences of 8192 tokens per GPU
     "config3_model_prefill": dict(batch=2, T=8192, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
                                   layers=16, d_ff=2560, vocab=50000),
-    # BASELINE config 5: attention core only, Q/K/V given; the sequence is sharded over the GPUs
+    # benchmark configuration 5: attention core only, Q/K/V given; the sequence is sharded over the GPUs
     "config5_long_prefill": dict(batch=1, T=131072, d_model=2048, heads=16, window=1024, n_persistent=16,
                                  dtype="bf16"),
 }
@@ -382,7 +382,7 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
 
 
 def decode_attention_probe(dev, peaks, batch=256, heads=10, dh=64, window=512, n_persistent=16, layers=4, iters=10):
-    """The decode kernel alone on BASELINE config 4's geometry: one launch = one layer's attention for the whole
+    """The decode kernel alone on benchmark configuration 4's geometry: one launch = one layer's attention for the whole
     batch.  `layers` independent ring caches are cycled so that a launch never finds its ring in L2."""
     from titanmac_b200 import _native
 
@@ -428,7 +428,7 @@ def _dist_setup(args):
 
 
 def run_decode(args, wl_name: str, wl: dict) -> None:
-    """BASELINE config 4: prompt through the 16-layer model once, then `--steps` decode steps (CUDA graph)."""
+    """benchmark configuration 4: prompt through the 16-layer model once, then `--steps` decode steps (CUDA graph)."""
     from titanmac_b200 import TitanMAC, TitanMACConfig, _native
 
     dist, world, rank, local, dev = _dist_setup(args)
@@ -556,7 +556,7 @@ def run_decode(args, wl_name: str, wl: dict) -> None:
 
 
 def run_model_prefill(args, wl_name: str, wl: dict) -> None:
-    """BASELINE config 3: forward of the whole default model over `batch` sequences per GPU (weak scaling).
+    """benchmark configuration 3: forward of the whole default model over `batch` sequences per GPU (weak scaling).
 
     FLOPs are the reference forward's: per layer the attention module (QKV, live pairs, output projection) and
     the MLP, plus the LM head over all L rows.  The attention core's share of the step is measured with CUDA
@@ -786,7 +786,7 @@ def run_train(args, wl_name: str, wl: dict) -> None:
 
 
 def run_long(args, wl_name: str, wl: dict) -> None:
-    """BASELINE config 5: attention core over one long sequence, rows sharded over the GPUs with a K/V halo."""
+    """benchmark configuration 5: attention core over one long sequence, rows sharded over the GPUs with a K/V halo."""
     from oracle import windowed_oracle as wo
     from titanmac_b200 import _native, shard
 

@@ -41,7 +41,7 @@ LAYER_CASES = [
     ("dh64_multi_tile", 1, 284, 2, 64, 64, 16, 16, True),
     ("dh128_multi_tile", 1, 244, 1, 128, 100, 16, 17, True),
     ("dh64_np8_w129", 2, 400, 1, 64, 129, 8, 18, True),
-    # BASELINE config 1: batch 2, T=512, d_model 512, 8 heads x 64, w=256, Np=16, seed 0
+    # benchmark configuration 1: batch 2, T=512, d_model 512, 8 heads x 64, w=256, Np=16, seed 0
     ("config1_fp32", 2, 512, 8, 64, 256, 16, 0, False),
 ]
 

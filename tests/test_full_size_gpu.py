@@ -1,4 +1,4 @@
-"""Parity at the full sizes of BASELINE configs 3, 4 and 5, where the dense reference cannot run: sampled
+"""Parity at the full sizes of benchmark configurations 3, 4 and 5, where the dense reference cannot run: sampled
 row blocks (first, last, around every boundary of a 2/4/8-way sequence split) against the CPU oracle, the
 sharded layout against the unsharded result, and size-independent properties of a softmax average."""
 

@@ -124,7 +124,7 @@ def test_sharded_positions_match_unsharded_rows(algo):
 
 
 def test_two_kernels_agree_at_full_size_config2_tcgen05():
-    """BASELINE config 2 (B8, L=16+4096, 10 heads x 64, w=512): the two independent CUDA kernels agree,
+    """benchmark configuration 2 (B8, L=16+4096, 10 heads x 64, w=512): the two independent CUDA kernels agree,
     and sampled rows agree with the CPU oracle."""
     B, T, D, H, w, Np = 8, 4096, 640, 10, 512, 16
     x, w_qkv, w_out = wo.layer_inputs(B, T, D, Np, seed=0)
