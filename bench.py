@@ -66,7 +66,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention-core kernel,
 # taken from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126414080 + 25901568}
+NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126459392 + 24759296}
 
 
 def live_pairs(L: int, w: int, Np: int) -> int:
@@ -405,7 +405,7 @@ def decode_attention_probe(dev, peaks, batch=256, heads=10, dh=64, window=512, n
     ms = a.elapsed_time(b) / (iters * layers)
     nbytes = batch * heads * (window + 1 + n_persistent) * dh * 2 * 2
     gbs = nbytes / ms / 1e6
-    return {"bound": "hbm", "kernel": "decode_kernel (tmw_decode)", "achieved": gbs, "peak": peaks["hbm_gbs"],
+    return {"bound": "hbm", "kernel": "decode_stream_kernel (tmw_decode)", "achieved": gbs, "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "avg_launch_ms": ms,
             "algorithmic_bytes_per_launch": nbytes, "peak_source": f"{peaks['source']} copy bandwidth"}
 

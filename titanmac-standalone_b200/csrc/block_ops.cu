@@ -13,6 +13,15 @@ namespace {
 
 constexpr int kWarpsPerBlock = 8;
 
+// CTAs of `kernel` that fit on the whole GPU at once (the grid of a kernel whose threads loop over the work)
+template <typename K>
+int resident_ctas(K kernel, int threads) {
+    int sms = 148, dev = 0, per_sm = 1;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) per_sm = 1;
+    return sms * per_sm;
+}
+
 // NV = 8-element vectors per lane kept in registers; NV == 0: the row is read again for the second pass
 // (it comes out of L1/L2: the same warp has just read or written it).
 template <typename T, int NV>
@@ -95,15 +104,18 @@ add_rmsnorm_kernel(const T* x, const T* __restrict__ res, const T* __restrict__ 
 template <typename T>
 int launch_add_rmsnorm(long long rows, int dim, const void* x, const void* res, const void* scale, float eps,
                        void* sum_out, void* y, cudaStream_t stream) {
-    int sms = 148, dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long want = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    const unsigned blocks = (unsigned)(want < (long long)sms * 8 ? want : (long long)sms * 8);  // 8 blocks of 256 threads per SM
     const int nv = (dim / 8 + 31) / 32;
+    // one resident wave: every warp walks over its rows, nothing waits for a slot
 #define TMW_NORM_CASE(N)                                                                                     \
-    add_rmsnorm_kernel<T, N><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(                                    \
-        static_cast<const T*>(x), static_cast<const T*>(res), static_cast<const T*>(scale), eps,            \
-        static_cast<T*>(sum_out), static_cast<T*>(y), rows, dim)
+    {                                                                                                        \
+        static int wave = 0;                                                                                 \
+        if (wave == 0) wave = resident_ctas(add_rmsnorm_kernel<T, N>, kWarpsPerBlock * 32);                  \
+        const unsigned blocks = (unsigned)(want < wave ? want : wave);                                       \
+        add_rmsnorm_kernel<T, N><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(                                \
+            static_cast<const T*>(x), static_cast<const T*>(res), static_cast<const T*>(scale), eps,        \
+            static_cast<T*>(sum_out), static_cast<T*>(y), rows, dim);                                        \
+    }
     switch (nv) {
         case 1: TMW_NORM_CASE(1); break;
         case 2: TMW_NORM_CASE(2); break;
@@ -123,34 +135,45 @@ int launch_add_rmsnorm(long long rows, int dim, const void* x, const void* res, 
 // HBM (one read, one write) and not by arithmetic.
 __device__ __forceinline__ float gelu_erf(float x) {
     const float z = fabsf(x) * 0.70710678118654752f;
-    const float t = __frcp_rn(fmaf(0.3275911f, z, 1.0f));
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
     float poly = fmaf(1.061405429f, t, -1.453152027f);
     poly = fmaf(poly, t, 1.421413741f);
     poly = fmaf(poly, t, -0.284496736f);
     poly = fmaf(poly, t, 0.254829592f);
-    const float erfc_z = poly * t * exp2f(-z * z * 1.4426950408889634f);  // 1 - erf(z), z >= 0
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-z * z * 1.4426950408889634f));
+    const float erfc_z = poly * t * e;  // 1 - erf(z), z >= 0
     const float erf_abs = 1.0f - erfc_z;
     return 0.5f * x * (1.0f + copysignf(erf_abs, x));
 }
 
+constexpr int kGeluUnroll = 4;  // 16-byte loads in flight per thread
+
 template <typename T>
-__global__ void __launch_bounds__(256) gelu_kernel(const T* __restrict__ x, T* __restrict__ y, long long nvec) {
-    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
-        float a[8];
-        load8<T>(x + v * 8, a);
+__global__ void __launch_bounds__(256) gelu_kernel(const T* x, T* y, long long nvec) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * kGeluUnroll) {
+        float a[kGeluUnroll][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) a[i] = gelu_erf(a[i]);
-        store8<T>(y + v * 8, a);
+        for (int u = 0; u < kGeluUnroll; ++u)
+            if (v0 + u * stride < nvec) load8<T>(x + (v0 + u * stride) * 8, a[u]);
+#pragma unroll
+        for (int u = 0; u < kGeluUnroll; ++u)
+            if (v0 + u * stride < nvec) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a[u][i] = gelu_erf(a[u][i]);
+                store8<T>(y + (v0 + u * stride) * 8, a[u]);
+            }
     }
 }
 
 template <typename T>
 int launch_gelu(long long n, const void* x, void* y, cudaStream_t stream) {
-    int sms = 148, dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    static int wave = 0;
+    if (wave == 0) wave = resident_ctas(gelu_kernel<T>, 256);
     const long long nvec = n / 8;
-    const long long want = (nvec + 255) / 256;
-    const unsigned blocks = (unsigned)(want < (long long)sms * 8 ? want : (long long)sms * 8);
+    const long long want = (nvec + 256 * kGeluUnroll - 1) / (256 * kGeluUnroll);
+    const unsigned blocks = (unsigned)(want < wave ? want : wave);
     gelu_kernel<T><<<blocks, 256, 0, stream>>>(static_cast<const T*>(x), static_cast<T*>(y), nvec);
     TMW_CUDA_TRY(cudaGetLastError());
     return TMW_OK;
