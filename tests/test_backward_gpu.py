@@ -63,11 +63,12 @@ def test_core_gradients_against_oracle_autograd(dtype, tol, dh, H, B, L, w, Np):
         assert (lse.cpu() - want_lse).abs().max().item() <= (1e-4 if dtype == torch.float32 else 3e-2), algo
         d_o = torch.empty_like(o)
         d_o.copy_(g.to(DEV))
-        dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
-        _native.prefill_backward(qd, kd, vd, o, d_o, lse, dq, dk, dv, w, Np)
-        for got, want, nm in ((dq, qr.grad, "dq"), (dk, kr.grad, "dk"), (dv, vr.grad, "dv")):
-            err = (got.float().cpu() - want).abs().max().item()
-            assert err <= tol * max(1.0, want.abs().max().item()), (nm, algo, err)
+        for bwd_algo in (_native.ALGO_SIMT, _native.ALGO_AUTO):  # CUDA-core kernels, then tensor cores where they apply
+            dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+            _native.prefill_backward(qd, kd, vd, o, d_o, lse, dq, dk, dv, w, Np, algo=bwd_algo)
+            for got, want, nm in ((dq, qr.grad, "dq"), (dk, kr.grad, "dk"), (dv, vr.grad, "dv")):
+                err = (got.float().cpu() - want).abs().max().item()
+                assert err <= tol * max(1.0, want.abs().max().item()), (nm, algo, bwd_algo, err)
     _native.poll_status(torch.device(DEV))
 
 

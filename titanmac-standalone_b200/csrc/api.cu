@@ -198,6 +198,9 @@ int tmw_prefill_backward(const tmw_prefill_desc* desc, const void* q, const void
     if (d_o == nullptr || lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) return TMW_ERR_INVALID_ARGUMENT;
     if (!tmw::aligned16(d_o) || !tmw::aligned16(dq) || !tmw::aligned16(dk) || !tmw::aligned16(dv))
         return TMW_ERR_INVALID_ARGUMENT;
+    // desc->algo: TMW_ALGO_SIMT pins the CUDA-core kernels; otherwise the tensor-core kernels where they apply
+    if (desc->algo != TMW_ALGO_SIMT && tmw::prefill_backward_mma_supports(*desc))
+        return tmw::launch_prefill_backward_mma(*desc, q, k, v, o, d_o, lse, dq, dk, dv, static_cast<cudaStream_t>(stream));
     return tmw::launch_prefill_backward(*desc, q, k, v, o, d_o, lse, dq, dk, dv, static_cast<cudaStream_t>(stream));
 }
 

@@ -1,0 +1,366 @@
+// Backward of the windowed attention core on the warp-level tensor-core path (nvcuda::wmma, 16-bit inputs,
+// fp32 accumulation), for head_dim 64 and 128.  Same mathematics and the same two-kernel split as the
+// CUDA-core version in prefill_bwd.cu - a dQ kernel that owns 64 query rows and walks over the 64-key blocks
+// of their windows, a dK/dV kernel that owns 64 keys and walks over the query blocks that can see them - but
+// the five matrix products per (query block, key block) pair run as 16x16x16 tensor-core tiles:
+//
+//   S  = Q K^T          dP = dO V^T                (fp32 tiles to shared memory)
+//   P  = exp2(S c - lse) o mask,  dS = P o (dP - D)  (element-wise, rounded to the 16-bit type)
+//   dV += P^T dO        dK += dS^T Q               dQ += dS K
+//
+// Everything between the products goes through shared memory, which keeps the fragment layouts of the wmma
+// API opaque; it is a plain kernel, not a pipelined one.  Whole sequences only, like the CUDA-core version.
+#include <math_constants.h>
+#include <mma.h>
+
+#include "tmw_common.cuh"
+
+namespace tmw {
+namespace {
+
+using namespace nvcuda;
+
+constexpr int BR = 64;        // query rows per block
+constexpr int BC = 64;        // keys per block
+constexpr int kWarps = 8;
+constexpr int kThreadsMma = kWarps * 32;
+
+struct MmaBwdParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    const void* o;
+    const void* d_o;
+    const float* lse;
+    void* dq;
+    void* dk;
+    void* dv;
+    int rows, window, np;
+    long long qs[3], ks[3], vs[3], os[3];
+    float scale, scale_log2;
+};
+
+// Row strides in shared memory, padded by 16 bytes so that the 16 rows a tensor-core tile load touches fall
+// into different banks (an unpadded 128-byte row stride puts all of them on the same ones).
+template <int DH>
+struct Ld {
+    static constexpr int kT = DH + 8;   // 16-bit tiles [64 x DH]: K, V, Q, dO (and O while D is computed)
+    static constexpr int kP = 64 + 8;   // 16-bit [64 x 64]: P, dS
+    static constexpr int kS = 64 + 4;   // fp32 [64 x 64]: S, dP
+    static constexpr int kOut = DH + 4; // fp32 [64 x DH]: results on the way out (in the S and dP buffers)
+};
+
+template <typename T, int DH>
+struct MmaSmem {
+    static constexpr int kTile = 64 * Ld<DH>::kT * 2;
+    static constexpr int kPBytes = 64 * Ld<DH>::kP * 2;
+    static constexpr int kSBytes = 64 * Ld<DH>::kS * 4;
+    static constexpr int kK = 0, kV = kTile, kQ = 2 * kTile, kDO = 3 * kTile;
+    static constexpr int kP = 4 * kTile, kDS = kP + kPBytes;   // contiguous: together they also hold an O tile
+    static constexpr int kS = kDS + kPBytes, kDP = kS + kSBytes;  // contiguous: together they stage a result
+    static constexpr int kLse = kDP + kSBytes, kD = kLse + 64 * 4;
+    static constexpr int kBytes = kD + 64 * 4;
+    static_assert(kTile <= 2 * kPBytes, "an O tile must fit into the P and dS buffers");
+    static_assert(64 * Ld<DH>::kOut * 4 <= 2 * kSBytes, "an fp32 result tile must fit into the S and dP buffers");
+    static_assert(kTile % 32 == 0 && kPBytes % 32 == 0 && kSBytes % 32 == 0, "tensor-core tile loads want 32-byte alignment");
+};
+
+// copies rows [r0, r0 + 64) of a [rows, DH] tensor (row stride in elements) into a dense 16-bit tile; rows at or
+// beyond `limit` become zeros
+template <typename T, int DH>
+__device__ __forceinline__ void load_tile(T* tile, const T* base, long long row_stride, int r0, int limit) {
+    constexpr int CPR = DH / 8;
+    for (int c = threadIdx.x; c < 64 * CPR; c += kThreadsMma) {
+        const int j = c / CPR, col = (c % CPR) * 8;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (r0 + j < limit) val = *reinterpret_cast<const uint4*>(base + (long long)(r0 + j) * row_stride + col);
+        *reinterpret_cast<uint4*>(tile + j * Ld<DH>::kT + col) = val;
+    }
+}
+
+// out[64 x 64] (fp32, shared) = A[64 x DH] * B[64 x DH]^T, both 16-bit row-major tiles; 8 warps, 16 x 32 each
+template <typename T, int DH>
+__device__ __forceinline__ void gemm_abt(float* out, const T* a, const T* b) {
+    const int warp = threadIdx.x >> 5;
+    const int m0 = (warp >> 1) * 16, n0 = (warp & 1) * 32;
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2];
+    wmma::fill_fragment(acc[0], 0.f);
+    wmma::fill_fragment(acc[1], 0.f);
+    constexpr int LT = Ld<DH>::kT, LS = Ld<DH>::kS;
+#pragma unroll
+    for (int kk = 0; kk < DH; kk += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> fa;
+        wmma::load_matrix_sync(fa, a + m0 * LT + kk, LT);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::col_major> fb;  // B^T: element (k, n) = b[n][k]
+            wmma::load_matrix_sync(fb, b + (n0 + t * 16) * LT + kk, LT);
+            wmma::mma_sync(acc[t], fa, fb, acc[t]);
+        }
+    }
+    wmma::store_matrix_sync(out + m0 * LS + n0, acc[0], LS, wmma::mem_row_major);
+    wmma::store_matrix_sync(out + m0 * LS + n0 + 16, acc[1], LS, wmma::mem_row_major);
+}
+
+// accumulators of a [64 x DH] result spread over 8 warps: warp w owns the 16-row band (w / 2) and the column
+// tiles n = (w % 2) * DH / 32 + t, t < DH / 32
+template <int DH>
+struct Acc64 {
+    static constexpr int NT = DH / 32;
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> f[NT];
+    __device__ __forceinline__ void zero() {
+#pragma unroll
+        for (int t = 0; t < NT; ++t) wmma::fill_fragment(f[t], 0.f);
+    }
+};
+
+// acc[64 x DH] += A^T B with A = a[64(k) x 64(m)] (16-bit, row-major, used transposed) and B = b[64(k) x DH]
+template <typename T, int DH>
+__device__ __forceinline__ void gemm_atb_acc(Acc64<DH>& acc, const T* a, const T* b) {
+    const int warp = threadIdx.x >> 5;
+    const int m0 = (warp >> 1) * 16, nbase = (warp & 1) * (DH / 2);
+#pragma unroll
+    for (int kk = 0; kk < 64; kk += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::col_major> fa;  // A^T: element (m, k) = a[k][m]
+        wmma::load_matrix_sync(fa, a + kk * Ld<DH>::kP + m0, Ld<DH>::kP);
+#pragma unroll
+        for (int t = 0; t < Acc64<DH>::NT; ++t) {
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> fb;
+            wmma::load_matrix_sync(fb, b + kk * Ld<DH>::kT + nbase + t * 16, Ld<DH>::kT);
+            wmma::mma_sync(acc.f[t], fa, fb, acc.f[t]);
+        }
+    }
+}
+// acc[64 x DH] += A B with A = a[64(m) x 64(k)] (16-bit, row-major) and B = b[64(k) x DH]
+template <typename T, int DH>
+__device__ __forceinline__ void gemm_ab_acc(Acc64<DH>& acc, const T* a, const T* b) {
+    const int warp = threadIdx.x >> 5;
+    const int m0 = (warp >> 1) * 16, nbase = (warp & 1) * (DH / 2);
+#pragma unroll
+    for (int kk = 0; kk < 64; kk += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, T, wmma::row_major> fa;
+        wmma::load_matrix_sync(fa, a + m0 * Ld<DH>::kP + kk, Ld<DH>::kP);
+#pragma unroll
+        for (int t = 0; t < Acc64<DH>::NT; ++t) {
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, T, wmma::row_major> fb;
+            wmma::load_matrix_sync(fb, b + kk * Ld<DH>::kT + nbase + t * 16, Ld<DH>::kT);
+            wmma::mma_sync(acc.f[t], fa, fb, acc.f[t]);
+        }
+    }
+}
+// stages the accumulators as fp32 [64 x DH] in shared memory, then writes rows [r0, r0 + 64) < limit, times `mul`
+template <typename T, int DH>
+__device__ __forceinline__ void store_acc(Acc64<DH>& acc, float* stage, T* base, long long row_stride, int r0, int limit,
+                                          float mul) {
+    const int warp = threadIdx.x >> 5;
+    const int m0 = (warp >> 1) * 16, nbase = (warp & 1) * (DH / 2);
+#pragma unroll
+    for (int t = 0; t < Acc64<DH>::NT; ++t)
+        wmma::store_matrix_sync(stage + m0 * Ld<DH>::kOut + nbase + t * 16, acc.f[t], Ld<DH>::kOut, wmma::mem_row_major);
+    __syncthreads();
+    constexpr int CPR = DH / 8;
+    for (int c = threadIdx.x; c < 64 * CPR; c += kThreadsMma) {
+        const int j = c / CPR, col = (c % CPR) * 8;
+        if (r0 + j < limit) {
+            float t[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) t[e] = stage[j * Ld<DH>::kOut + col + e] * mul;
+            store8<T>(base + (long long)(r0 + j) * row_stride + col, t);
+        }
+    }
+}
+
+// lse and D = sum_d dO O of the 64 staged query rows (O tile in `o_tile`, dO tile in `do_tile`)
+template <typename T, int DH>
+__device__ __forceinline__ void row_stats(float* lse_s, float* d_s, const T* o_tile, const T* do_tile, const float* lse_g,
+                                          int i0, int limit) {
+    // four threads per row
+    const int row = threadIdx.x >> 2, part = threadIdx.x & 3;
+    float sum = 0.f;
+    for (int c = part * (DH / 4); c < (part + 1) * (DH / 4); ++c)
+        sum = fmaf(to_f32<T>(o_tile[row * Ld<DH>::kT + c]), to_f32<T>(do_tile[row * Ld<DH>::kT + c]), sum);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (part == 0) {
+        d_s[row] = sum;
+        lse_s[row] = i0 + row < limit ? lse_g[i0 + row] : 0.f;
+    }
+}
+
+// P and dS of one (query block, key block) pair from S and dP.  `key_pos(c)` = position of key column c, or -1 for
+// a persistent key; a column is hidden by returning -2.
+template <typename T, int DH, typename KeyPos>
+__device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, const float* dp_s, const float* lse_s,
+                                             const float* d_s, int i0, int rows, int np, int window, float scale_log2,
+                                             KeyPos key_pos) {
+    for (int e = threadIdx.x; e < 64 * 64; e += kThreadsMma) {
+        const int r = e >> 6, c = e & 63;
+        const int i = i0 + r;
+        const int g = key_pos(c);
+        const bool vis = i < rows && (g == -1 || (g >= 0 && i >= np && g <= i && i - g <= window));
+        const int es = r * Ld<DH>::kS + c, ep = r * Ld<DH>::kP + c;
+        float p = 0.f;
+        if (vis) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(s_s[es] * scale_log2 - lse_s[r]));
+        p_s[ep] = from_f32<T>(p);
+        ds_s[ep] = from_f32<T>(p * (dp_s[es] - d_s[r]));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+template <typename T, int DH>
+__global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdParams p, int n_seq_blocks) {
+    using L = MmaSmem<T, DH>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    T* k_s = reinterpret_cast<T*>(smem + L::kK);
+    T* v_s = reinterpret_cast<T*>(smem + L::kV);
+    T* q_s = reinterpret_cast<T*>(smem + L::kQ);
+    T* do_s = reinterpret_cast<T*>(smem + L::kDO);
+    T* p_s = reinterpret_cast<T*>(smem + L::kP);
+    T* ds_s = reinterpret_cast<T*>(smem + L::kDS);
+    float* s_s = reinterpret_cast<float*>(smem + L::kS);
+    float* dp_s = reinterpret_cast<float*>(smem + L::kDP);
+    float* lse_s = reinterpret_cast<float*>(smem + L::kLse);
+    float* d_s = reinterpret_cast<float*>(smem + L::kD);
+
+    const int h = blockIdx.y, b = blockIdx.z;
+    const bool pers = (int)blockIdx.x >= n_seq_blocks;
+    const int k0 = pers ? ((int)blockIdx.x - n_seq_blocks) * BC : p.np + (int)blockIdx.x * BC;
+    const int k_end = pers ? min(p.np, k0 + BC) : min(p.rows, k0 + BC);
+    const T* qg = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1];
+    const T* kg = static_cast<const T*>(p.k) + b * p.ks[0] + h * p.ks[1];
+    const T* vg = static_cast<const T*>(p.v) + b * p.vs[0] + h * p.vs[1];
+    const T* og = static_cast<const T*>(p.o) + b * p.os[0] + h * p.os[1];
+    const T* dog = static_cast<const T*>(p.d_o) + b * p.os[0] + h * p.os[1];
+    const float* lse_g = p.lse + ((long long)b * gridDim.y + h) * p.rows;
+
+    load_tile<T, DH>(k_s, kg, p.ks[2], k0, k_end);
+    load_tile<T, DH>(v_s, vg, p.vs[2], k0, k_end);
+    Acc64<DH> dk, dv;
+    dk.zero();
+    dv.zero();
+    const int i_lo = pers ? 0 : k0;
+    const int i_hi = pers ? p.rows - 1 : (int)min((long long)p.rows - 1, (long long)k_end - 1 + p.window);
+    auto key_pos = [&](int c) { return k0 + c < k_end ? (pers ? -1 : k0 + c) : -2; };
+    for (int i0 = i_lo; i0 <= i_hi; i0 += BR) {
+        __syncthreads();  // the previous round's products have read q_s, do_s, p_s, ds_s
+        load_tile<T, DH>(q_s, qg, p.qs[2], i0, p.rows);
+        load_tile<T, DH>(do_s, dog, p.os[2], i0, p.rows);
+        load_tile<T, DH>(p_s, og, p.os[2], i0, p.rows);  // the O tile, in the P / dS buffers for a moment
+        __syncthreads();
+        row_stats<T, DH>(lse_s, d_s, p_s, do_s, lse_g, i0, p.rows);
+        gemm_abt<T, DH>(s_s, q_s, k_s);
+        gemm_abt<T, DH>(dp_s, do_s, v_s);
+        __syncthreads();
+        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, p.rows, p.np, p.window, p.scale_log2, key_pos);
+        __syncthreads();
+        gemm_atb_acc<T, DH>(dv, p_s, do_s);
+        gemm_atb_acc<T, DH>(dk, ds_s, q_s);
+    }
+    __syncthreads();
+    T* dkg = static_cast<T*>(p.dk) + b * p.ks[0] + h * p.ks[1];
+    T* dvg = static_cast<T*>(p.dv) + b * p.vs[0] + h * p.vs[1];
+    store_acc<T, DH>(dk, s_s, dkg, p.ks[2], k0, k_end, p.scale);
+    __syncthreads();
+    store_acc<T, DH>(dv, s_s, dvg, p.vs[2], k0, k_end, 1.0f);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+template <typename T, int DH>
+__global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdParams p) {
+    using L = MmaSmem<T, DH>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    T* k_s = reinterpret_cast<T*>(smem + L::kK);
+    T* v_s = reinterpret_cast<T*>(smem + L::kV);
+    T* q_s = reinterpret_cast<T*>(smem + L::kQ);
+    T* do_s = reinterpret_cast<T*>(smem + L::kDO);
+    T* p_s = reinterpret_cast<T*>(smem + L::kP);
+    T* ds_s = reinterpret_cast<T*>(smem + L::kDS);
+    float* s_s = reinterpret_cast<float*>(smem + L::kS);
+    float* dp_s = reinterpret_cast<float*>(smem + L::kDP);
+    float* lse_s = reinterpret_cast<float*>(smem + L::kLse);
+    float* d_s = reinterpret_cast<float*>(smem + L::kD);
+
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int i0 = blockIdx.x * BR;
+    const T* qg = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1];
+    const T* kg = static_cast<const T*>(p.k) + b * p.ks[0] + h * p.ks[1];
+    const T* vg = static_cast<const T*>(p.v) + b * p.vs[0] + h * p.vs[1];
+    const T* og = static_cast<const T*>(p.o) + b * p.os[0] + h * p.os[1];
+    const T* dog = static_cast<const T*>(p.d_o) + b * p.os[0] + h * p.os[1];
+    const float* lse_g = p.lse + ((long long)b * gridDim.y + h) * p.rows;
+
+    load_tile<T, DH>(q_s, qg, p.qs[2], i0, p.rows);
+    load_tile<T, DH>(do_s, dog, p.os[2], i0, p.rows);
+    load_tile<T, DH>(p_s, og, p.os[2], i0, p.rows);
+    __syncthreads();
+    row_stats<T, DH>(lse_s, d_s, p_s, do_s, lse_g, i0, p.rows);
+    Acc64<DH> dq;
+    dq.zero();
+    // key blocks: the persistent keys in blocks of 64, then the positions [glo, i_last] of this block's windows
+    const int i_last = min(i0 + BR, p.rows) - 1;
+    const int glo = max(p.np, i0 - p.window);
+    const int n_pers_blocks = (p.np + BC - 1) / BC;
+    const int n_win_blocks = i_last >= p.np ? (i_last - glo) / BC + 1 : 0;
+    for (int jb = 0; jb < n_pers_blocks + n_win_blocks; ++jb) {
+        const bool pers = jb < n_pers_blocks;
+        const int k0 = pers ? jb * BC : glo + (jb - n_pers_blocks) * BC;
+        const int k_end = pers ? min(p.np, k0 + BC) : min(i_last + 1, k0 + BC);
+        __syncthreads();  // the previous round's product has read k_s and ds_s; row_stats has read p_s
+        load_tile<T, DH>(k_s, kg, p.ks[2], k0, k_end);
+        load_tile<T, DH>(v_s, vg, p.vs[2], k0, k_end);
+        __syncthreads();
+        gemm_abt<T, DH>(s_s, q_s, k_s);
+        gemm_abt<T, DH>(dp_s, do_s, v_s);
+        __syncthreads();
+        auto key_pos = [&](int c) { return k0 + c < k_end ? (pers ? -1 : k0 + c) : -2; };
+        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, p.rows, p.np, p.window, p.scale_log2, key_pos);
+        __syncthreads();
+        gemm_ab_acc<T, DH>(dq, ds_s, k_s);
+    }
+    __syncthreads();
+    T* dqg = static_cast<T*>(p.dq) + b * p.qs[0] + h * p.qs[1];
+    store_acc<T, DH>(dq, s_s, dqg, p.qs[2], i0, p.rows, p.scale);
+}
+
+template <typename T, int DH>
+int launch_mma(const MmaBwdParams& p, int batch, int heads, cudaStream_t stream) {
+    using L = MmaSmem<T, DH>;
+    auto kq = bwd_mma_dq_kernel<T, DH>;
+    auto kkv = bwd_mma_dkv_kernel<T, DH>;
+    TMW_CUDA_TRY(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    TMW_CUDA_TRY(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    const dim3 gq((p.rows + BR - 1) / BR, heads, batch);
+    kq<<<gq, kThreadsMma, L::kBytes, stream>>>(p);
+    TMW_CUDA_TRY(cudaGetLastError());
+    const int n_seq = (p.rows - p.np + BC - 1) / BC, n_pers = (p.np + BC - 1) / BC;
+    const dim3 gk(n_seq + n_pers, heads, batch);
+    kkv<<<gk, kThreadsMma, L::kBytes, stream>>>(p, n_seq);
+    TMW_CUDA_TRY(cudaGetLastError());
+    return TMW_OK;
+}
+
+}  // namespace
+
+bool prefill_backward_mma_supports(const tmw_prefill_desc& d) {
+    return (d.dtype == TMW_BF16 || d.dtype == TMW_F16) && (d.head_dim == 64 || d.head_dim == 128) && d.batch <= 65535 &&
+           d.heads <= 65535;
+}
+
+int launch_prefill_backward_mma(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
+                                const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream) {
+    MmaBwdParams p;
+    p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.lse = lse; p.dq = dq; p.dk = dk; p.dv = dv;
+    p.rows = d.q_rows; p.window = d.window; p.np = d.n_persistent;
+    for (int i = 0; i < 3; ++i) {
+        p.qs[i] = d.q_stride[i]; p.ks[i] = d.k_stride[i]; p.vs[i] = d.v_stride[i]; p.os[i] = d.o_stride[i];
+    }
+    p.scale = d.scale != 0.f ? d.scale : 1.0f / sqrtf((float)d.head_dim);
+    p.scale_log2 = p.scale * 1.4426950408889634f;
+    if (d.dtype == TMW_BF16)
+        return d.head_dim == 64 ? launch_mma<__nv_bfloat16, 64>(p, d.batch, d.heads, stream)
+                                : launch_mma<__nv_bfloat16, 128>(p, d.batch, d.heads, stream);
+    return d.head_dim == 64 ? launch_mma<__half, 64>(p, d.batch, d.heads, stream)
+                            : launch_mma<__half, 128>(p, d.batch, d.heads, stream);
+}
+
+}  // namespace tmw

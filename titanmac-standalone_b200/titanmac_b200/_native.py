@@ -249,7 +249,7 @@ def prefill(
 
 def prefill_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor,
                      lse: torch.Tensor, dq: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor, window: int,
-                     n_persistent: int, scale: float = 0.0) -> None:
+                     n_persistent: int, scale: float = 0.0, algo: int = ALGO_AUTO) -> None:
     """``tmw_prefill_backward``: fills ``dq, dk, dv`` (same strides as ``q, k, v``) from ``d_o`` (same strides as
     ``o``), the saved output and the log-sum-exp of ``prefill(..., lse=...)``.  Whole sequences only."""
     _require_cuda(q, k, v, o, d_o, lse, dq, dk, dv)
@@ -261,7 +261,7 @@ def prefill_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch
         raise ValueError("lse must be a contiguous fp32 [B, H, rows] tensor")
     d = PrefillDesc()
     d.dtype = _DTYPES[q.dtype]
-    d.algo = ALGO_AUTO
+    d.algo = algo  # ALGO_SIMT pins the CUDA-core kernels, otherwise tensor cores for 16-bit types and head_dim 64 / 128
     d.batch, d.heads, d.head_dim = B, H, dh
     d.q_rows, d.k_rows = L, k.shape[2]
     d.window, d.n_persistent = window, n_persistent
