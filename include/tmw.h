@@ -103,7 +103,8 @@ TMW_API int tmw_prefill_lse(const tmw_prefill_desc* desc, const void* q, const v
  * given d_o (gradient of o, addressed like o) and the o and lse of tmw_prefill_lse, writes dq, dk, dv
  * (addressed like q, k, v: the same strides).  Replaces what autograd does through the reference's mask
  * conversion and scaled-dot-product call (windowed_attention.py:307-323) - there over all L x L pairs,
- * here over the visible pairs only.  fp32 arithmetic on CUDA cores for every dtype.
+ * here over the visible pairs only.  Warp-level tensor cores (fp32 accumulation) for bf16 / f16 with head_dim
+ * 64 or 128; fp32 arithmetic on CUDA cores otherwise, or for every case when desc->algo is TMW_ALGO_SIMT.
  */
 TMW_API int tmw_prefill_backward(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v,
                                  const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,
