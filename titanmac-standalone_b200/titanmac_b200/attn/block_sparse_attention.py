@@ -53,8 +53,14 @@ class BlockSparseAttention(nn.Module):
         """``[3 * d_model, taps]``: the three depthwise filters in the channel order of the QKV projection."""
         return torch.cat([self.conv_q.weight[:, 0], self.conv_k.weight[:, 0], self.conv_v.weight[:, 0]], dim=0)
 
-    @torch.no_grad()
     def forward(self, x: torch.Tensor, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if torch.is_grad_enabled() and x.requires_grad:
+            raise NotImplementedError("BlockSparseAttention (B200) has no backward pass; run it under "
+                                      "torch.no_grad(), or train with use_block_sparse=False")
+        with torch.no_grad():
+            return self._forward(x)
+
+    def _forward(self, x: torch.Tensor) -> torch.Tensor:
         if not self.causal:
             raise NotImplementedError("causal=False is not supported")
         if self.training and self.dropout_p > 0:
