@@ -124,6 +124,19 @@ TMW_API int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block
                                      const void* v, void* o, void* stream);
 
 /*
+ * tmw_prefill_block_sparse that also returns the row log-sum-exp (see tmw_prefill_lse), and its backward.
+ * lse holds batch x heads x L floats in two planes: [batch, heads, L - n_persistent] for the sequence rows,
+ * followed by [batch, heads, n_persistent] for the persistent rows.  The backward writes dq, dk, dv (addressed
+ * like q, k, v) from d_o (addressed like o): what autograd does through the reference's per-block matmul /
+ * softmax / matmul (block_sparse_attention.py:163-199, 258-343).
+ */
+TMW_API int tmw_prefill_block_sparse_lse(const tmw_prefill_desc* desc, int32_t block_size, const void* q, const void* k,
+                                         const void* v, void* o, float* lse, void* stream);
+TMW_API int tmw_prefill_block_sparse_backward(const tmw_prefill_desc* desc, int32_t block_size, const void* q,
+                                              const void* k, const void* v, const void* o, const void* d_o,
+                                              const float* lse, void* dq, void* dk, void* dv, void* stream);
+
+/*
  * Causal depthwise convolution along the rows: y[b, t, c] = sum_j weight[c, j] * x[b, t - (taps-1) + j, c],
  * rows before the first count as zero.  x, y: [batch, rows, channels] contiguous (channels a multiple of 8,
  * 16-byte aligned); weight: [channels, taps] contiguous, same dtype, 1 <= taps <= 8; y must not overlap x.

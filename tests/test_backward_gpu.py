@@ -86,3 +86,50 @@ def test_block_trains_end_to_end():
     with torch.no_grad():
         y2 = block(x.detach())
     assert (y.detach() - y2).abs().max().item() <= 1e-4
+
+
+def test_block_sparse_module_gradients_match_reference_fp32():
+    from titanmac_b200 import BlockSparseAttention
+
+    z = np.load(os.path.join(HERE, "golden", "block_sparse_backward_golden.npz"))
+    for name in sorted({k.split("/")[0] for k in z.files}):
+        B, T, H, dh, w, bs, Np, _ = (int(v) for v in z[f"{name}/meta"])
+        t = lambda key: torch.from_numpy(z[f"{name}/{key}"])  # noqa: E731
+        mod = BlockSparseAttention(d_model=H * dh, n_heads=H, window_size=w, block_size=bs, n_persistent=Np)
+        mod.load_state_dict({k[len(name) + 4:]: torch.from_numpy(z[k]) for k in z.files if k.startswith(f"{name}/sd/")})
+        mod = mod.to(DEV)
+        x = t("x").to(DEV).requires_grad_(True)
+        y = mod(x)
+        assert (y.detach().cpu() - t("y")).abs().max().item() <= 2e-5, name
+        (y * t("g").to(DEV)).sum().backward()
+        err = (x.grad.cpu() - t("dx")).abs().max().item()
+        assert err <= 3e-5 * max(1.0, t("dx").abs().max().item()), (name, "dx", err)
+        for pname, prm in mod.named_parameters():
+            want = t(f"grad/{pname}")
+            err = (prm.grad.cpu() - want).abs().max().item()
+            assert err <= 3e-5 * max(1.0, want.abs().max().item()), (name, pname, err)
+    _native.poll_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("dh,H,B,T,w,bs,Np", [(64, 2, 1, 700, 128, 64, 16), (128, 1, 1, 400, 100, 32, 5),
+                                               (64, 1, 2, 300, 0, 16, 0)])
+def test_block_sparse_core_gradients_bf16_both_backward_kernels(dh, H, B, T, w, bs, Np):
+    from oracle import block_sparse_oracle as bo
+
+    L = Np + T
+    gen = torch.Generator().manual_seed(dh + T)
+    q, k, v, g = (torch.randn(B, H, L, dh, generator=gen).to(torch.bfloat16) for _ in range(4))
+    qr, kr, vr = (t.float().clone().requires_grad_(True) for t in (q, k, v))
+    (bo.attention_core(qr, kr, vr, w, bs, Np) * g.float()).sum().backward()
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    lse = torch.empty(B * H * L, dtype=torch.float32, device=DEV)
+    o = _native.prefill(qd, kd, vd, w, Np, window_block=bs, lse=lse)
+    d_o = torch.empty_like(o)
+    d_o.copy_(g.to(DEV))
+    for bwd_algo in (_native.ALGO_SIMT, _native.ALGO_AUTO):
+        dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+        _native.prefill_backward(qd, kd, vd, o, d_o, lse, dq, dk, dv, w, Np, algo=bwd_algo, window_block=bs)
+        for got, want, nm in ((dq, qr.grad, "dq"), (dk, kr.grad, "dk"), (dv, vr.grad, "dv")):
+            err = (got.float().cpu() - want).abs().max().item()
+            assert err <= 4e-2 * max(1.0, want.abs().max().item()), (nm, bwd_algo, err)
+    _native.poll_status(torch.device(DEV))

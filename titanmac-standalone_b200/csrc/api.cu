@@ -206,6 +206,31 @@ int tmw_prefill_backward(const tmw_prefill_desc* desc, const void* q, const void
 
 int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block_size, const void* q, const void* k,
                              const void* v, void* o, void* stream) {
+    return tmw_prefill_block_sparse_lse(desc, block_size, q, k, v, o, nullptr, stream);
+}
+
+int tmw_prefill_block_sparse_backward(const tmw_prefill_desc* desc, int32_t block_size, const void* q, const void* k,
+                                      const void* v, const void* o, const void* d_o, const float* lse, void* dq,
+                                      void* dk, void* dv, void* stream) {
+    const int rc = tmw::validate_prefill(desc, q, k, v, o);
+    if (rc != TMW_OK) return rc;
+    if (block_size <= 0 || block_size > (1 << 20)) return TMW_ERR_INVALID_ARGUMENT;
+    if (desc->q_pos0 != 0 || desc->k_pos0 != desc->n_persistent || desc->q_rows != desc->k_rows) {
+        tmw::set_error_text("tmw_prefill_block_sparse_backward: whole sequences only");
+        return TMW_ERR_UNSUPPORTED;
+    }
+    if (desc->batch == 0 || desc->heads == 0 || desc->q_rows == 0) return TMW_OK;
+    if (d_o == nullptr || lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (!tmw::aligned16(d_o) || !tmw::aligned16(dq) || !tmw::aligned16(dk) || !tmw::aligned16(dv))
+        return TMW_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (desc->algo != TMW_ALGO_SIMT && tmw::prefill_backward_mma_supports(*desc))
+        return tmw::launch_prefill_backward_mma(*desc, q, k, v, o, d_o, lse, dq, dk, dv, s, block_size, true);
+    return tmw::launch_prefill_backward(*desc, q, k, v, o, d_o, lse, dq, dk, dv, s, block_size, true);
+}
+
+int tmw_prefill_block_sparse_lse(const tmw_prefill_desc* desc, int32_t block_size, const void* q, const void* k,
+                                 const void* v, void* o, float* lse, void* stream) {
     const int rc = tmw::validate_prefill(desc, q, k, v, o);
     if (rc != TMW_OK) return rc;
     if (block_size <= 0 || block_size > (1 << 20)) {
@@ -222,11 +247,15 @@ int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block_size, c
     const bool tc_ok = tmw::prefill_tc_supports(d, q, k, v, o) && (int64_t)d.q_rows + d.window + block_size < ((int64_t)1 << 29);
     if (d.algo == TMW_ALGO_TCGEN05 && !tc_ok) return TMW_ERR_UNSUPPORTED;
     const bool use_tc = d.algo != TMW_ALGO_SIMT && tc_ok;
-    auto launch = [&](const tmw_prefill_desc& dd, const void* qq, void* oo, cudaStream_t st, bool all_keys) {
-        return use_tc ? tmw::launch_prefill_tc(dd, qq, k, v, oo, st, block_size, all_keys)
-                      : tmw::launch_prefill_simt(dd, qq, k, v, oo, st, block_size, all_keys);
-    };
     const int np = d.n_persistent;
+    // the log-sum-exp comes in two planes: [batch, heads, L - np] for the sequence rows (first launch), then
+    // [batch, heads, np] for the persistent rows (second launch)
+    float* lse_pers = lse != nullptr ? lse + (size_t)d.batch * d.heads * (d.q_rows - np) : nullptr;
+    auto launch = [&](const tmw_prefill_desc& dd, const void* qq, void* oo, cudaStream_t st, bool all_keys) {
+        float* l = all_keys ? lse_pers : lse;
+        return use_tc ? tmw::launch_prefill_tc(dd, qq, k, v, oo, st, block_size, all_keys, l)
+                      : tmw::launch_prefill_simt(dd, qq, k, v, oo, st, block_size, all_keys, l);
+    };
     if (np == 0) return launch(d, q, o, s, false);
     // Two independent launches: the sequence rows [np, L) with the block-granular window, and the np
     // persistent query rows, which see every key (one query tile per (batch, head) walking over all key

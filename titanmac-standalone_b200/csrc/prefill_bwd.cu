@@ -41,9 +41,27 @@ struct BwdParams {
     void* dk;
     void* dv;
     int rows, window, np;  // rows = L
+    int block;        // 0: per-token window; > 0: block-granular left edge (first_visible_pos)
+    int pers_global;  // 1: the np persistent query rows see every key (the block-sparse class); then the
+                      //    log-sum-exp comes in two planes: [batch, heads, rows - np] for the sequence rows,
+                      //    followed by [batch, heads, np] for the persistent rows
     long long qs[3], ks[3], vs[3], os[3];  // q / dq, k / dk, v / dv, o / dO share strides pairwise
     float scale, scale_log2;
 };
+
+// log-sum-exp of query row `row` of (batch b, head h)
+__device__ __forceinline__ float lse_at(const BwdParams& p, int b, int h, int heads, int row) {
+    const long long bh = (long long)b * heads + h;
+    if (!p.pers_global) return p.lse[bh * p.rows + row];
+    if (row >= p.np) return p.lse[bh * (p.rows - p.np) + (row - p.np)];
+    return p.lse[(long long)gridDim.z * heads * (p.rows - p.np) + bh * p.np + row];
+}
+// does the query at position i see the key at position g (g < np: a persistent key)?
+__device__ __forceinline__ bool sees(const BwdParams& p, int i, int g) {
+    if (g < p.np) return true;
+    if (i < p.np) return p.pers_global != 0;
+    return g <= i && g >= first_visible_pos(i, p.np, p.window, p.block);
+}
 
 // this lane's slice of a row: chunks sub, sub + LPR, ... of 8 elements each
 template <typename T, int DH>
@@ -153,14 +171,16 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const BwdParams p) {
         load_slice<T, DH>(og + (long long)row * p.os[2], sub, oreg);
 #pragma unroll
         for (int e = 0; e < S::DPL; ++e) dsum = fmaf(doreg[e], oreg[e], dsum);
-        lse = p.lse[((long long)b * gridDim.y + h) * p.rows + row];
+        lse = lse_at(p, b, h, gridDim.y, row);
     }
     dsum = reduce_row<S::LPR>(dsum);
 
     // virtual key index u: [0, np) persistent keys, then the positions [glo, ghi] of this CTA's windows
     const int p_last = min(r0 + S::ROWS, p.rows) - 1;
-    const int glo = max(p.np, r0 - p.window);
-    const int n_win = p_last >= p.np ? p_last - glo + 1 : 0;
+    const bool all_seq = p.pers_global && r0 < p.np;  // a persistent row in this CTA: every sequence key
+    const int glo = all_seq ? p.np : first_visible_pos(max(r0, p.np), p.np, p.window, p.block);
+    const int ghi = all_seq ? p.rows - 1 : p_last;
+    const int n_win = (all_seq || p_last >= p.np) && ghi >= glo ? ghi - glo + 1 : 0;
     const int n_keys = p.np + n_win;
     for (int u0 = 0; u0 < n_keys; u0 += S::BN) {
         __syncthreads();
@@ -185,7 +205,7 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const BwdParams p) {
             const float dp = reduce_row<S::LPR>(dot_slice<DH>(doreg, v_tile[j], sub));
             const int u = u0 + j;
             const int g = u < p.np ? u : glo + (u - p.np);
-            const bool vis = valid && (u < p.np || (row >= p.np && g <= row && row - g <= p.window));
+            const bool vis = valid && sees(p, row, g);
             const float pj = vis ? exp2f(s * p.scale_log2 - lse) : 0.f;
             axpy_slice<DH>(acc, pj * (dp - dsum), k_tile[j], sub);
         }
@@ -215,8 +235,6 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(const BwdParams p, in
     const T* dog = static_cast<const T*>(p.d_o) + b * p.os[0] + h * p.os[1];
     T* dkg = static_cast<T*>(p.dk) + b * p.ks[0] + h * p.ks[1];
     T* dvg = static_cast<T*>(p.dv) + b * p.vs[0] + h * p.vs[1];
-    const float* lse_g = p.lse + ((long long)b * gridDim.y + h) * p.rows;
-
     float kreg[S::DPL], vreg[S::DPL], dk[S::DPL], dv[S::DPL];
 #pragma unroll
     for (int e = 0; e < S::DPL; ++e) kreg[e] = vreg[e] = dk[e] = dv[e] = 0.f;
@@ -225,14 +243,22 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(const BwdParams p, in
         load_slice<T, DH>(vg + (long long)key * p.vs[2], sub, vreg);
     }
     // query rows that can see a key of this CTA: every row for persistent keys, [k0, last key + window] else
-    const int i_lo = pers_block ? 0 : k0;
-    const int i_hi = pers_block ? p.rows - 1 : (int)min((long long)p.rows - 1, (long long)k_end - 1 + p.window);
+    // A sequence key is seen by the rows from its own position to the last row whose (possibly block-granular)
+    // window still reaches it, and, for the block-sparse class, by the np persistent rows: those come first as
+    // a range of their own ([0, np) never overlaps [k0, ...) because k0 >= np).
+    const int reach = p.window + (p.block > 0 ? p.block - 1 : 0);
+    const int main_lo = pers_block ? 0 : k0;
+    const int main_hi = pers_block ? p.rows - 1 : (int)min((long long)p.rows - 1, (long long)k_end - 1 + reach);
+    const int n_ranges = (!pers_block && p.pers_global && p.np > 0) ? 2 : 1;
+    for (int range = 0; range < n_ranges; ++range) {
+    const int i_lo = (n_ranges == 2 && range == 0) ? 0 : main_lo;
+    const int i_hi = (n_ranges == 2 && range == 0) ? p.np - 1 : main_hi;
     for (int i0 = i_lo; i0 <= i_hi; i0 += S::BN) {
         __syncthreads();
         stage_rows<T, DH, S::BN>(q_tile, qg, p.qs[2], i0, i_hi + 1);
         stage_rows<T, DH, S::BN>(do_tile, dog, p.os[2], i0, i_hi + 1);
         if (tid < S::BN) {
-            lse_s[tid] = i0 + tid <= i_hi ? lse_g[i0 + tid] : 0.f;
+            lse_s[tid] = i0 + tid <= i_hi ? lse_at(p, b, h, gridDim.y, i0 + tid) : 0.f;
             dsum_s[tid] = 0.f;
         }
         __syncthreads();
@@ -255,12 +281,13 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(const BwdParams p, in
             const int i = i0 + j;  // query position
             const float s = reduce_row<S::LPR>(dot_slice<DH>(kreg, q_tile[j], sub));
             const float dp = reduce_row<S::LPR>(dot_slice<DH>(vreg, do_tile[j], sub));
-            const bool vis = valid && (pers_block || (i >= p.np && key <= i && i - key <= p.window));
+            const bool vis = valid && sees(p, i, key);
             const float pj = vis ? exp2f(s * p.scale_log2 - lse_s[j]) : 0.f;
             axpy_slice<DH>(dv, pj, do_tile[j], sub);
             axpy_slice<DH>(dk, pj * (dp - dsum_s[j]), q_tile[j], sub);
         }
     }
+    }  // ranges
     if (valid) {
         store_slice<T, DH>(dkg + (long long)key * p.ks[2], sub, dk, p.scale);
         store_slice<T, DH>(dvg + (long long)key * p.vs[2], sub, dv, 1.0f);
@@ -298,8 +325,11 @@ int launch_dh(const BwdParams& p, int batch, int heads, int dh, cudaStream_t str
 }  // namespace
 
 int launch_prefill_backward(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
-                            const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream) {
+                            const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream,
+                            int window_block, bool pers_global) {
     BwdParams p;
+    p.block = window_block;
+    p.pers_global = pers_global ? 1 : 0;
     p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.lse = lse; p.dq = dq; p.dk = dk; p.dv = dv;
     p.rows = d.q_rows; p.window = d.window; p.np = d.n_persistent;
     for (int i = 0; i < 3; ++i) {

@@ -36,9 +36,20 @@ struct MmaBwdParams {
     void* dk;
     void* dv;
     int rows, window, np;
+    int block;        // 0: per-token window; > 0: block-granular left edge (first_visible_pos)
+    int pers_global;  // 1: the np persistent query rows see every key; lse then comes as
+                      //    [batch, heads, rows - np] followed by [batch, heads, np]
     long long qs[3], ks[3], vs[3], os[3];
     float scale, scale_log2;
 };
+
+// log-sum-exp of query row `row` of (batch b, head h); gridDim.z is the batch size
+__device__ __forceinline__ float lse_at(const MmaBwdParams& p, int b, int h, int heads, int row) {
+    const long long bh = (long long)b * heads + h;
+    if (!p.pers_global) return p.lse[bh * p.rows + row];
+    if (row >= p.np) return p.lse[bh * (p.rows - p.np) + (row - p.np)];
+    return p.lse[(long long)gridDim.z * heads * (p.rows - p.np) + bh * p.np + row];
+}
 
 // Row strides in shared memory, padded by 16 bytes so that the 16 rows a tensor-core tile load touches fall
 // into different banks (an unpadded 128-byte row stride puts all of them on the same ones).
@@ -172,8 +183,8 @@ __device__ __forceinline__ void store_acc(Acc64<DH>& acc, float* stage, T* base,
 
 // lse and D = sum_d dO O of the 64 staged query rows (O tile in `o_tile`, dO tile in `do_tile`)
 template <typename T, int DH>
-__device__ __forceinline__ void row_stats(float* lse_s, float* d_s, const T* o_tile, const T* do_tile, const float* lse_g,
-                                          int i0, int limit) {
+__device__ __forceinline__ void row_stats(float* lse_s, float* d_s, const T* o_tile, const T* do_tile,
+                                          const MmaBwdParams& p, int b, int h, int i0, int limit) {
     // four threads per row
     const int row = threadIdx.x >> 2, part = threadIdx.x & 3;
     float sum = 0.f;
@@ -183,7 +194,7 @@ __device__ __forceinline__ void row_stats(float* lse_s, float* d_s, const T* o_t
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     if (part == 0) {
         d_s[row] = sum;
-        lse_s[row] = i0 + row < limit ? lse_g[i0 + row] : 0.f;
+        lse_s[row] = i0 + row < limit ? lse_at(p, b, h, gridDim.y, i0 + row) : 0.f;
     }
 }
 
@@ -191,13 +202,17 @@ __device__ __forceinline__ void row_stats(float* lse_s, float* d_s, const T* o_t
 // a persistent key; a column is hidden by returning -2.
 template <typename T, int DH, typename KeyPos>
 __device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, const float* dp_s, const float* lse_s,
-                                             const float* d_s, int i0, int rows, int np, int window, float scale_log2,
-                                             KeyPos key_pos) {
+                                             const float* d_s, int i0, int rows, const MmaBwdParams& p, KeyPos key_pos) {
+    const int np = p.np;
+    const float scale_log2 = p.scale_log2;
     for (int e = threadIdx.x; e < 64 * 64; e += kThreadsMma) {
         const int r = e >> 6, c = e & 63;
         const int i = i0 + r;
         const int g = key_pos(c);
-        const bool vis = i < rows && (g == -1 || (g >= 0 && i >= np && g <= i && i - g <= window));
+        // persistent key: always; sequence key: the persistent rows see it only in the block-sparse class, a
+        // sequence row sees it inside its (possibly block-granular) causal window
+        const bool vis = i < rows && (g == -1 || (g >= 0 && (i < np ? p.pers_global != 0
+                                                                    : g <= i && g >= first_visible_pos(i, np, p.window, p.block))));
         const int es = r * Ld<DH>::kS + c, ep = r * Ld<DH>::kP + c;
         float p = 0.f;
         if (vis) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(s_s[es] * scale_log2 - lse_s[r]));
@@ -231,31 +246,39 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdPa
     const T* vg = static_cast<const T*>(p.v) + b * p.vs[0] + h * p.vs[1];
     const T* og = static_cast<const T*>(p.o) + b * p.os[0] + h * p.os[1];
     const T* dog = static_cast<const T*>(p.d_o) + b * p.os[0] + h * p.os[1];
-    const float* lse_g = p.lse + ((long long)b * gridDim.y + h) * p.rows;
-
     load_tile<T, DH>(k_s, kg, p.ks[2], k0, k_end);
     load_tile<T, DH>(v_s, vg, p.vs[2], k0, k_end);
     Acc64<DH> dk, dv;
     dk.zero();
     dv.zero();
-    const int i_lo = pers ? 0 : k0;
-    const int i_hi = pers ? p.rows - 1 : (int)min((long long)p.rows - 1, (long long)k_end - 1 + p.window);
+    // query rows that see these keys: the rows from the key's own position to the last row whose (possibly
+    // block-granular) window reaches it, and in the block-sparse class also the np persistent rows, which come
+    // first as a range of their own ([0, np) never overlaps [k0, ...) because k0 >= np)
+    const int reach = p.window + (p.block > 0 ? p.block - 1 : 0);
+    const int main_lo = pers ? 0 : k0;
+    const int main_hi = pers ? p.rows - 1 : (int)min((long long)p.rows - 1, (long long)k_end - 1 + reach);
+    const int n_ranges = (!pers && p.pers_global && p.np > 0) ? 2 : 1;
     auto key_pos = [&](int c) { return k0 + c < k_end ? (pers ? -1 : k0 + c) : -2; };
+    for (int range = 0; range < n_ranges; ++range) {
+    const bool prefix = n_ranges == 2 && range == 0;
+    const int i_lo = prefix ? 0 : main_lo, i_hi = prefix ? p.np - 1 : main_hi;
+    const int limit = i_hi + 1;  // rows of this range end here (the prefix range must not touch sequence rows)
     for (int i0 = i_lo; i0 <= i_hi; i0 += BR) {
         __syncthreads();  // the previous round's products have read q_s, do_s, p_s, ds_s
-        load_tile<T, DH>(q_s, qg, p.qs[2], i0, p.rows);
-        load_tile<T, DH>(do_s, dog, p.os[2], i0, p.rows);
-        load_tile<T, DH>(p_s, og, p.os[2], i0, p.rows);  // the O tile, in the P / dS buffers for a moment
+        load_tile<T, DH>(q_s, qg, p.qs[2], i0, limit);
+        load_tile<T, DH>(do_s, dog, p.os[2], i0, limit);
+        load_tile<T, DH>(p_s, og, p.os[2], i0, limit);  // the O tile, in the P / dS buffers for a moment
         __syncthreads();
-        row_stats<T, DH>(lse_s, d_s, p_s, do_s, lse_g, i0, p.rows);
+        row_stats<T, DH>(lse_s, d_s, p_s, do_s, p, b, h, i0, limit);
         gemm_abt<T, DH>(s_s, q_s, k_s);
         gemm_abt<T, DH>(dp_s, do_s, v_s);
         __syncthreads();
-        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, p.rows, p.np, p.window, p.scale_log2, key_pos);
+        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, limit, p, key_pos);
         __syncthreads();
         gemm_atb_acc<T, DH>(dv, p_s, do_s);
         gemm_atb_acc<T, DH>(dk, ds_s, q_s);
     }
+    }  // ranges
     __syncthreads();
     T* dkg = static_cast<T*>(p.dk) + b * p.ks[0] + h * p.ks[1];
     T* dvg = static_cast<T*>(p.dv) + b * p.vs[0] + h * p.vs[1];
@@ -287,24 +310,24 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
     const T* vg = static_cast<const T*>(p.v) + b * p.vs[0] + h * p.vs[1];
     const T* og = static_cast<const T*>(p.o) + b * p.os[0] + h * p.os[1];
     const T* dog = static_cast<const T*>(p.d_o) + b * p.os[0] + h * p.os[1];
-    const float* lse_g = p.lse + ((long long)b * gridDim.y + h) * p.rows;
-
     load_tile<T, DH>(q_s, qg, p.qs[2], i0, p.rows);
     load_tile<T, DH>(do_s, dog, p.os[2], i0, p.rows);
     load_tile<T, DH>(p_s, og, p.os[2], i0, p.rows);
     __syncthreads();
-    row_stats<T, DH>(lse_s, d_s, p_s, do_s, lse_g, i0, p.rows);
+    row_stats<T, DH>(lse_s, d_s, p_s, do_s, p, b, h, i0, p.rows);
     Acc64<DH> dq;
     dq.zero();
     // key blocks: the persistent keys in blocks of 64, then the positions [glo, i_last] of this block's windows
     const int i_last = min(i0 + BR, p.rows) - 1;
-    const int glo = max(p.np, i0 - p.window);
+    const bool all_seq = p.pers_global && i0 < p.np;  // a persistent row in this block: every sequence key
+    const int glo = all_seq ? p.np : first_visible_pos(max(i0, p.np), p.np, p.window, p.block);
+    const int ghi = all_seq ? p.rows - 1 : i_last;
     const int n_pers_blocks = (p.np + BC - 1) / BC;
-    const int n_win_blocks = i_last >= p.np ? (i_last - glo) / BC + 1 : 0;
+    const int n_win_blocks = (all_seq || i_last >= p.np) && ghi >= glo ? (ghi - glo) / BC + 1 : 0;
     for (int jb = 0; jb < n_pers_blocks + n_win_blocks; ++jb) {
         const bool pers = jb < n_pers_blocks;
         const int k0 = pers ? jb * BC : glo + (jb - n_pers_blocks) * BC;
-        const int k_end = pers ? min(p.np, k0 + BC) : min(i_last + 1, k0 + BC);
+        const int k_end = pers ? min(p.np, k0 + BC) : min(ghi + 1, k0 + BC);
         __syncthreads();  // the previous round's product has read k_s and ds_s; row_stats has read p_s
         load_tile<T, DH>(k_s, kg, p.ks[2], k0, k_end);
         load_tile<T, DH>(v_s, vg, p.vs[2], k0, k_end);
@@ -313,7 +336,7 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
         gemm_abt<T, DH>(dp_s, do_s, v_s);
         __syncthreads();
         auto key_pos = [&](int c) { return k0 + c < k_end ? (pers ? -1 : k0 + c) : -2; };
-        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, p.rows, p.np, p.window, p.scale_log2, key_pos);
+        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, p.rows, p, key_pos);
         __syncthreads();
         gemm_ab_acc<T, DH>(dq, ds_s, k_s);
     }
@@ -347,8 +370,11 @@ bool prefill_backward_mma_supports(const tmw_prefill_desc& d) {
 }
 
 int launch_prefill_backward_mma(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
-                                const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream) {
+                                const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream,
+                                int window_block, bool pers_global) {
     MmaBwdParams p;
+    p.block = window_block;
+    p.pers_global = pers_global ? 1 : 0;
     p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.lse = lse; p.dq = dq; p.dk = dk; p.dv = dv;
     p.rows = d.q_rows; p.window = d.window; p.np = d.n_persistent;
     for (int i = 0; i < 3; ++i) {

@@ -139,12 +139,16 @@ int launch_prefill_simt(const tmw_prefill_desc& d, const void* q, const void* k,
                         cudaStream_t stream, int window_block = 0, bool all_keys = false, float* lse = nullptr);
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
                       cudaStream_t stream, int window_block = 0, bool all_keys = false, float* lse = nullptr);
+// window_block / pers_global select the mask of the block-sparse class (see first_visible_pos; pers_global: the
+// persistent query rows see every key, and lse comes as [batch, heads, rows - np] followed by [batch, heads, np])
 int launch_prefill_backward(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
-                            const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream);
+                            const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream,
+                            int window_block = 0, bool pers_global = false);
 // the same on the warp-level tensor-core path (16-bit types, head_dim 64 / 128)
 bool prefill_backward_mma_supports(const tmw_prefill_desc& d);
 int launch_prefill_backward_mma(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
-                                const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream);
+                                const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream,
+                                int window_block = 0, bool pers_global = false);
 bool prefill_tc_supports(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o);
 int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, const void* v_new, void* o,
                   const int64_t qs[2], const int64_t ns[2], const int64_t os[2], const int32_t* pos,

@@ -98,6 +98,14 @@ SIGNATURES = {
         ctypes.c_int,
         [ctypes.POINTER(PrefillDesc)] + [ctypes.c_void_p] * 10,
     ),
+    "tmw_prefill_block_sparse_lse": (
+        ctypes.c_int,
+        [ctypes.POINTER(PrefillDesc), ctypes.c_int32] + [ctypes.c_void_p] * 6,
+    ),
+    "tmw_prefill_block_sparse_backward": (
+        ctypes.c_int,
+        [ctypes.POINTER(PrefillDesc), ctypes.c_int32] + [ctypes.c_void_p] * 10,
+    ),
     "tmw_prefill_block_sparse": (
         ctypes.c_int,
         [ctypes.POINTER(PrefillDesc), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
@@ -232,12 +240,15 @@ def prefill(
     d.o_stride[:] = _bhrd_strides(out)
     with torch.cuda.device(q.device):
         if lse is not None:
-            if window_block > 0:
-                raise NotImplementedError("the log-sum-exp output exists for the windowed mask only")
-            if lse.dtype != torch.float32 or lse.shape != (B, H, rq) or not lse.is_contiguous() or lse.device != q.device:
-                raise ValueError("lse must be a contiguous fp32 [B, H, rows] tensor on the same device")
-            check(lib().tmw_prefill_lse(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                        lse.data_ptr(), _stream_ptr(q.device)))
+            if lse.dtype != torch.float32 or lse.numel() != B * H * rq or not lse.is_contiguous() or lse.device != q.device:
+                raise ValueError("lse must be a contiguous fp32 tensor of B * H * rows elements on the same device")
+            if window_block > 0:  # two planes: [B, H, rows - Np] then [B, H, Np]
+                check(lib().tmw_prefill_block_sparse_lse(ctypes.byref(d), window_block, q.data_ptr(), k.data_ptr(),
+                                                         v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                                         _stream_ptr(q.device)))
+            else:
+                check(lib().tmw_prefill_lse(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                            lse.data_ptr(), _stream_ptr(q.device)))
         elif window_block > 0:
             check(lib().tmw_prefill_block_sparse(ctypes.byref(d), window_block, q.data_ptr(), k.data_ptr(),
                                                  v.data_ptr(), out.data_ptr(), _stream_ptr(q.device)))
@@ -249,7 +260,7 @@ def prefill(
 
 def prefill_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor,
                      lse: torch.Tensor, dq: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor, window: int,
-                     n_persistent: int, scale: float = 0.0, algo: int = ALGO_AUTO) -> None:
+                     n_persistent: int, scale: float = 0.0, algo: int = ALGO_AUTO, window_block: int = 0) -> None:
     """``tmw_prefill_backward``: fills ``dq, dk, dv`` (same strides as ``q, k, v``) from ``d_o`` (same strides as
     ``o``), the saved output and the log-sum-exp of ``prefill(..., lse=...)``.  Whole sequences only."""
     _require_cuda(q, k, v, o, d_o, lse, dq, dk, dv)
@@ -257,8 +268,8 @@ def prefill_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch
     for a, b_ in ((dq, q), (dk, k), (dv, v), (d_o, o)):
         if a.shape != b_.shape or a.stride() != b_.stride() or a.dtype != q.dtype:
             raise ValueError("dq, dk, dv, d_o must match q, k, v, o in shape, strides and dtype")
-    if lse.dtype != torch.float32 or lse.shape != (B, H, L) or not lse.is_contiguous():
-        raise ValueError("lse must be a contiguous fp32 [B, H, rows] tensor")
+    if lse.dtype != torch.float32 or lse.numel() != B * H * L or not lse.is_contiguous():
+        raise ValueError("lse must be the contiguous fp32 tensor that prefill(..., lse=...) filled")
     d = PrefillDesc()
     d.dtype = _DTYPES[q.dtype]
     d.algo = algo  # ALGO_SIMT pins the CUDA-core kernels, otherwise tensor cores for 16-bit types and head_dim 64 / 128
@@ -271,9 +282,15 @@ def prefill_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch
     d.v_stride[:] = _bhrd_strides(v)
     d.o_stride[:] = _bhrd_strides(o)
     with torch.cuda.device(q.device):
-        check(lib().tmw_prefill_backward(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                         d_o.data_ptr(), lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                         _stream_ptr(q.device)))
+        if window_block > 0:
+            check(lib().tmw_prefill_block_sparse_backward(ctypes.byref(d), window_block, q.data_ptr(), k.data_ptr(),
+                                                          v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+                                                          dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                                          _stream_ptr(q.device)))
+        else:
+            check(lib().tmw_prefill_backward(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                             d_o.data_ptr(), lse.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                             dv.data_ptr(), _stream_ptr(q.device)))
 
 
 def causal_dwconv(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -12,8 +12,9 @@ that concatenates each block's keys, builds a mask and runs a softmax — is two
 ``tmw_causal_dwconv`` over the whole QKV projection output (the three filters stacked) and
 ``tmw_prefill_block_sparse`` reading Q, K, V as strided views of the result.
 
-Not supported (raises ``NotImplementedError``): ``causal=False``, dropout in training mode, autograd
-through the module.  Like the reference, a caller-supplied ``attn_mask`` is ignored (:218-219).
+Not supported (raises ``NotImplementedError``): ``causal=False`` and dropout in training mode.  With grad
+mode on and a gradient due, the attention core runs as an autograd function (``tmw_prefill_block_sparse_lse`` /
+``tmw_prefill_block_sparse_backward``) and the convolutions as differentiable library calls.  Like the reference, a caller-supplied ``attn_mask`` is ignored (:218-219).
 The ring-cache generation path of ``TitanMAC`` belongs to ``WindowedAttention`` only.
 """
 
@@ -26,6 +27,36 @@ import torch
 import torch.nn as nn
 
 from .. import _native
+
+
+class _BlockSparseCore(torch.autograd.Function):
+    """``qkv [B, L, 3, H, dh]`` (after the convolutions) → ``o [B, L, H, dh]``; backward through
+    ``tmw_prefill_block_sparse_backward``."""
+
+    @staticmethod
+    def forward(ctx, qkv: torch.Tensor, window: int, block: int, n_persistent: int, scale: float, algo: int):
+        qkv = qkv.contiguous()
+        B, L, _, H, dh = qkv.shape
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        o = torch.empty((B, L, H, dh), dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty((B * H * L,), dtype=torch.float32, device=qkv.device)
+        _native.prefill(q, k, v, window, n_persistent, out=o.permute(0, 2, 1, 3), scale=scale, algo=algo,
+                        window_block=block, lse=lse)
+        ctx.save_for_backward(qkv, o, lse)
+        ctx.args = (window, block, n_persistent, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o: torch.Tensor):
+        qkv, o, lse = ctx.saved_tensors
+        window, block, n_persistent, scale = ctx.args
+        d_o = d_o.contiguous()
+        dqkv = torch.empty_like(qkv)
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        dq, dk, dv = (dqkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+        _native.prefill_backward(q, k, v, o.permute(0, 2, 1, 3), d_o.permute(0, 2, 1, 3), lse, dq, dk, dv, window,
+                                 n_persistent, scale=scale, window_block=block)
+        return dqkv, None, None, None, None, None
 
 
 class BlockSparseAttention(nn.Module):
@@ -54,11 +85,32 @@ class BlockSparseAttention(nn.Module):
         return torch.cat([self.conv_q.weight[:, 0], self.conv_k.weight[:, 0], self.conv_v.weight[:, 0]], dim=0)
 
     def forward(self, x: torch.Tensor, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if torch.is_grad_enabled() and x.requires_grad:
-            raise NotImplementedError("BlockSparseAttention (B200) has no backward pass; run it under "
-                                      "torch.no_grad(), or train with use_block_sparse=False")
+        if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
+            return self._forward_train(x)
         with torch.no_grad():
             return self._forward(x)
+
+    def _forward_train(self, x: torch.Tensor) -> torch.Tensor:
+        """Grad mode: the projections and the depthwise convolutions are differentiable library calls, the
+        attention core is an autograd function with its own backward kernels."""
+        if not self.causal:
+            raise NotImplementedError("causal=False is not supported")
+        if self.training and self.dropout_p > 0:
+            raise NotImplementedError("attention dropout in training mode is not supported")
+        if not x.is_cuda:
+            raise RuntimeError("BlockSparseAttention (B200) needs CUDA tensors; there is no CPU path")
+        B, L, D = x.shape
+        if self.n_persistent >= L:
+            raise ValueError(f"n_persistent ({self.n_persistent}) must be < seq_len ({L})")
+        qkv = self.qkv_proj(x)
+        if self.use_conv:
+            w = torch.cat([self.conv_q.weight, self.conv_k.weight, self.conv_v.weight], dim=0)  # [3D, 1, taps]
+            taps = w.shape[-1]
+            qkv = torch.nn.functional.conv1d(qkv.transpose(1, 2), w, padding=taps - 1, groups=3 * D)[:, :, :L]
+            qkv = qkv.transpose(1, 2)
+        o = _BlockSparseCore.apply(qkv.reshape(B, L, 3, self.n_heads, self.d_head), self.window_size, self.block_size,
+                                   self.n_persistent, self.scale, self.algo)
+        return self.dropout(self.out_proj(o.view(B, L, D)))
 
     def _forward(self, x: torch.Tensor) -> torch.Tensor:
         if not self.causal:
