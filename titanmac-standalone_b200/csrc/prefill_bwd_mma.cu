@@ -202,7 +202,8 @@ __device__ __forceinline__ void row_stats(float* lse_s, float* d_s, const T* o_t
 // a persistent key; a column is hidden by returning -2.
 template <typename T, int DH, typename KeyPos>
 __device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, const float* dp_s, const float* lse_s,
-                                             const float* d_s, int i0, int rows, const MmaBwdParams& p, KeyPos key_pos) {
+                                             const float* d_s, int i0, int rows, const MmaBwdParams& p, int wblock,
+                                             bool pers_global, KeyPos key_pos) {
     const int np = p.np;
     const float scale_log2 = p.scale_log2;
     for (int e = threadIdx.x; e < 64 * 64; e += kThreadsMma) {
@@ -211,8 +212,8 @@ __device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, 
         const int g = key_pos(c);
         // persistent key: always; sequence key: the persistent rows see it only in the block-sparse class, a
         // sequence row sees it inside its (possibly block-granular) causal window
-        const bool vis = i < rows && (g == -1 || (g >= 0 && (i < np ? p.pers_global != 0
-                                                                    : g <= i && g >= first_visible_pos(i, np, p.window, p.block))));
+        const bool vis = i < rows && (g == -1 || (g >= 0 && (i < np ? pers_global
+                                                                    : g <= i && g >= first_visible_pos(i, np, p.window, wblock))));
         const int es = r * Ld<DH>::kS + c, ep = r * Ld<DH>::kP + c;
         float p = 0.f;
         if (vis) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(s_s[es] * scale_log2 - lse_s[r]));
@@ -222,9 +223,13 @@ __device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, 
 }
 
 // ---------------------------------------------------------------------------------------------------------
-template <typename T, int DH>
+// GENERAL = false: the plain windowed mask, every mode parameter a compile-time constant (the block-sparse
+// logic costs the common case nothing); GENERAL = true: block-granular window and global persistent rows.
+template <typename T, int DH, bool GENERAL>
 __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdParams p, int n_seq_blocks) {
     using L = MmaSmem<T, DH>;
+    const int wblock = GENERAL ? p.block : 0;
+    const bool pers_global = GENERAL && p.pers_global != 0;
     extern __shared__ __align__(128) unsigned char smem[];
     T* k_s = reinterpret_cast<T*>(smem + L::kK);
     T* v_s = reinterpret_cast<T*>(smem + L::kV);
@@ -254,10 +259,10 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdPa
     // query rows that see these keys: the rows from the key's own position to the last row whose (possibly
     // block-granular) window reaches it, and in the block-sparse class also the np persistent rows, which come
     // first as a range of their own ([0, np) never overlaps [k0, ...) because k0 >= np)
-    const int reach = p.window + (p.block > 0 ? p.block - 1 : 0);
+    const int reach = p.window + (wblock > 0 ? wblock - 1 : 0);
     const int main_lo = pers ? 0 : k0;
     const int main_hi = pers ? p.rows - 1 : (int)min((long long)p.rows - 1, (long long)k_end - 1 + reach);
-    const int n_ranges = (!pers && p.pers_global && p.np > 0) ? 2 : 1;
+    const int n_ranges = (!pers && pers_global && p.np > 0) ? 2 : 1;
     auto key_pos = [&](int c) { return k0 + c < k_end ? (pers ? -1 : k0 + c) : -2; };
     for (int range = 0; range < n_ranges; ++range) {
     const bool prefix = n_ranges == 2 && range == 0;
@@ -273,7 +278,7 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdPa
         gemm_abt<T, DH>(s_s, q_s, k_s);
         gemm_abt<T, DH>(dp_s, do_s, v_s);
         __syncthreads();
-        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, limit, p, key_pos);
+        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, limit, p, wblock, pers_global, key_pos);
         __syncthreads();
         gemm_atb_acc<T, DH>(dv, p_s, do_s);
         gemm_atb_acc<T, DH>(dk, ds_s, q_s);
@@ -288,9 +293,11 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdPa
 }
 
 // ---------------------------------------------------------------------------------------------------------
-template <typename T, int DH>
+template <typename T, int DH, bool GENERAL>
 __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdParams p) {
     using L = MmaSmem<T, DH>;
+    const int wblock = GENERAL ? p.block : 0;
+    const bool pers_global = GENERAL && p.pers_global != 0;
     extern __shared__ __align__(128) unsigned char smem[];
     T* k_s = reinterpret_cast<T*>(smem + L::kK);
     T* v_s = reinterpret_cast<T*>(smem + L::kV);
@@ -319,8 +326,8 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
     dq.zero();
     // key blocks: the persistent keys in blocks of 64, then the positions [glo, i_last] of this block's windows
     const int i_last = min(i0 + BR, p.rows) - 1;
-    const bool all_seq = p.pers_global && i0 < p.np;  // a persistent row in this block: every sequence key
-    const int glo = all_seq ? p.np : first_visible_pos(max(i0, p.np), p.np, p.window, p.block);
+    const bool all_seq = pers_global && i0 < p.np;  // a persistent row in this block: every sequence key
+    const int glo = all_seq ? p.np : first_visible_pos(max(i0, p.np), p.np, p.window, wblock);
     const int ghi = all_seq ? p.rows - 1 : i_last;
     const int n_pers_blocks = (p.np + BC - 1) / BC;
     const int n_win_blocks = (all_seq || i_last >= p.np) && ghi >= glo ? (ghi - glo) / BC + 1 : 0;
@@ -336,7 +343,7 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
         gemm_abt<T, DH>(dp_s, do_s, v_s);
         __syncthreads();
         auto key_pos = [&](int c) { return k0 + c < k_end ? (pers ? -1 : k0 + c) : -2; };
-        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, p.rows, p, key_pos);
+        softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, p.rows, p, wblock, pers_global, key_pos);
         __syncthreads();
         gemm_ab_acc<T, DH>(dq, ds_s, k_s);
     }
@@ -348,8 +355,9 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
 template <typename T, int DH>
 int launch_mma(const MmaBwdParams& p, int batch, int heads, cudaStream_t stream) {
     using L = MmaSmem<T, DH>;
-    auto kq = bwd_mma_dq_kernel<T, DH>;
-    auto kkv = bwd_mma_dkv_kernel<T, DH>;
+    const bool general = p.block > 0 || p.pers_global != 0;
+    auto kq = general ? bwd_mma_dq_kernel<T, DH, true> : bwd_mma_dq_kernel<T, DH, false>;
+    auto kkv = general ? bwd_mma_dkv_kernel<T, DH, true> : bwd_mma_dkv_kernel<T, DH, false>;
     TMW_CUDA_TRY(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     TMW_CUDA_TRY(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     const dim3 gq((p.rows + BR - 1) / BR, heads, batch);
