@@ -6,7 +6,10 @@ tokens prepended to every sequence (:608-619), the block stack (:629-640), final
 norm, tied LM head over all rows and the slice that drops the persistent rows
 (:652-662), optional shifted cross-entropy (:674-684).  Parameter names match the
 reference (``embed_tokens``, ``embed_positions``, ``persistent_tokens``,
-``layers.N...``, ``norm``, ``lm_head``), so its checkpoints load.
+``layers.N...``, ``norm``, ``lm_head``), so its checkpoints load.  Under
+``torch.no_grad()`` the fused inference kernels run; with grad mode on the same call
+is differentiable (the attention cores through their own backward kernels, norms and
+GELU through PyTorch), so ``forward(ids, labels=...)["loss"].backward()`` trains.
 
 ``prefill`` / ``decode_step`` / ``generate`` are new: the reference has no KV cache,
 its generation helper re-runs the whole forward for every new token
@@ -68,7 +71,6 @@ class TitanMAC(nn.Module):
             x = torch.cat([self.persistent_tokens[None].expand(B, -1, -1), x], dim=1)
         return x
 
-    @torch.no_grad()
     def forward(self, input_ids: torch.Tensor, labels: Optional[torch.Tensor] = None,
                 attention_mask: Optional[torch.Tensor] = None) -> Dict[str, torch.Tensor]:
         Np = self.config.n_persistent
