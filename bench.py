@@ -56,6 +56,9 @@ WORKLOADS = {
                                                dtype="bf16", block_size=64, conv_taps=4),
     # config 2's layer, forward + backward (gradients of the input and of both weights)
     "config2_layer_train": dict(batch=8, T=4096, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16"),
+    # the same with the reference's default (block-sparse) attention class
+    "config2_block_sparse_layer_train": dict(batch=8, T=4096, d_model=640, heads=10, window=512, n_persistent=16,
+                                             dtype="bf16", block_size=64, conv_taps=4),
     # benchmark configuration 3: whole 16-layer model forward (prefill), 2 sequences of 8192 tokens per GPU
     "config3_model_prefill": dict(batch=2, T=8192, d_model=640, heads=10, window=512, n_persistent=16, dtype="bf16",
                                   layers=16, d_ff=2560, vocab=50000),
@@ -674,7 +677,17 @@ def run_train(args, wl_name: str, wl: dict) -> None:
     B, T, D, H, w, Np = wl["batch"], wl["T"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
     L = Np + T
     x_cpu, w_qkv, w_out = wo.layer_inputs(B, T, D, Np, seed=rank)
-    mod = WindowedAttention(WindowConfig(window_size=w, num_heads=H, head_dim=D // H, n_persistent=Np))
+    bs = wl.get("block_size", 0)
+    if bs:
+        from titanmac_b200 import BlockSparseAttention
+
+        mod = BlockSparseAttention(d_model=D, n_heads=H, window_size=w, block_size=bs, n_persistent=Np,
+                                   conv_kernel=wl["conv_taps"])
+        with torch.no_grad():
+            for conv, wt in zip((mod.conv_q, mod.conv_k, mod.conv_v), block_sparse_conv_weights(wl, seed=rank)):
+                conv.weight.copy_(wt[:, None, :])
+    else:
+        mod = WindowedAttention(WindowConfig(window_size=w, num_heads=H, head_dim=D // H, n_persistent=Np))
     with torch.no_grad():
         mod.qkv_proj.weight.copy_(w_qkv)
         mod.out_proj.weight.copy_(w_out)
@@ -710,19 +723,19 @@ def run_train(args, wl_name: str, wl: dict) -> None:
     # the backward kernels alone (saved tensors of one forward)
     qkv = torch.randn(B, L, 3, H, D // H, device=dev).to(torch.bfloat16)
     q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
-    lse = torch.empty(B, H, L, dtype=torch.float32, device=dev)
-    o = _native.prefill(q, k, v, w, Np, lse=lse)
+    lse = torch.empty(B * H * L, dtype=torch.float32, device=dev)
+    o = _native.prefill(q, k, v, w, Np, lse=lse, window_block=bs)
     d_o = torch.empty_like(o)
     d_o.normal_()
     dqkv = torch.empty_like(qkv)
     dq, dk, dv = (dqkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
     for _ in range(2):
-        _native.prefill_backward(q, k, v, o, d_o, lse, dq, dk, dv, w, Np)
+        _native.prefill_backward(q, k, v, o, d_o, lse, dq, dk, dv, w, Np, window_block=bs)
     c, d_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n_core = 5
     c.record()
     for _ in range(n_core):
-        _native.prefill_backward(q, k, v, o, d_o, lse, dq, dk, dv, w, Np)
+        _native.prefill_backward(q, k, v, o, d_o, lse, dq, dk, dv, w, Np, window_block=bs)
     d_.record()
     torch.cuda.synchronize()
     core_ms = c.elapsed_time(d_) / n_core
@@ -903,7 +916,7 @@ def main() -> None:
                                   "the CPU reference arm is timed on the layer workloads only"}), flush=True)
             return
         run_reference_arm(args, args.workload, wl)
-    elif args.workload == "config2_layer_train":
+    elif args.workload in ("config2_layer_train", "config2_block_sparse_layer_train"):
         run_train(args, args.workload, wl)
     elif args.workload == "config3_model_prefill":
         run_model_prefill(args, args.workload, wl)
