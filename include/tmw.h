@@ -148,6 +148,14 @@ TMW_API int tmw_causal_dwconv(int32_t dtype, int32_t batch, int32_t rows, int32_
                               const void* x, const void* weight, void* y, void* stream);
 
 /*
+ * Backward of tmw_causal_dwconv: dx (like x) and dw (fp32 [channels, taps], ADDED to: zero it first) from dy.
+ * Replaces autograd through the three Conv1d calls of block_sparse_attention.py:241-256.
+ */
+TMW_API int tmw_causal_dwconv_backward(int32_t dtype, int32_t batch, int32_t rows, int32_t channels, int32_t taps,
+                                       const void* x, const void* weight, const void* dy, void* dx, float* dw,
+                                       void* stream);
+
+/*
  * Decode: one new token per sequence against a ring cache of the last window+1
  * keys.  The reference has no incremental decode (its generation helper re-runs
  * the full forward per token, examples/train_math.py:146-161); this entry point

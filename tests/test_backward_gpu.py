@@ -154,3 +154,22 @@ def test_model_trains_end_to_end(block_sparse):
     with torch.no_grad():
         ref = model(ids)["logits"]
     assert (out["logits"].detach() - ref).abs().max().item() <= 2e-3
+
+
+@pytest.mark.parametrize("taps", [1, 4, 6])
+def test_convolution_backward_against_oracle_autograd(taps):
+    from oracle import block_sparse_oracle as bo
+
+    gen = torch.Generator().manual_seed(taps)
+    x = torch.randn(2, 150, 3 * 64, generator=gen)
+    w = torch.randn(3 * 64, taps, generator=gen) * 0.5
+    dy = torch.randn(2, 150, 3 * 64, generator=gen)
+    xr, wr = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    (bo.causal_dwconv(xr, wr) * dy).sum().backward()
+    dx, dw = _native.causal_dwconv_backward(x.to(DEV), w.to(DEV), dy.to(DEV))
+    assert (dx.cpu() - xr.grad).abs().max().item() <= 1e-5
+    assert (dw.cpu() - wr.grad).abs().max().item() <= 1e-4 * max(1.0, wr.grad.abs().max().item())
+    dx16, dw16 = _native.causal_dwconv_backward(x.to(torch.bfloat16).to(DEV), w.to(torch.bfloat16).to(DEV),
+                                                dy.to(torch.bfloat16).to(DEV))
+    assert (dx16.float().cpu() - xr.grad).abs().max().item() <= 6e-2
+    assert (dw16.float().cpu() - wr.grad).abs().max().item() <= 2e-2 * max(1.0, wr.grad.abs().max().item())

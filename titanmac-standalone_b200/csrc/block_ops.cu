@@ -239,6 +239,113 @@ int launch_dwconv_taps(int batch, int rows, int channels, const void* x, const v
     return TMW_OK;
 }
 
+// Backward of the convolution.  dx[t] = sum_j w[j] dy[t + (TAPS-1) - j] looks ahead, so a thread walks its strip
+// of rows from the bottom up with the TAPS rows dy[t .. t+TAPS-1] in registers.  dw[c][j] = sum over batch and rows
+// of dy[t][c] x[t - (TAPS-1) + j][c]: a thread accumulates its strip's share and adds it to an fp32 buffer
+// [channels, TAPS] (zero on entry) with atomics.
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(kConvThreads)
+dwconv_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ dy, T* __restrict__ dx,
+                  float* __restrict__ dw, int rows, int channels) {
+    const int vec = blockIdx.x * kConvThreads + threadIdx.x;
+    if (vec * 8 >= channels) return;
+    const int t0 = blockIdx.y * kConvStrip;
+    const int t1 = min(rows, t0 + kConvStrip);
+    const long long base = (long long)blockIdx.z * rows * channels + vec * 8;
+    float wr[TAPS][8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) wr[j][c] = to_f32<T>(w[(long long)(vec * 8 + c) * TAPS + j]);
+    // ---- dx: bottom-up, ahead[m] = dy[t + m]
+    float ahead[TAPS][8];
+#pragma unroll
+    for (int m = 0; m < TAPS - 1; ++m) {  // the state "before" row t1 - 1: dy[t1 + m]
+        if (t1 + m < rows) {
+            load8<T>(dy + base + (long long)(t1 + m) * channels, ahead[m]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) ahead[m][c] = 0.f;
+        }
+    }
+    for (int t = t1 - 1; t >= t0; --t) {
+#pragma unroll
+        for (int m = TAPS - 1; m >= 1; --m)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) ahead[m][c] = ahead[m - 1][c];
+        load8<T>(dy + base + (long long)t * channels, ahead[0]);
+        float out[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            float a = 0.f;
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) a = fmaf(wr[j][c], ahead[TAPS - 1 - j][c], a);
+            out[c] = a;
+        }
+        store8<T>(dx + base + (long long)t * channels, out);
+    }
+    // ---- dw: top-down like the forward, hist[j] = x[t - (TAPS-1) + j]
+    float hist[TAPS][8], acc[TAPS][8];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[j][c] = 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) {
+        const int t = t0 - (TAPS - 1) + j;
+        if (t >= 0) {
+            load8<T>(x + base + (long long)t * channels, hist[j + 1]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) hist[j + 1][c] = 0.f;
+        }
+    }
+    for (int t = t0; t < t1; ++t) {
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; ++j)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) hist[j][c] = hist[j + 1][c];
+        load8<T>(x + base + (long long)t * channels, hist[TAPS - 1]);
+        float g[8];
+        load8<T>(dy + base + (long long)t * channels, g);
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[j][c] = fmaf(g[c], hist[j][c], acc[j][c]);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) atomicAdd(dw + (long long)(vec * 8 + c) * TAPS + j, acc[j][c]);
+}
+
+template <typename T, int TAPS>
+int launch_dwconv_bwd_taps(int batch, int rows, int channels, const void* x, const void* w, const void* dy, void* dx,
+                           float* dw, cudaStream_t stream) {
+    const dim3 grid((channels / 8 + kConvThreads - 1) / kConvThreads, (rows + kConvStrip - 1) / kConvStrip, batch);
+    dwconv_bwd_kernel<T, TAPS><<<grid, kConvThreads, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(w),
+                                                                  static_cast<const T*>(dy), static_cast<T*>(dx), dw,
+                                                                  rows, channels);
+    TMW_CUDA_TRY(cudaGetLastError());
+    return TMW_OK;
+}
+
+template <typename T>
+int launch_dwconv_bwd(int batch, int rows, int channels, int taps, const void* x, const void* w, const void* dy,
+                      void* dx, float* dw, cudaStream_t stream) {
+    switch (taps) {
+        case 1: return launch_dwconv_bwd_taps<T, 1>(batch, rows, channels, x, w, dy, dx, dw, stream);
+        case 2: return launch_dwconv_bwd_taps<T, 2>(batch, rows, channels, x, w, dy, dx, dw, stream);
+        case 3: return launch_dwconv_bwd_taps<T, 3>(batch, rows, channels, x, w, dy, dx, dw, stream);
+        case 4: return launch_dwconv_bwd_taps<T, 4>(batch, rows, channels, x, w, dy, dx, dw, stream);
+        case 5: return launch_dwconv_bwd_taps<T, 5>(batch, rows, channels, x, w, dy, dx, dw, stream);
+        case 6: return launch_dwconv_bwd_taps<T, 6>(batch, rows, channels, x, w, dy, dx, dw, stream);
+        case 7: return launch_dwconv_bwd_taps<T, 7>(batch, rows, channels, x, w, dy, dx, dw, stream);
+        case 8: return launch_dwconv_bwd_taps<T, 8>(batch, rows, channels, x, w, dy, dx, dw, stream);
+        default: return TMW_ERR_UNSUPPORTED;
+    }
+}
+
 template <typename T>
 int launch_dwconv(int batch, int rows, int channels, int taps, const void* x, const void* w, void* y,
                   cudaStream_t stream) {
@@ -279,6 +386,26 @@ extern "C" int tmw_causal_dwconv(int32_t dtype, int32_t batch, int32_t rows, int
         case TMW_F32: return launch_dwconv<float>(batch, rows, channels, taps, x, weight, y, s);
         case TMW_BF16: return launch_dwconv<__nv_bfloat16>(batch, rows, channels, taps, x, weight, y, s);
         default: return launch_dwconv<__half>(batch, rows, channels, taps, x, weight, y, s);
+    }
+}
+
+extern "C" int tmw_causal_dwconv_backward(int32_t dtype, int32_t batch, int32_t rows, int32_t channels, int32_t taps,
+                                          const void* x, const void* weight, const void* dy, void* dx, float* dw,
+                                          void* stream) {
+    using namespace tmw;
+    if (batch < 0 || rows < 0 || channels <= 0) return TMW_ERR_INVALID_ARGUMENT;
+    if (dtype != TMW_F32 && dtype != TMW_BF16 && dtype != TMW_F16) return TMW_ERR_INVALID_ARGUMENT;
+    if (taps < 1 || taps > 8 || channels % 8 != 0) return TMW_ERR_UNSUPPORTED;
+    if (batch == 0 || rows == 0) return TMW_OK;
+    if (x == nullptr || weight == nullptr || dy == nullptr || dx == nullptr || dw == nullptr || dx == dy)
+        return TMW_ERR_INVALID_ARGUMENT;
+    if ((((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dx) & 15) != 0) return TMW_ERR_INVALID_ARGUMENT;
+    if (batch > 65535 || (rows + kConvStrip - 1) / kConvStrip > 65535) return TMW_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case TMW_F32: return launch_dwconv_bwd<float>(batch, rows, channels, taps, x, weight, dy, dx, dw, s);
+        case TMW_BF16: return launch_dwconv_bwd<__nv_bfloat16>(batch, rows, channels, taps, x, weight, dy, dx, dw, s);
+        default: return launch_dwconv_bwd<__half>(batch, rows, channels, taps, x, weight, dy, dx, dw, s);
     }
 }
 

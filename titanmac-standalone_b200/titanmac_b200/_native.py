@@ -111,6 +111,10 @@ SIGNATURES = {
         [ctypes.POINTER(PrefillDesc), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
          ctypes.c_void_p, ctypes.c_void_p],
     ),
+    "tmw_causal_dwconv_backward": (
+        ctypes.c_int,
+        [ctypes.c_int32] * 5 + [ctypes.c_void_p] * 6,
+    ),
     "tmw_causal_dwconv": (
         ctypes.c_int,
         [ctypes.c_int32] * 5 + [ctypes.c_void_p] * 4,
@@ -405,6 +409,25 @@ class RingCache:
                 check(lib().tmw_decode(ctypes.byref(c), q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
                                        out.data_ptr(), qs, ns, os_, pos.data_ptr(), _stream_ptr(self.device)))
         return out
+
+
+def causal_dwconv_backward(x: torch.Tensor, weight: torch.Tensor, dy: torch.Tensor):
+    """Gradients of ``causal_dwconv``: returns ``(dx like x, dw [C, taps] in weight's dtype)``."""
+    _require_cuda(x, weight, dy)
+    x = x if x.is_contiguous() else x.contiguous()
+    dy = dy if dy.is_contiguous() else dy.contiguous()
+    weight = weight if weight.is_contiguous() else weight.contiguous()
+    if dy.shape != x.shape or dy.dtype != x.dtype or weight.dtype != x.dtype:
+        raise ValueError("causal_dwconv_backward: x, dy of one shape and dtype, weight of the same dtype")
+    B, T, C = x.shape
+    dx = torch.empty_like(x)
+    dw = torch.zeros((C, weight.shape[1]), dtype=torch.float32, device=x.device)
+    if B and T:
+        with torch.cuda.device(x.device):
+            check(lib().tmw_causal_dwconv_backward(_DTYPES[x.dtype], B, T, C, weight.shape[1], x.data_ptr(),
+                                                   weight.data_ptr(), dy.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                                                   _stream_ptr(x.device)))
+    return dx, dw.to(weight.dtype)
 
 
 def gelu_supported(x: torch.Tensor) -> bool:

@@ -14,7 +14,7 @@ that concatenates each block's keys, builds a mask and runs a softmax — is two
 
 Not supported (raises ``NotImplementedError``): ``causal=False`` and dropout in training mode.  With grad
 mode on and a gradient due, the attention core runs as an autograd function (``tmw_prefill_block_sparse_lse`` /
-``tmw_prefill_block_sparse_backward``) and the convolutions as differentiable library calls.  Like the reference, a caller-supplied ``attn_mask`` is ignored (:218-219).
+``tmw_prefill_block_sparse_backward``), and so do the convolutions (``tmw_causal_dwconv_backward``).  Like the reference, a caller-supplied ``attn_mask`` is ignored (:218-219).
 The ring-cache generation path of ``TitanMAC`` belongs to ``WindowedAttention`` only.
 """
 
@@ -27,6 +27,21 @@ import torch
 import torch.nn as nn
 
 from .. import _native
+
+
+class _CausalDwConv(torch.autograd.Function):
+    """``tmw_causal_dwconv`` with ``tmw_causal_dwconv_backward``: ``x [B, T, C]``, ``weight [C, taps]``."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        x, weight = x.contiguous(), weight.contiguous()
+        ctx.save_for_backward(x, weight)
+        return _native.causal_dwconv(x, weight)
+
+    @staticmethod
+    def backward(ctx, dy: torch.Tensor):
+        x, weight = ctx.saved_tensors
+        return _native.causal_dwconv_backward(x, weight, dy)
 
 
 class _BlockSparseCore(torch.autograd.Function):
@@ -91,8 +106,8 @@ class BlockSparseAttention(nn.Module):
             return self._forward(x)
 
     def _forward_train(self, x: torch.Tensor) -> torch.Tensor:
-        """Grad mode: the projections and the depthwise convolutions are differentiable library calls, the
-        attention core is an autograd function with its own backward kernels."""
+        """Grad mode: the projections are differentiable library calls; the depthwise convolutions and the attention
+        core are autograd functions with their own backward kernels."""
         if not self.causal:
             raise NotImplementedError("causal=False is not supported")
         if self.training and self.dropout_p > 0:
@@ -104,10 +119,7 @@ class BlockSparseAttention(nn.Module):
             raise ValueError(f"n_persistent ({self.n_persistent}) must be < seq_len ({L})")
         qkv = self.qkv_proj(x)
         if self.use_conv:
-            w = torch.cat([self.conv_q.weight, self.conv_k.weight, self.conv_v.weight], dim=0)  # [3D, 1, taps]
-            taps = w.shape[-1]
-            qkv = torch.nn.functional.conv1d(qkv.transpose(1, 2), w, padding=taps - 1, groups=3 * D)[:, :, :L]
-            qkv = qkv.transpose(1, 2)
+            qkv = _CausalDwConv.apply(qkv, self.stacked_conv_weight())
         o = _BlockSparseCore.apply(qkv.reshape(B, L, 3, self.n_heads, self.d_head), self.window_size, self.block_size,
                                    self.n_persistent, self.scale, self.algo)
         return self.dropout(self.out_proj(o.view(B, L, D)))
