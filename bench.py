@@ -69,7 +69,9 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention-core kernel,
 # taken from the ncu capture summarised under profiles/ (None until captured)
-NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126459392 + 24759296}
+NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126459392 + 24759296,
+                     # backward: the dQ kernel plus the dK/dV kernel (one call launches both)
+                     "config2_layer_train": (211875584 + 31798784) + (245088000 + 71269632)}
 
 
 def live_pairs(L: int, w: int, Np: int) -> int:
@@ -783,9 +785,9 @@ def run_train(args, wl_name: str, wl: dict) -> None:
                            l2="inputs rotate over 4 sets; activations + gradients per step > 126 MB L2",
                            flops_per_step_per_gpu=flops),
             "roofline": {"bound": "tensor", "kernel": "attention-core backward (tmw_prefill_backward: dQ and dK/dV "
-                         "kernels on CUDA cores, fp32)", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                         "kernels, warp-level tensor cores)", "achieved": achieved, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                         "peak_source": f"{peaks['source']} bf16 burst", "avg_launch_ms": core_ms, "traffic": None,
+                         "peak_source": f"{peaks['source']} bf16 burst", "avg_launch_ms": core_ms, "traffic": NCU_TRAFFIC_BYTES.get(wl_name),
                          "algorithmic_flops_per_launch": flops["core_bwd"]},
             "e2e": {"value": flops["total"] * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": 2 * x_host.numel() * 2, "d2h_bytes_per_step": dx_host.numel() * 2,
