@@ -89,6 +89,23 @@ __device__ __forceinline__ void load_tile(T* tile, const T* base, long long row_
     }
 }
 
+// the same copy with cp.async: 16 bytes per request straight into shared memory, no register staging, so all
+// requests of a round's tiles are in flight at once; rows at or beyond `limit` are zero-filled (source size 0)
+template <typename T, int DH>
+__device__ __forceinline__ void load_tile_async(T* tile, const T* base, long long row_stride, int r0, int limit) {
+    constexpr int CPR = DH / 8;
+    for (int c = threadIdx.x; c < 64 * CPR; c += kThreadsMma) {
+        const int j = c / CPR, col = (c % CPR) * 8;
+        const bool live = r0 + j < limit;
+        const T* src = live ? base + (long long)(r0 + j) * row_stride + col : base;
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(tile + j * Ld<DH>::kT + col);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(live ? 16 : 0) : "memory");
+    }
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
 // out[64 x 64] (fp32, shared) = A[64 x DH] * B[64 x DH]^T, both 16-bit row-major tiles; 8 warps, 16 x 32 each
 template <typename T, int DH>
 __device__ __forceinline__ void gemm_abt(float* out, const T* a, const T* b) {
@@ -270,9 +287,11 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdPa
     const int limit = i_hi + 1;  // rows of this range end here (the prefix range must not touch sequence rows)
     for (int i0 = i_lo; i0 <= i_hi; i0 += BR) {
         __syncthreads();  // the previous round's products have read q_s, do_s, p_s, ds_s
-        load_tile<T, DH>(q_s, qg, p.qs[2], i0, limit);
-        load_tile<T, DH>(do_s, dog, p.os[2], i0, limit);
-        load_tile<T, DH>(p_s, og, p.os[2], i0, limit);  // the O tile, in the P / dS buffers for a moment
+        load_tile_async<T, DH>(q_s, qg, p.qs[2], i0, limit);
+        load_tile_async<T, DH>(do_s, dog, p.os[2], i0, limit);
+        load_tile_async<T, DH>(p_s, og, p.os[2], i0, limit);  // the O tile, in the P / dS buffers for a moment
+        async_commit();
+        async_wait<0>();
         __syncthreads();
         row_stats<T, DH>(lse_s, d_s, p_s, do_s, p, b, h, i0, limit);
         gemm_abt<T, DH>(s_s, q_s, k_s);
@@ -299,8 +318,6 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
     const int wblock = GENERAL ? p.block : 0;
     const bool pers_global = GENERAL && p.pers_global != 0;
     extern __shared__ __align__(128) unsigned char smem[];
-    T* k_s = reinterpret_cast<T*>(smem + L::kK);
-    T* v_s = reinterpret_cast<T*>(smem + L::kV);
     T* q_s = reinterpret_cast<T*>(smem + L::kQ);
     T* do_s = reinterpret_cast<T*>(smem + L::kDO);
     T* p_s = reinterpret_cast<T*>(smem + L::kP);
@@ -331,13 +348,35 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
     const int ghi = all_seq ? p.rows - 1 : i_last;
     const int n_pers_blocks = (p.np + BC - 1) / BC;
     const int n_win_blocks = (all_seq || i_last >= p.np) && ghi >= glo ? (ghi - glo) / BC + 1 : 0;
-    for (int jb = 0; jb < n_pers_blocks + n_win_blocks; ++jb) {
+    // K and V tiles alternate between two buffer pairs: round jb + 1's tiles are requested (cp.async) before
+    // round jb computes
+    T* k_buf[2] = {reinterpret_cast<T*>(smem + L::kK), reinterpret_cast<T*>(smem + L::kBytes)};
+    T* v_buf[2] = {reinterpret_cast<T*>(smem + L::kV), reinterpret_cast<T*>(smem + L::kBytes + L::kTile)};
+    const int n_blocks = n_pers_blocks + n_win_blocks;
+    auto block_range = [&](int jb, int& k0, int& k_end) {
         const bool pers = jb < n_pers_blocks;
-        const int k0 = pers ? jb * BC : glo + (jb - n_pers_blocks) * BC;
-        const int k_end = pers ? min(p.np, k0 + BC) : min(ghi + 1, k0 + BC);
-        __syncthreads();  // the previous round's product has read k_s and ds_s; row_stats has read p_s
-        load_tile<T, DH>(k_s, kg, p.ks[2], k0, k_end);
-        load_tile<T, DH>(v_s, vg, p.vs[2], k0, k_end);
+        k0 = pers ? jb * BC : glo + (jb - n_pers_blocks) * BC;
+        k_end = pers ? min(p.np, k0 + BC) : min(ghi + 1, k0 + BC);
+    };
+    auto request = [&](int jb) {
+        if (jb < n_blocks) {
+            int k0, k_end;
+            block_range(jb, k0, k_end);
+            load_tile_async<T, DH>(k_buf[jb & 1], kg, p.ks[2], k0, k_end);
+            load_tile_async<T, DH>(v_buf[jb & 1], vg, p.vs[2], k0, k_end);
+        }
+        async_commit();  // an empty group past the end keeps the wait count uniform
+    };
+    request(0);
+    for (int jb = 0; jb < n_blocks; ++jb) {
+        const bool pers = jb < n_pers_blocks;
+        int k0, k_end;
+        block_range(jb, k0, k_end);
+        T* k_s = k_buf[jb & 1];
+        T* v_s = v_buf[jb & 1];
+        __syncthreads();  // the previous round's product has read the other K buffer and ds_s; row_stats has read p_s
+        request(jb + 1);
+        async_wait<1>();  // this round's tiles have landed (the next round's may still be in flight)
         __syncthreads();
         gemm_abt<T, DH>(s_s, q_s, k_s);
         gemm_abt<T, DH>(dp_s, do_s, v_s);
@@ -358,10 +397,11 @@ int launch_mma(const MmaBwdParams& p, int batch, int heads, cudaStream_t stream)
     const bool general = p.block > 0 || p.pers_global != 0;
     auto kq = general ? bwd_mma_dq_kernel<T, DH, true> : bwd_mma_dq_kernel<T, DH, false>;
     auto kkv = general ? bwd_mma_dkv_kernel<T, DH, true> : bwd_mma_dkv_kernel<T, DH, false>;
-    TMW_CUDA_TRY(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    constexpr int kDqBytes = L::kBytes + 2 * L::kTile;  // second K / V buffer pair
+    TMW_CUDA_TRY(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqBytes));
     TMW_CUDA_TRY(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
     const dim3 gq((p.rows + BR - 1) / BR, heads, batch);
-    kq<<<gq, kThreadsMma, L::kBytes, stream>>>(p);
+    kq<<<gq, kThreadsMma, kDqBytes, stream>>>(p);
     TMW_CUDA_TRY(cudaGetLastError());
     const int n_seq = (p.rows - p.np + BC - 1) / BC, n_pers = (p.np + BC - 1) / BC;
     const dim3 gk(n_seq + n_pers, heads, batch);
