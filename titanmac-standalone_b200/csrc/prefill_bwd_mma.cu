@@ -243,15 +243,13 @@ __device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, 
 // GENERAL = false: the plain windowed mask, every mode parameter a compile-time constant (the block-sparse
 // logic costs the common case nothing); GENERAL = true: block-granular window and global persistent rows.
 template <typename T, int DH, bool GENERAL>
-__global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdParams p, int n_seq_blocks) {
+__global__ void __launch_bounds__(kThreadsMma, DH == 64 ? 2 : 1) bwd_mma_dkv_kernel(const MmaBwdParams p, int n_seq_blocks) {
     using L = MmaSmem<T, DH>;
     const int wblock = GENERAL ? p.block : 0;
     const bool pers_global = GENERAL && p.pers_global != 0;
     extern __shared__ __align__(128) unsigned char smem[];
     T* k_s = reinterpret_cast<T*>(smem + L::kK);
     T* v_s = reinterpret_cast<T*>(smem + L::kV);
-    T* q_s = reinterpret_cast<T*>(smem + L::kQ);
-    T* do_s = reinterpret_cast<T*>(smem + L::kDO);
     T* p_s = reinterpret_cast<T*>(smem + L::kP);
     T* ds_s = reinterpret_cast<T*>(smem + L::kDS);
     float* s_s = reinterpret_cast<float*>(smem + L::kS);
@@ -275,34 +273,81 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dkv_kernel(const MmaBwdPa
     dv.zero();
     // query rows that see these keys: the rows from the key's own position to the last row whose (possibly
     // block-granular) window reaches it, and in the block-sparse class also the np persistent rows, which come
-    // first as a range of their own ([0, np) never overlaps [k0, ...) because k0 >= np)
+    // first as rounds of their own ([0, np) never overlaps [k0, ...) because k0 >= np; their rows end at np so
+    // that a prefix round never touches sequence rows)
     const int reach = p.window + (wblock > 0 ? wblock - 1 : 0);
     const int main_lo = pers ? 0 : k0;
     const int main_hi = pers ? p.rows - 1 : (int)min((long long)p.rows - 1, (long long)k_end - 1 + reach);
-    const int n_ranges = (!pers && pers_global && p.np > 0) ? 2 : 1;
+    const int n_prefix = (!pers && pers_global && p.np > 0) ? (p.np + BR - 1) / BR : 0;
+    const int n_rounds = n_prefix + (main_hi - main_lo) / BR + 1;
+    auto round_rows = [&](int r, int& i0, int& limit) {
+        if (r < n_prefix) {
+            i0 = r * BR;
+            limit = p.np;
+        } else {
+            i0 = main_lo + (r - n_prefix) * BR;
+            limit = main_hi + 1;
+        }
+    };
+    // Q and dO tiles alternate between two buffer pairs: round r + 1's tiles are requested (cp.async) before
+    // round r computes
+    auto q_buf = [&](int r) { return reinterpret_cast<T*>(smem + ((r & 1) ? L::kBytes : L::kQ)); };
+    auto do_buf = [&](int r) { return reinterpret_cast<T*>(smem + ((r & 1) ? L::kBytes + L::kTile : L::kDO)); };
+    auto request = [&](int r) {
+        if (r < n_rounds) {
+            int i0, limit;
+            round_rows(r, i0, limit);
+            load_tile_async<T, DH>(q_buf(r), qg, p.qs[2], i0, limit);
+            load_tile_async<T, DH>(do_buf(r), dog, p.os[2], i0, limit);
+        }
+        async_commit();  // an empty group past the end keeps the wait count uniform
+    };
     auto key_pos = [&](int c) { return k0 + c < k_end ? (pers ? -1 : k0 + c) : -2; };
-    for (int range = 0; range < n_ranges; ++range) {
-    const bool prefix = n_ranges == 2 && range == 0;
-    const int i_lo = prefix ? 0 : main_lo, i_hi = prefix ? p.np - 1 : main_hi;
-    const int limit = i_hi + 1;  // rows of this range end here (the prefix range must not touch sequence rows)
-    for (int i0 = i_lo; i0 <= i_hi; i0 += BR) {
-        __syncthreads();  // the previous round's products have read q_s, do_s, p_s, ds_s
-        load_tile_async<T, DH>(q_s, qg, p.qs[2], i0, limit);
-        load_tile_async<T, DH>(do_s, dog, p.os[2], i0, limit);
-        load_tile_async<T, DH>(p_s, og, p.os[2], i0, limit);  // the O tile, in the P / dS buffers for a moment
-        async_commit();
+    // D = sum_d dO O per query row: four threads per row, each with DH / 4 elements of O straight from global
+    // memory in registers (requested before the round's barrier, used after the first two products)
+    const int st_row = threadIdx.x >> 2, st_col = (threadIdx.x & 3) * (DH / 4);
+    constexpr int OV = DH / 32;
+    request(0);
+    for (int r = 0; r < n_rounds; ++r) {
+        int i0, limit;
+        round_rows(r, i0, limit);
+        T* q_s = q_buf(r);
+        T* do_s = do_buf(r);
+        const bool st_live = i0 + st_row < limit;
+        uint4 o_reg[OV];
+#pragma unroll
+        for (int e = 0; e < OV; ++e)
+            o_reg[e] = st_live ? *reinterpret_cast<const uint4*>(og + (long long)(i0 + st_row) * p.os[2] + st_col + e * 8)
+                               : make_uint4(0, 0, 0, 0);
+        const float st_lse = st_live ? lse_at(p, b, h, gridDim.y, i0 + st_row) : 0.f;
         async_wait<0>();
-        __syncthreads();
-        row_stats<T, DH>(lse_s, d_s, p_s, do_s, p, b, h, i0, limit);
+        __syncthreads();  // this round's Q / dO have landed; the previous round's products have read the other
+                          // buffer pair, p_s and ds_s
+        request(r + 1);
         gemm_abt<T, DH>(s_s, q_s, k_s);
         gemm_abt<T, DH>(dp_s, do_s, v_s);
+        {
+            float sum = 0.f;
+#pragma unroll
+            for (int e = 0; e < OV; ++e) {
+                const T* ov = reinterpret_cast<const T*>(&o_reg[e]);
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    sum = fmaf(to_f32<T>(ov[x]), to_f32<T>(do_s[st_row * Ld<DH>::kT + st_col + e * 8 + x]), sum);
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if ((threadIdx.x & 3) == 0) {
+                d_s[st_row] = sum;
+                lse_s[st_row] = st_lse;
+            }
+        }
         __syncthreads();
         softmax_grad<T, DH>(p_s, ds_s, s_s, dp_s, lse_s, d_s, i0, limit, p, wblock, pers_global, key_pos);
         __syncthreads();
         gemm_atb_acc<T, DH>(dv, p_s, do_s);
         gemm_atb_acc<T, DH>(dk, ds_s, q_s);
     }
-    }  // ranges
     __syncthreads();
     T* dkg = static_cast<T*>(p.dk) + b * p.ks[0] + h * p.ks[1];
     T* dvg = static_cast<T*>(p.dv) + b * p.vs[0] + h * p.vs[1];
@@ -350,8 +395,8 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
     const int n_win_blocks = (all_seq || i_last >= p.np) && ghi >= glo ? (ghi - glo) / BC + 1 : 0;
     // K and V tiles alternate between two buffer pairs: round jb + 1's tiles are requested (cp.async) before
     // round jb computes
-    T* k_buf[2] = {reinterpret_cast<T*>(smem + L::kK), reinterpret_cast<T*>(smem + L::kBytes)};
-    T* v_buf[2] = {reinterpret_cast<T*>(smem + L::kV), reinterpret_cast<T*>(smem + L::kBytes + L::kTile)};
+    auto k_buf = [&](int jb) { return reinterpret_cast<T*>(smem + ((jb & 1) ? L::kBytes : L::kK)); };
+    auto v_buf = [&](int jb) { return reinterpret_cast<T*>(smem + ((jb & 1) ? L::kBytes + L::kTile : L::kV)); };
     const int n_blocks = n_pers_blocks + n_win_blocks;
     auto block_range = [&](int jb, int& k0, int& k_end) {
         const bool pers = jb < n_pers_blocks;
@@ -362,8 +407,8 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
         if (jb < n_blocks) {
             int k0, k_end;
             block_range(jb, k0, k_end);
-            load_tile_async<T, DH>(k_buf[jb & 1], kg, p.ks[2], k0, k_end);
-            load_tile_async<T, DH>(v_buf[jb & 1], vg, p.vs[2], k0, k_end);
+            load_tile_async<T, DH>(k_buf(jb), kg, p.ks[2], k0, k_end);
+            load_tile_async<T, DH>(v_buf(jb), vg, p.vs[2], k0, k_end);
         }
         async_commit();  // an empty group past the end keeps the wait count uniform
     };
@@ -372,8 +417,8 @@ __global__ void __launch_bounds__(kThreadsMma) bwd_mma_dq_kernel(const MmaBwdPar
         const bool pers = jb < n_pers_blocks;
         int k0, k_end;
         block_range(jb, k0, k_end);
-        T* k_s = k_buf[jb & 1];
-        T* v_s = v_buf[jb & 1];
+        T* k_s = k_buf(jb);
+        T* v_s = v_buf(jb);
         __syncthreads();  // the previous round's product has read the other K buffer and ds_s; row_stats has read p_s
         request(jb + 1);
         async_wait<1>();  // this round's tiles have landed (the next round's may still be in flight)
@@ -397,15 +442,15 @@ int launch_mma(const MmaBwdParams& p, int batch, int heads, cudaStream_t stream)
     const bool general = p.block > 0 || p.pers_global != 0;
     auto kq = general ? bwd_mma_dq_kernel<T, DH, true> : bwd_mma_dq_kernel<T, DH, false>;
     auto kkv = general ? bwd_mma_dkv_kernel<T, DH, true> : bwd_mma_dkv_kernel<T, DH, false>;
-    constexpr int kDqBytes = L::kBytes + 2 * L::kTile;  // second K / V buffer pair
+    constexpr int kDqBytes = L::kBytes + 2 * L::kTile;  // second buffer pair: K / V in the dQ kernel, Q / dO in the other
     TMW_CUDA_TRY(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqBytes));
-    TMW_CUDA_TRY(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes));
+    TMW_CUDA_TRY(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqBytes));
     const dim3 gq((p.rows + BR - 1) / BR, heads, batch);
     kq<<<gq, kThreadsMma, kDqBytes, stream>>>(p);
     TMW_CUDA_TRY(cudaGetLastError());
     const int n_seq = (p.rows - p.np + BC - 1) / BC, n_pers = (p.np + BC - 1) / BC;
     const dim3 gk(n_seq + n_pers, heads, batch);
-    kkv<<<gk, kThreadsMma, L::kBytes, stream>>>(p, n_seq);
+    kkv<<<gk, kThreadsMma, kDqBytes, stream>>>(p, n_seq);
     TMW_CUDA_TRY(cudaGetLastError());
     return TMW_OK;
 }
