@@ -111,3 +111,38 @@ def test_config4_full_batch_decode_step_sampled_sequences():
     k_before[:, :, slot] = qkv[:, 1]
     v_before[:, :, slot] = qkv[:, 2]
     assert torch.equal(cache.k_ring, k_before) and torch.equal(cache.v_ring, v_before)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("block", [0, 64])
+def test_config2_full_size_backward_invariants(block):
+    """Backward at the full size of benchmark configuration 2 (dense autograd over 4112 x 4112 pairs is the
+    thing being replaced), through identities that hold for any mask because every row of P sums to one:
+      sum_j dV_j = sum_i dO_i                       (dV = P^T dO)
+      sum_i Q_i . dQ_i = sum_j K_j . dK_j           (both are scale * sum_ij dS_ij Q_i . K_j)
+      backward(2 dO) = 2 backward(dO)               (linear in dO)
+    per (sequence, head), for the windowed mask and the block-sparse one."""
+    B, H, dh, w, Np, T = 8, 10, 64, 512, 16, 4096
+    L = Np + T
+    q, k, v = device_inputs(B, H, L, dh, seed=21)
+    like = lambda t: torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=DEV)  # noqa: E731
+    lse = torch.empty((B, H, L), dtype=torch.float32, device=DEV)
+    o = _native.prefill(q, k, v, w, Np, window_block=block, lse=lse)
+    d_o = like(o).copy_(device_inputs(B, H, L, dh, seed=22)[0])
+    grads = []
+    for mul in (1.0, 2.0):
+        dq, dk, dv = like(q), like(k), like(v)
+        _native.prefill_backward(q, k, v, o, like(o).copy_(d_o.float() * mul), lse, dq, dk, dv, w, Np, window_block=block)
+        grads.append((dq.float(), dk.float(), dv.float()))
+    _native.poll_status(torch.device(DEV))
+    dq, dk, dv = grads[0]
+    # column sums over 4112 bf16-rounded rows: compare relative to the size of the terms summed
+    lhs, rhs = dv.sum(dim=2), d_o.float().sum(dim=2)
+    assert ((lhs - rhs).abs().max() / d_o.float().abs().sum(dim=2).max()).item() < 3e-4
+    a = (q.float() * dq).sum(dim=(2, 3))
+    b = (k.float() * dk).sum(dim=(2, 3))
+    denom = (q.float() * dq).abs().sum(dim=(2, 3))
+    assert ((a - b).abs() / denom).max().item() < 1e-3
+    for g1, g2 in zip(grads[0], grads[1]):
+        assert ((2 * g1 - g2).abs().max() / g2.abs().max()).item() < 1e-2  # one bf16 rounding of each side
+    assert all(torch.isfinite(g).all().item() for g in grads[0])
