@@ -9,7 +9,9 @@
 //   dV += P^T dO        dK += dS^T Q               dQ += dS K
 //
 // Everything between the products goes through shared memory, which keeps the fragment layouts of the wmma
-// API opaque; it is a plain kernel, not a pipelined one.  Whole sequences only, like the CUDA-core version.
+// API opaque.  The tiles a kernel walks over (K / V in the dQ kernel, Q / dO in the dK/dV kernel) are requested
+// one pair ahead with cp.async into a second buffer pair, so a round's loads overlap the previous round's
+// products.  Whole sequences only, like the CUDA-core version.
 #include <math_constants.h>
 #include <mma.h>
 
