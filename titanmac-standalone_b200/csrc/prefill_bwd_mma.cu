@@ -225,19 +225,30 @@ __device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, 
                                              bool pers_global, KeyPos key_pos) {
     const int np = p.np;
     const float scale_log2 = p.scale_log2;
-    for (int e = threadIdx.x; e < 64 * 64; e += kThreadsMma) {
-        const int r = e >> 6, c = e & 63;
+    // two adjacent columns per thread: 8-byte reads of S and dP, 4-byte writes of P and dS (a warp covers one row)
+    for (int e = threadIdx.x; e < 64 * 32; e += kThreadsMma) {
+        const int r = e >> 5, c = (e & 31) * 2;
         const int i = i0 + r;
-        const int g = key_pos(c);
-        // persistent key: always; sequence key: the persistent rows see it only in the block-sparse class, a
-        // sequence row sees it inside its (possibly block-granular) causal window
-        const bool vis = i < rows && (g == -1 || (g >= 0 && (i < np ? pers_global
-                                                                    : g <= i && g >= first_visible_pos(i, np, p.window, wblock))));
         const int es = r * Ld<DH>::kS + c, ep = r * Ld<DH>::kP + c;
-        float p = 0.f;
-        if (vis) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(s_s[es] * scale_log2 - lse_s[r]));
-        p_s[ep] = from_f32<T>(p);
-        ds_s[ep] = from_f32<T>(p * (dp_s[es] - d_s[r]));
+        const float2 s2 = *reinterpret_cast<const float2*>(s_s + es);
+        const float2 dp2 = *reinterpret_cast<const float2*>(dp_s + es);
+        const float sv[2] = {s2.x, s2.y}, dpv[2] = {dp2.x, dp2.y};
+        const int lo = i >= np ? first_visible_pos(i, np, p.window, wblock) : 0;
+        const float lse = lse_s[r], d = d_s[r];
+        T pr[2], dsr[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int g = key_pos(c + x);
+            // persistent key: always; sequence key: the persistent rows see it only in the block-sparse class, a
+            // sequence row sees it inside its (possibly block-granular) causal window
+            const bool vis = i < rows && (g == -1 || (g >= 0 && (i < np ? pers_global : g <= i && g >= lo)));
+            float pv = 0.f;
+            if (vis) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pv) : "f"(sv[x] * scale_log2 - lse));
+            pr[x] = from_f32<T>(pv);
+            dsr[x] = from_f32<T>(pv * (dpv[x] - d));
+        }
+        *reinterpret_cast<uint32_t*>(p_s + ep) = *reinterpret_cast<const uint32_t*>(pr);
+        *reinterpret_cast<uint32_t*>(ds_s + ep) = *reinterpret_cast<const uint32_t*>(dsr);
     }
 }
 
