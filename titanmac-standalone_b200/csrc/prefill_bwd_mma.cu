@@ -225,19 +225,24 @@ __device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, 
                                              bool pers_global, KeyPos key_pos) {
     const int np = p.np;
     const float scale_log2 = p.scale_log2;
-    // two adjacent columns per thread: 8-byte reads of S and dP, 4-byte writes of P and dS (a warp covers one row)
-    for (int e = threadIdx.x; e < 64 * 32; e += kThreadsMma) {
-        const int r = e >> 5, c = (e & 31) * 2;
+    // four adjacent columns per thread (a warp covers two whole rows): 16-byte reads of S and dP, 8-byte writes of
+    // P and dS; the padded row strides keep both aligned
+    constexpr int CW = 4, TPR = 64 / CW;
+    static_assert(Ld<DH>::kS % 4 == 0 && Ld<DH>::kP % 4 == 0, "row strides must keep 16-byte / 8-byte alignment");
+    for (int e = threadIdx.x; e < 64 * TPR; e += kThreadsMma) {
+        const int r = e / TPR, c = (e % TPR) * CW;
         const int i = i0 + r;
         const int es = r * Ld<DH>::kS + c, ep = r * Ld<DH>::kP + c;
-        const float2 s2 = *reinterpret_cast<const float2*>(s_s + es);
-        const float2 dp2 = *reinterpret_cast<const float2*>(dp_s + es);
-        const float sv[2] = {s2.x, s2.y}, dpv[2] = {dp2.x, dp2.y};
+        __align__(16) float sv[CW];
+        __align__(16) float dpv[CW];
+        *reinterpret_cast<float4*>(sv) = *reinterpret_cast<const float4*>(s_s + es);
+        *reinterpret_cast<float4*>(dpv) = *reinterpret_cast<const float4*>(dp_s + es);
         const int lo = i >= np ? first_visible_pos(i, np, p.window, wblock) : 0;
         const float lse = lse_s[r], d = d_s[r];
-        T pr[2], dsr[2];
+        __align__(8) T pr[CW];
+        __align__(8) T dsr[CW];
 #pragma unroll
-        for (int x = 0; x < 2; ++x) {
+        for (int x = 0; x < CW; ++x) {
             const int g = key_pos(c + x);
             // persistent key: always; sequence key: the persistent rows see it only in the block-sparse class, a
             // sequence row sees it inside its (possibly block-granular) causal window
@@ -247,8 +252,8 @@ __device__ __forceinline__ void softmax_grad(T* p_s, T* ds_s, const float* s_s, 
             pr[x] = from_f32<T>(pv);
             dsr[x] = from_f32<T>(pv * (dpv[x] - d));
         }
-        *reinterpret_cast<uint32_t*>(p_s + ep) = *reinterpret_cast<const uint32_t*>(pr);
-        *reinterpret_cast<uint32_t*>(ds_s + ep) = *reinterpret_cast<const uint32_t*>(dsr);
+        *reinterpret_cast<uint2*>(p_s + ep) = *reinterpret_cast<const uint2*>(pr);
+        *reinterpret_cast<uint2*>(ds_s + ep) = *reinterpret_cast<const uint2*>(dsr);
     }
 }
 
