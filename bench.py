@@ -71,7 +71,7 @@ WORKLOADS = {
 # taken from the ncu capture summarised under profiles/ (None until captured)
 NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126459392 + 24759296,
                      # backward: the dQ kernel plus the dK/dV kernel (one call launches both)
-                     "config2_layer_train": (211873792 + 32027136) + (242003712 + 70183680)}
+                     "config2_layer_train": (211887360 + 32490752) + (235155200 + 69292800)}
 
 
 def live_pairs(L: int, w: int, Np: int) -> int:
