@@ -123,6 +123,26 @@ def test_sharded_positions_match_unsharded_rows(algo):
         assert (part.float() - full[:, :, r0:r1].float()).abs().max().item() <= 1e-2, (r0, r1)
 
 
+@pytest.mark.parametrize("dh", [64, 128])
+def test_rows_behind_a_short_persistent_block_are_never_multiplied(dh):
+    """8 persistent keys fill half of the 16-row persistent tile of the tensor-core kernel.  The sequence rows
+    right behind them (here: NaN, like a halo that has not arrived yet) lie outside the window of the queries
+    asked for, so they must not reach the output - not even as 0 x NaN inside a matrix product."""
+    L, w, Np, B, H = 1100, 100, 8, 1, 2
+    q, k, v = (t.to(torch.bfloat16) for t in wo.qkv_inputs(B, H, L, dh, seed=11))
+    r0 = Np + 8 + w + 5  # the first query whose window starts behind the poisoned rows
+    ref = wo.attention_core_rows(q[:, :, r0:].float(), k.float(), v.float(), r0, w, Np)
+    kp, vp = k.clone(), v.clone()
+    kp[:, :, Np:Np + 8] = float("nan")
+    vp[:, :, Np:Np + 8] = float("nan")
+    o = _native.prefill(q[:, :, r0:].contiguous().to(DEV), kp.to(DEV), vp.to(DEV), w, Np, q_pos0=r0, k_pos0=Np,
+                        algo=_native.ALGO_TCGEN05)
+    _native.poll_status()
+    assert not torch.isnan(o).any()
+    err = (o.float().cpu() - ref).abs().max().item()
+    assert err <= BF16_TOL, err
+
+
 def test_two_kernels_agree_at_full_size_config2_tcgen05():
     """benchmark configuration 2 (B8, L=16+4096, 10 heads x 64, w=512): the two independent CUDA kernels agree,
     and sampled rows agree with the CPU oracle."""

@@ -56,20 +56,10 @@ struct Budget {
 constexpr int BM = 128;  // query rows per tile
 constexpr int BN = 128;  // keys per tile
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
-#ifndef TMW_POLY_OF4
-#define TMW_POLY_OF4 0
-#endif
-// Of every 4 column pairs, how many take the polynomial exp2 on the FMA pipe instead of the MUFU unit.
-// Measured on config 2's core: 0 -> 146 us, 1 -> 152 us, 2 -> 166 us (the polynomial costs 14 instructions per
-// pair against 2, and with two CTAs per SM the MUFU unit is not the limit), so it is off.
-constexpr int kPolyOf4 = TMW_POLY_OF4;
-#ifndef TMW_ALTERNATE
-#define TMW_ALTERNATE 2
-#endif
-// the two softmax groups take turns with their exponentials: 0 never, 1 always, 2 only for head_dim 128
-// (measured: +10 % at head_dim 128 / window 1024, -6 % at head_dim 64 / window 512)
+// The two softmax groups of a two-tile CTA take turns with their exponentials for head_dim 128 (measured: +10 %
+// at head_dim 128 / window 1024, -6 % at head_dim 64 / window 512, where it is off).
 template <int DH>
-struct Alternate { static constexpr bool value = TMW_ALTERNATE == 1 || (TMW_ALTERNATE == 2 && DH == 128); };  // of every 4 column pairs, how many take the polynomial exp2
+struct Alternate { static constexpr bool value = DH == 128; };
 
 // tensor-memory columns (32-bit each, 128 lanes): S0 | S1 | O0 | O1; P aliases S
 // head_dim 64 : S0 0 | S1 128 | P0 256 | P1 320 | O0 384 | O1 448   (P has its own columns: the next QK
@@ -90,13 +80,6 @@ struct TmemMap {
     }
 };
 
-#ifdef TMW_TRACE
-// Build-time instrumentation (never part of the shipped library): clock stamps of one CTA.
-__device__ long long g_trace[4096];
-#define TRACE(slot) do { if (trace_on) g_trace[(slot)] = clock64(); } while (0)
-#else
-#define TRACE(slot) do { } while (0)
-#endif
 
 struct TcParams {
     int q_rows, k_rows, window, np, np_pad, q_pos0, k_pos0;
@@ -210,29 +193,6 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     uint64_t d;
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
-}
-
-// exp2 of two values on the FMA pipe instead of the MUFU unit: round to the nearest integer j with
-// the 1.5 * 2^23 trick, evaluate a cubic for 2^f on f = x - j in [-0.5, 0.5] (relative error 7.5e-5,
-// far below the 16-bit rounding of P) and add j to the exponent field.  x is clamped at -126.
-__device__ __forceinline__ uint64_t poly_exp2_x2(uint64_t x) {
-    float x0, x1;
-    unpack2(x, x0, x1);
-    x = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-    const uint64_t magic = pack2(12582912.f, 12582912.f);
-    const uint64_t neg_magic = pack2(-12582912.f, -12582912.f);
-    const uint64_t fx = add2(x, magic);
-    const uint64_t j = add2(fx, neg_magic);
-    const uint64_t f = fma2(j, pack2(-1.f, -1.f), x);
-    uint64_t pl = fma2(pack2(0.0551716648042202f, 0.0551716648042202f), f, pack2(0.2426111251115799f, 0.2426111251115799f));
-    pl = fma2(pl, f, pack2(0.6932609677314758f, 0.6932609677314758f));
-    pl = fma2(pl, f, pack2(0.9999280571937561f, 0.9999280571937561f));
-    float p0, p1, f0, f1;
-    unpack2(pl, p0, p1);
-    unpack2(fx, f0, f1);
-    const float e0 = __int_as_float(__float_as_int(p0) + (__float_as_int(f0) << 23));
-    const float e1 = __int_as_float(__float_as_int(p1) + (__float_as_int(f1) << 23));
-    return pack2(e0, e1);
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -422,10 +382,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int wblock = GENERAL ? p.block : 0;
     const bool all_keys = GENERAL && p.all_keys != 0;
     const CtaPlan plan = make_plan(p, blockIdx.x, TILES, wblock, all_keys);
-#ifdef TMW_TRACE
-    const bool trace_on = blockIdx.x == 8 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
-    if (trace_on && threadIdx.x == 0) g_trace[0] = clock64();
-#endif
 
     if (threadIdx.x == 0) {
         // the tensor maps live in the kernel parameters; fetch them into the descriptor cache early
@@ -507,6 +463,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             }
         } else if (warp == 1) {
             // ---------------- producer: persistent K/V, then V tiles ----------------
+            // (the persistent maps end at row np: rows np .. np_pad - 1 of the tile arrive as zeros)
             if (p.np > 0 && leader) {
                 mbar_expect_tx(bar(BAR_KP_FULL), 2 * pers_bytes);
                 int c1, c2;
@@ -655,18 +612,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                         mbar_wait(bar(BAR_S_FREE + t), i & 1, abort_flag, p.status);
                         qk_win();
                     }
-                    TRACE(100 + (i * 2 + t) * 4 + 0);
                     mbar_wait(p_bar, i & 1, abort_flag, p.status);
-                    TRACE(100 + (i * 2 + t) * 4 + 1);
                     if (i < q.has_pers) pv_pers(); else pv_win(i > 0 ? 1u : 0u);
-                    TRACE(100 + (i * 2 + t) * 4 + 2);
                     if (TM::kSplitP) {
                         if (leader) tc_commit(bar(i + 1 < q.n_items ? BAR_PV_DONE + t : BAR_O_DONE + t));
                     } else {
                         if (i + 1 < q.n_items) qk_win();
                         else if (leader) tc_commit(bar(BAR_O_DONE + t));
                     }
-                    TRACE(100 + (i * 2 + t) * 4 + 3);
                 }
             }
             // hand back the stages of the tiles behind my last one (or all of them if I had none)
@@ -732,10 +685,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     hid[c] = __all_sync(0xffffffffu, j_hi - c * 32 < 0 || j_lo - c * 32 > 31);
             }
 
-            TRACE(1000 + t * 500 + item * 8 + 0 + ((warp & 3) ? 2000 : 0));
             mbar_wait(bar(BAR_S_FULL + t), item & 1, abort_flag, p.status);
             tc_fence_after();
-            TRACE(1000 + t * 500 + item * 8 + 1 + ((warp & 3) ? 2000 : 0));
 
             uint32_t s[4][32];
 #pragma unroll
@@ -748,7 +699,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(BAR_S_FREE + t));
             }
-            TRACE(1000 + t * 500 + item * 8 + 2 + ((warp & 3) ? 2000 : 0));
 
             // mask (only the chunks in which some row of the warp has a hidden key), then the row maximum
             // over four independent chains of 3-input max
@@ -806,9 +756,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
             }
 
-            TRACE(1000 + t * 500 + item * 8 + 3 + ((warp & 3) ? 2000 : 0));
-            // P = exp2(S * c - m), packed two 16-bit values per column, written over S.  kPolyOf4 of every
-            // four column pairs take the polynomial on the FMA pipe, the others the MUFU unit.
+            // P = exp2(S * c - m) on the special-function unit, packed two 16-bit values per column
             const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
             const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
             const uint64_t negm2 = pack2(neg_m, neg_m);
@@ -828,19 +776,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     for (int i = 0; i < 16; ++i) {
                         const uint64_t x = fma2(pack2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
                                                 scale2, negm2);
-                        uint64_t e;
-                        float e0, e1;
-                        if ((i & 3) < kPolyOf4) {
-                            e = poly_exp2_x2(x);
-                            unpack2(e, e0, e1);
-                        } else {
-                            float x0, x1;
-                            unpack2(x, x0, x1);
-                            e0 = fast_exp2(x0);
-                            e1 = fast_exp2(x1);
-                            e = pack2(e0, e1);
-                        }
-                        lacc[i & 1] = add2(lacc[i & 1], e);
+                        float x0, x1;
+                        unpack2(x, x0, x1);
+                        const float e0 = fast_exp2(x0);
+                        const float e1 = fast_exp2(x1);
+                        lacc[i & 1] = add2(lacc[i & 1], pack2(e0, e1));
                         if (BF16) {
                             const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                             packed[i] = *reinterpret_cast<const uint32_t*>(&h);
@@ -857,7 +797,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 unpack2(lacc[1], a2, a3);
                 l_sum += (a0 + a1) + (a2 + a3);
             }
-            TRACE(1000 + t * 500 + item * 8 + 4 + ((warp & 3) ? 2000 : 0));
             if (kAlternate) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(other_turn);
@@ -866,7 +805,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(BAR_P_READY + t));
-            TRACE(1000 + t * 500 + item * 8 + 5 + ((warp & 3) ? 2000 : 0));
         }
 
         for (int r = q.n_items; r < rounds; ++r) {  // keep the hand-over going for the group with more items
@@ -879,7 +817,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             // ---------------- epilogue: O / l -> shared memory (swizzled) -> TMA store ----------------
             mbar_wait(bar(BAR_O_DONE + t), 0, abort_flag, p.status);
             tc_fence_after();
-            TRACE(1 + t * 4 + ((warp & 3) ? 2000 : 0));
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
             if (p.lse != nullptr && row < q.rows)
                 p.lse[((long long)batch * gridDim.y + head) * p.q_rows + (blockIdx.x * TILES + t) * BM + row] =
@@ -921,7 +858,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                     tma_store_4d(&map_o, smem_u32(stage + u * L::kSubTileBytes), u * 64, c1, c2, batch);
                 tma_store_commit_and_wait();
             }
-            TRACE(2 + t * 4 + ((warp & 3) ? 2000 : 0));
         }
     }
 
@@ -959,32 +895,77 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Map over a [batch, heads, rows, dh] tensor given by element strides {batch, head, row}; the two
-// middle axes are ordered by stride.  Returns false on failure; sets *heads_first.
+// Strides (in elements) that the tensor maps of a [batch, heads, rows, dh] tensor use.  The stride of an
+// extent-1 axis is never used for addressing; it gets a harmless valid value.
+struct MapStrides {
+    int64_t row, head, batch;
+    bool heads_first;  // the head axis has the smaller stride and comes before the row axis in the map
+};
+MapStrides map_strides(int batch, int heads, int rows, int dh, const int64_t stride[3]) {
+    MapStrides m;
+    m.row = rows > 1 ? stride[2] : dh;
+    m.head = heads > 1 ? stride[1] : m.row * rows;
+    const int64_t inner_span = m.head * heads > m.row * rows ? m.head * heads : m.row * rows;
+    m.batch = batch > 1 ? stride[0] : inner_span;
+    m.heads_first = m.head < m.row;
+    return m;
+}
+
+// What cuTensorMapEncodeTiled accepts: strides that are positive multiples of 16 bytes below 2^40 bytes.
+// (Broadcast views with a zero stride and the like go to the CUDA-core kernel.)
+bool map_strides_ok(const MapStrides& m) {
+    const int64_t limit = ((int64_t)1 << 40) / 2;
+    return m.row > 0 && m.head > 0 && m.batch > 0 && m.row < limit && m.head < limit && m.batch < limit &&
+           m.row % 8 == 0 && m.head % 8 == 0 && m.batch % 8 == 0;
+}
+
+// Encoded maps are kept per host thread, keyed by everything that goes into them: a caller that runs the same
+// buffers again (a layer inside a captured or repeated step) pays for the six driver calls once.
+struct MapKey {
+    const void* base;
+    int64_t row, head, batch_stride;
+    int32_t dtype, batch, heads, rows, dh, box_rows;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && row == o.row && head == o.head && batch_stride == o.batch_stride && dtype == o.dtype &&
+               batch == o.batch && heads == o.heads && rows == o.rows && dh == o.dh && box_rows == o.box_rows;
+    }
+};
+struct MapCache {
+    static constexpr int kEntries = 64;
+    MapKey key[kEntries];
+    CUtensorMap map[kEntries];
+    bool used[kEntries] = {false};
+    int next = 0;
+};
+
+// Map over rows [0, rows) of a [batch, heads, *, dh] tensor laid out by `m`: a box of box_rows rows x 64
+// columns of one (batch, head).  Rows of a box at or beyond `rows` are filled with zeros on load and dropped
+// on store.  Returns false on failure.
 bool make_map(CUtensorMap* map, const void* base, int dtype, int batch, int heads, int rows, int dh,
-              const int64_t stride[3], int box_rows, bool* heads_first) {
+              const MapStrides& m, int box_rows) {
+    static thread_local MapCache cache;
+    const MapKey key{base, m.row, m.head, m.batch, dtype, batch, heads, rows, dh, box_rows};
+    for (int i = 0; i < MapCache::kEntries; ++i)
+        if (cache.used[i] && cache.key[i] == key) {
+            *map = cache.map[i];
+            return true;
+        }
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
-    // a stride of an extent-1 axis is never used for addressing; give it a harmless valid value
-    const int64_t row_stride = rows > 1 ? stride[2] : dh;
-    const int64_t head_stride = heads > 1 ? stride[1] : row_stride * rows;
-    const int64_t inner_span = head_stride * heads > row_stride * rows ? head_stride * heads : row_stride * rows;
-    const int64_t batch_stride = batch > 1 ? stride[0] : inner_span;
-    *heads_first = head_stride < row_stride;
     cuuint64_t dims[4];
     cuuint64_t strides[3];
     cuuint32_t box[4];
     dims[0] = (cuuint64_t)dh;
     box[0] = 64;
-    if (*heads_first) {
-        dims[1] = (cuuint64_t)heads; strides[0] = (cuuint64_t)head_stride * 2; box[1] = 1;
-        dims[2] = (cuuint64_t)rows;  strides[1] = (cuuint64_t)row_stride * 2;  box[2] = (cuuint32_t)box_rows;
+    if (m.heads_first) {
+        dims[1] = (cuuint64_t)heads; strides[0] = (cuuint64_t)m.head * 2; box[1] = 1;
+        dims[2] = (cuuint64_t)rows;  strides[1] = (cuuint64_t)m.row * 2;  box[2] = (cuuint32_t)box_rows;
     } else {
-        dims[1] = (cuuint64_t)rows;  strides[0] = (cuuint64_t)row_stride * 2;  box[1] = (cuuint32_t)box_rows;
-        dims[2] = (cuuint64_t)heads; strides[1] = (cuuint64_t)head_stride * 2; box[2] = 1;
+        dims[1] = (cuuint64_t)rows;  strides[0] = (cuuint64_t)m.row * 2;  box[1] = (cuuint32_t)box_rows;
+        dims[2] = (cuuint64_t)heads; strides[1] = (cuuint64_t)m.head * 2; box[2] = 1;
     }
     dims[3] = (cuuint64_t)batch;
-    strides[2] = (cuuint64_t)batch_stride * 2;
+    strides[2] = (cuuint64_t)m.batch * 2;
     box[3] = 1;
     const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
     const CUtensorMapDataType dt = dtype == TMW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -997,10 +978,36 @@ bool make_map(CUtensorMap* map, const void* base, int dtype, int batch, int head
         set_error_text(text);
         return false;
     }
+    const int slot = cache.next;
+    cache.next = (cache.next + 1) % MapCache::kEntries;
+    cache.key[slot] = key;
+    cache.map[slot] = *map;
+    cache.used[slot] = true;
     return true;
 }
 
 int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
+
+// the opt-in to more than 48 KB of dynamic shared memory is per kernel and per device: made once
+int allow_shared_memory(const void* kern, int bytes) {
+    constexpr int kMaxDevices = 64, kMaxKernels = 32;
+    struct Entry { const void* kern; int allowed[kMaxDevices]; };
+    static std::mutex mutex;
+    static Entry table[kMaxKernels] = {};
+    int dev = 0;
+    TMW_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mutex);
+    Entry* e = nullptr;
+    for (int i = 0; i < kMaxKernels && e == nullptr; ++i) {
+        if (table[i].kern == kern) e = &table[i];
+        else if (table[i].kern == nullptr) { table[i].kern = kern; e = &table[i]; }
+    }
+    if (e == nullptr || dev < 0 || dev >= kMaxDevices || e->allowed[dev] < bytes) {
+        TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        if (e != nullptr && dev >= 0 && dev < kMaxDevices) e->allowed[dev] = bytes;
+    }
+    return TMW_OK;
+}
 
 template <int DH, int KS, int VS, int TILES>
 int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream,
@@ -1008,13 +1015,20 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     using L = TcSmem<DH, KS, VS, TILES>;
     const int np_pad = np_pad_of(d.n_persistent);
     CUtensorMap mq, mk, mv, mo, mkp, mvp;
-    bool hf[4] = {false, false, false, false}, hf_p[2];
-    if (!make_map(&mq, q, d.dtype, d.batch, d.heads, d.q_rows, DH, d.q_stride, BM, &hf[0]) ||
-        !make_map(&mk, k, d.dtype, d.batch, d.heads, d.k_rows, DH, d.k_stride, BN, &hf[1]) ||
-        !make_map(&mv, v, d.dtype, d.batch, d.heads, d.k_rows, DH, d.v_stride, BN, &hf[2]) ||
-        !make_map(&mo, o, d.dtype, d.batch, d.heads, d.q_rows, DH, d.o_stride, BM, &hf[3]) ||
-        !make_map(&mkp, k, d.dtype, d.batch, d.heads, d.k_rows, DH, d.k_stride, np_pad > 0 ? np_pad : 16, &hf_p[0]) ||
-        !make_map(&mvp, v, d.dtype, d.batch, d.heads, d.k_rows, DH, d.v_stride, np_pad > 0 ? np_pad : 16, &hf_p[1]))
+    const MapStrides sq = map_strides(d.batch, d.heads, d.q_rows, DH, d.q_stride);
+    const MapStrides sk = map_strides(d.batch, d.heads, d.k_rows, DH, d.k_stride);
+    const MapStrides sv = map_strides(d.batch, d.heads, d.k_rows, DH, d.v_stride);
+    const MapStrides so = map_strides(d.batch, d.heads, d.q_rows, DH, d.o_stride);
+    // The persistent tile is a box of np_pad rows of a map that ENDS at row np: the rows between np and
+    // np_pad are zero-filled instead of being read from the first sequence rows (whatever those hold - even
+    // Inf or NaN bits of a buffer that is still being filled - must not reach 0 x V in the P V product).
+    const int np_rows = d.n_persistent > 0 ? d.n_persistent : 1;
+    if (!make_map(&mq, q, d.dtype, d.batch, d.heads, d.q_rows, DH, sq, BM) ||
+        !make_map(&mk, k, d.dtype, d.batch, d.heads, d.k_rows, DH, sk, BN) ||
+        !make_map(&mv, v, d.dtype, d.batch, d.heads, d.k_rows, DH, sv, BN) ||
+        !make_map(&mo, o, d.dtype, d.batch, d.heads, d.q_rows, DH, so, BM) ||
+        !make_map(&mkp, k, d.dtype, d.batch, d.heads, np_rows, DH, sk, np_pad > 0 ? np_pad : 16) ||
+        !make_map(&mvp, v, d.dtype, d.batch, d.heads, np_rows, DH, sv, np_pad > 0 ? np_pad : 16))
         return TMW_ERR_CUDA;
     TcParams p;
     p.q_rows = d.q_rows; p.k_rows = d.k_rows; p.window = d.window; p.np = d.n_persistent; p.np_pad = np_pad;
@@ -1023,7 +1037,7 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     p.all_keys = all_keys ? 1 : 0;
     p.lse = lse;
     p.q_pos0 = d.q_pos0; p.k_pos0 = d.k_pos0;
-    p.dim_order = (hf[0] ? 1 : 0) | (hf[1] ? 2 : 0) | (hf[2] ? 4 : 0) | (hf[3] ? 8 : 0);
+    p.dim_order = (sq.heads_first ? 1 : 0) | (sk.heads_first ? 2 : 0) | (sv.heads_first ? 4 : 0) | (so.heads_first ? 8 : 0);
     const float scale = d.scale != 0.f ? d.scale : 1.0f / sqrtf((float)DH);
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = device_status_word();
@@ -1033,7 +1047,8 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     constexpr int kThreadsTc = Budget<TILES>::kThreads;
     const bool general = window_block > 0 || all_keys;
     auto run = [&](auto kern) -> int {
-        TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        const int rc = allow_shared_memory(reinterpret_cast<const void*>(kern), smem_bytes);
+        if (rc != TMW_OK) return rc;
         kern<<<grid, kThreadsTc, smem_bytes, stream>>>(mq, mk, mv, mo, mkp, mvp, p);
         return TMW_OK;
     };
@@ -1049,17 +1064,8 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
 
 constexpr int kMaxDynamicSmem = 232448;  // 227 KB per CTA on sm_100
 constexpr int kTwoCtaSmem = (233472 - 2 * 1024) / 2;  // 228 KB per SM, 1 KB per CTA reserved by the system
-#ifndef TMW_TILES64
-#define TMW_TILES64 1
-#endif
 
 }  // namespace
-
-#ifdef TMW_TRACE
-extern "C" __attribute__((visibility("default"))) int tmw_debug_trace(long long* host_out, int n) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * n);
-}
-#endif
 
 bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, const void*, const void*) {
     if (d.dtype != TMW_BF16 && d.dtype != TMW_F16) return false;
@@ -1071,6 +1077,12 @@ bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, co
     if (need > kMaxDynamicSmem) return false;
     // positions are combined in 32-bit arithmetic inside the kernel
     if ((int64_t)d.q_pos0 + d.q_rows + d.window + 4 * BN >= (int64_t)1 << 30) return false;
+    // layouts a tensor map cannot describe
+    if (!map_strides_ok(map_strides(d.batch, d.heads, d.q_rows, d.head_dim, d.q_stride)) ||
+        !map_strides_ok(map_strides(d.batch, d.heads, d.k_rows, d.head_dim, d.k_stride)) ||
+        !map_strides_ok(map_strides(d.batch, d.heads, d.k_rows, d.head_dim, d.v_stride)) ||
+        !map_strides_ok(map_strides(d.batch, d.heads, d.q_rows, d.head_dim, d.o_stride)))
+        return false;
     return true;
 }
 
@@ -1080,7 +1092,7 @@ int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, c
         // One query tile per CTA and two CTAs per SM when two such CTAs fit into shared memory (they do
         // unless there are many persistent keys): independent CTAs drift apart, so one CTA's exponentials,
         // start-up and output phase overlap the other's matrix products.
-        if (TMW_TILES64 == 1 && TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem)
+        if (TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem)
             return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block, all_keys, lse);
         return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block, all_keys, lse);
     }
