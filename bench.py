@@ -15,6 +15,15 @@ with the inputs already in HBM; ``e2e`` is the same through the module's public
 region; ``roofline`` describes the attention-core kernel timed in place with CUDA
 events; ``cpu_baseline`` is the CPU oracle port timed on a bounded sample.
 
+The ``--steps`` region is repeated until half a second of device time has been
+timed; ``ms_per_step`` is the median region (each region counted with its slowest
+rank) and ``timing`` holds min / max and every rank's own median.  The default
+workload's line also carries, under ``extra``, the benchmark's other
+configurations measured in the same run: the decode step of configuration 4
+(256 sequences over the GPUs), the long-context core of configuration 5 (on
+several GPUs sequence-sharded, with sampled row blocks of the sharded output held
+against the CPU oracle) and configuration 2 as one batch of 8 split over the GPUs.
+
 ``--impl reference`` times the reference's CPU path (the oracle port: the same
 PyTorch operations the reference issues, all host threads) on a bounded sample of
 the same workload.
@@ -67,11 +76,15 @@ WORKLOADS = {
                                  dtype="bf16"),
 }
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention-core kernel,
-# taken from the ncu capture summarised under profiles/ (None until captured)
+# DRAM traffic per launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel, measured on
+# exactly the geometry of the workload (config 2: batch 8, L = 4112, 10 heads x 64, window 512: Q + K + V read
+# once = 126.4 MB, 24.8 MB of the 42.1 MB of O written back before the kernel ends).  None = not captured for
+# the kernel as it is now.
 NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126459392 + 24759296,
                      # backward: the dQ kernel plus the dK/dV kernel (one call launches both)
                      "config2_layer_train": (211887360 + 32490752) + (235155200 + 69292800)}
+
+MIN_TIMED_SECONDS = 0.5  # the --steps region is repeated until at least this much device time has been timed
 
 
 def live_pairs(L: int, w: int, Np: int) -> int:
@@ -176,6 +189,72 @@ def physical_gpu_index(local_index: int) -> int:
     return local_index
 
 
+def bind_to_gpu_cores(local_index: int) -> dict:
+    """Pins this process to the CPU cores that NVML reports as local to its GPU (its NUMA node), so that the
+    pinned host buffers allocated afterwards and the threads that drive the copies sit next to the GPU."""
+    info = {"bound": False}
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(physical_gpu_index(local_index))
+        n_words = (os.cpu_count() + 63) // 64
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, n_words)
+        cores = [64 * i + b for i, wd in enumerate(words) for b in range(64) if (wd >> b) & 1]
+        world_local = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")))
+        if cores:
+            # ranks whose GPUs share a NUMA node share its cores out among themselves
+            per = max(1, len(cores) // max(1, world_local))
+            mine = cores[(local_index * per) % len(cores):][:per] or cores
+            os.sched_setaffinity(0, set(mine))
+            info = {"bound": True, "cores": len(mine), "first_core": mine[0], "numa_cores": len(cores)}
+            try:
+                info["numa_node"] = pynvml.nvmlDeviceGetNumaNodeId(h)
+            except Exception:  # noqa: BLE001 - older bindings
+                pass
+    except Exception as e:  # noqa: BLE001 - binding is an optimisation; the run goes on unbound
+        info["error"] = type(e).__name__
+    return info
+
+
+def timed_regions(step, steps: int, barrier, world: int, dev, min_seconds: float = MIN_TIMED_SECONDS,
+                  max_regions: int = 200):
+    """Times `steps` calls of step(i) with CUDA events, bracketed by barrier() on both sides, as often as it
+    takes to cover `min_seconds` of device time (the count is fixed from the first region's time, maximum over
+    the ranks, so that every rank runs the same number).  Returns this rank's region times in ms."""
+    import torch.distributed as dist
+
+    regions, i, n_regions = [], 0, 1
+    while len(regions) < n_regions:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for _ in range(steps):
+            step(i)
+            i += 1
+        b.record()
+        barrier()
+        regions.append(a.elapsed_time(b))
+        if len(regions) == 1:
+            t = torch.tensor([regions[0]], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            n_regions = int(min(max_regions, max(1, math.ceil(min_seconds * 1e3 / max(float(t.item()), 1e-3)))))
+    return regions
+
+
+def gather_ranks(values, world: int, dev):
+    """[world, len(values)] float64 tensor on the host: every rank's numbers, for per-rank reporting."""
+    import torch.distributed as dist
+
+    t = torch.tensor(values, device=dev, dtype=torch.float64)
+    if world == 1:
+        return t[None].cpu()
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return torch.stack(out).cpu()
+
+
 # --------------------------------------------------------------------------------------
 # CPU side: the reference's path, restated (oracle port)
 # --------------------------------------------------------------------------------------
@@ -248,11 +327,15 @@ def run_reference_arm(args, wl_name: str, wl: dict) -> None:
 # --------------------------------------------------------------------------------------
 
 
-def run_ours(args, wl_name: str, wl: dict) -> None:
-    import torch.distributed as dist
+_DIST = None
 
-    from oracle import windowed_oracle as wo  # seeded input recipe (and the CPU baseline leg below)
-    from titanmac_b200 import WindowConfig, WindowedAttention, _native
+
+def _dist_setup(args):
+    """(dist, world, rank, local, dev); the process group is made once per process."""
+    global _DIST
+    if _DIST is not None:
+        return _DIST
+    import torch.distributed as dist
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -265,10 +348,53 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    _DIST = (dist, world, rank, local, dev)
+    return _DIST
 
-    dtype = torch.bfloat16 if wl["dtype"] == "bf16" else torch.float32
+
+def make_barrier(dist, world):
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    return barrier
+
+
+def region_stats(regions, steps: int, world: int, dev) -> dict:
+    """Per-step times from every rank's region times: a region counts with its slowest rank; the median region
+    is the reported one; the per-rank medians show which GPU (or host) is the slow one."""
+    allr = gather_ranks(regions, world, dev) / steps             # [world, regions] ms per step
+    worst = allr.max(dim=0).values
+    return {"ms_per_step": float(worst.median()), "min": float(worst.min()), "max": float(worst.max()),
+            "regions": len(regions), "timed_seconds": float(allr.max(dim=0).values.sum() * steps / 1e3),
+            "per_rank_ms_per_step": [round(float(v), 5) for v in allr.median(dim=1).values]}
+
+
+def pcie_ceiling(nbytes: int, world: int, dev, barrier, iters: int = 10) -> dict:
+    """Plain pinned-memory copies of `nbytes`, every rank at the same time and nothing else running: what the
+    host links give when all GPUs copy at once - the ceiling of the end-to-end leg."""
+    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    devb = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    out = {}
+    for name, (dst, src) in (("h2d", (devb, host)), ("d2h", (host, devb))):
+        dst.copy_(src, non_blocking=True)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for _ in range(iters):
+            dst.copy_(src, non_blocking=True)
+        b.record()
+        barrier()
+        gbs = nbytes * iters / (a.elapsed_time(b) * 1e-3) / 1e9
+        out[name + "_gbs_per_rank"] = [round(float(v), 2) for v in gather_ranks([gbs], world, dev)[:, 0]]
+    return out
+
+
+def make_layer(wl: dict, rank: int, dev, dtype):
+    from oracle import windowed_oracle as wo  # seeded input recipe
+    from titanmac_b200 import WindowConfig, WindowedAttention
+
     B, T, D, H, w, Np = wl["batch"], wl["T"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
-    L = Np + T
     x_cpu, w_qkv, w_out = wo.layer_inputs(B, T, D, Np, seed=rank)
     if "block_size" in wl:
         from titanmac_b200 import BlockSparseAttention
@@ -283,107 +409,133 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
     with torch.no_grad():
         mod.qkv_proj.weight.copy_(w_qkv)
         mod.out_proj.weight.copy_(w_out)
-    mod = mod.to(device=dev, dtype=dtype)
+    return mod.to(device=dev, dtype=dtype), x_cpu
+
+
+def run_ours(args, wl_name: str, wl: dict) -> None:
+    from titanmac_b200 import HostPipeline, _native
+
+    dist, world, rank, local, dev = _dist_setup(args)
+    affinity = bind_to_gpu_cores(local)  # before any pinned allocation
+    barrier = make_barrier(dist, world)
+    dtype = torch.bfloat16 if wl["dtype"] == "bf16" else torch.float32
+    B, T, D, Np = wl["batch"], wl["T"], wl["d_model"], wl["n_persistent"]
+    L = Np + T
+    mod, x_cpu = make_layer(wl, rank, dev, dtype)
 
     # several input sets so that consecutive steps do not find their inputs in L2 (126 MB)
     n_sets = 4
     xs = [(x_cpu.to(dtype) + 0.001 * i).to(dev) for i in range(n_sets)]
     flops = layer_flops(wl)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     for i in range(args.warmup):
         mod(xs[i % n_sets])
     _native.poll_status(dev)
 
-    # ---- timed region: inputs resident in HBM --------------------------------------
+    # ---- timed regions: inputs resident in HBM ---------------------------------------
     mod.core_events = []
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(physical_gpu_index(local)) as clocks:
-        barrier()
-        start.record()
-        for i in range(args.steps):
-            mod(xs[i % n_sets])
-        end.record()
-        barrier()
-    elapsed_ms = start.elapsed_time(end)
+        regions = timed_regions(lambda i: mod(xs[i % n_sets]), args.steps, barrier, world, dev)
     core_ms = [a.elapsed_time(b) for a, b in mod.core_events]
     mod.core_events = None
     _native.poll_status(dev)
+    stats = region_stats(regions, args.steps, world, dev)
+    core_all = gather_ranks([sum(core_ms) / max(1, len(core_ms)), statistics.median(core_ms)], world, dev)
+    core_avg_ms = float(core_all[:, 0].max())
 
     # ---- end to end: host buffers, copies inside the timed region -------------------
     # Every step copies its input from pinned host memory and its output back; HostPipeline (public API)
     # overlaps the two copies and the forward of consecutive steps on three streams.
-    from titanmac_b200 import HostPipeline
-
     x_host = x_cpu.to(dtype).pin_memory()
     y_hosts = [torch.empty((B, L, D), dtype=dtype).pin_memory() for _ in range(2)]
     pipe = HostPipeline(mod, (B, L, D), dtype, dev, depth=2)
     main_stream = torch.cuda.current_stream(dev)
-
     for i in range(max(3, args.warmup // 4)):
         pipe.submit(x_host, y_hosts[i % 2])
     pipe.drain()
     e2e_steps = max(3, min(args.steps, 50))
-    barrier()
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record(main_stream)
-    pipe.follow(main_stream)
-    for i in range(e2e_steps):
-        pipe.submit(x_host, y_hosts[i % 2])
-    pipe.join(main_stream)
-    e2.record(main_stream)
-    barrier()
-    e2e_ms = s2.elapsed_time(e2)
-    if rank == 0:  # the result really came back: compare the last output with a device-resident forward
-        ref = mod(x_host.to(dev)).float().cpu()
-        err = (y_hosts[(e2e_steps - 1) % 2].float() - ref).abs().max().item()
-        if not err <= 1e-2:
-            raise SystemExit(f"end-to-end output differs from the device-resident forward by {err}")
 
-    t = torch.tensor([elapsed_ms, e2e_ms, sum(core_ms) / max(1, len(core_ms))], device=dev, dtype=torch.float64)
+    class _Pipe:  # one e2e region = e2e_steps submissions between follow() and join()
+        n = 0
+
+    def e2e_region():
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        s2.record(main_stream)
+        pipe.follow(main_stream)
+        for _ in range(e2e_steps):
+            pipe.submit(x_host, y_hosts[_Pipe.n % 2])
+            _Pipe.n += 1
+        pipe.join(main_stream)
+        e2.record(main_stream)
+        barrier()
+        return s2.elapsed_time(e2)
+
+    first = e2e_region()
+    t = torch.tensor([first], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, core_avg_ms = (float(v) for v in t.cpu())
+    n_e2e = int(min(50, max(1, math.ceil(MIN_TIMED_SECONDS * 1e3 / max(float(t.item()), 1e-3)))))
+    e2e_regions = [first] + [e2e_region() for _ in range(n_e2e - 1)]
+    e2e_stats = region_stats(e2e_regions, e2e_steps, world, dev)
+    if rank == 0:  # the result really came back: compare the last output with a device-resident forward
+        ref = mod(x_host.to(dev)).float().cpu()
+        err = (y_hosts[(_Pipe.n - 1) % 2].float() - ref).abs().max().item()
+        if not err <= 1e-2:
+            raise SystemExit(f"end-to-end output differs from the device-resident forward by {err}")
+    h2d_bytes = x_host.numel() * x_host.element_size()
+    d2h_bytes = y_hosts[0].numel() * y_hosts[0].element_size()
+    pcie = pcie_ceiling(h2d_bytes, world, dev, barrier)
+    del pipe, xs
+
+    # ---- the other configurations of the benchmark, carried in the same line ----------
+    extra = {}
+    if "block_size" not in wl and wl_name == "config2_layer_prefill" and not args.no_extra:
+        extra = measure_extras(args, dist, world, rank, local, dev, barrier)
 
     if rank == 0:
         peaks = load_peaks()
-        value = flops["total"] * world * args.steps / (elapsed_ms * 1e-3) / 1e12
-        e2e_value = flops["total"] * world * e2e_steps / (e2e_ms * 1e-3) / 1e12
+        ms_step = stats["ms_per_step"]
+        value = flops["total"] * world / (ms_step * 1e-3) / 1e12
+        e2e_value = flops["total"] * world / (e2e_stats["ms_per_step"] * 1e-3) / 1e12
         achieved = flops["core"] / (core_avg_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops"]
+        clk = clocks.report()
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
             "config": dict(workload=wl_name, **wl, global_batch=B * world, parallelism=f"batch-sharded x{world}",
                            l2="inputs rotate over 4 sets; x+qkv+o per step = 210 MB > 126 MB L2",
                            flops_per_step_per_gpu=flops),
+            "timing": dict(stats, how=f"regions of {args.steps} steps repeated until {MIN_TIMED_SECONDS} s are timed; a "
+                           "region counts with its slowest rank; ms_per_step is the median region",
+                           ms_times_median_sm_mhz=(ms_step * clk["sm_mhz"] if clk.get("sm_mhz") else None)),
             "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill_block_sparse)"
                          if "block_size" in wl else "attention core (tmw_prefill)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16 burst", "avg_launch_ms": core_avg_ms,
+                         "avg_launch_ms_per_rank": [round(float(v), 5) for v in core_all[:, 0]],
+                         "median_launch_ms_per_rank": [round(float(v), 5) for v in core_all[:, 1]],
                          "traffic": NCU_TRAFFIC_BYTES.get(wl_name),
                          "algorithmic_flops_per_launch": flops["core"]},
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
-                    "d2h_bytes_per_step": y_hosts[0].numel() * y_hosts[0].element_size(), "steps": e2e_steps,
-                    "ms_per_step": e2e_ms / e2e_steps,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps, "ms_per_step": e2e_stats["ms_per_step"],
+                    "regions": e2e_stats["regions"], "min_ms_per_step": e2e_stats["min"],
+                    "max_ms_per_step": e2e_stats["max"], "per_rank_ms_per_step": e2e_stats["per_rank_ms_per_step"],
+                    "per_rank_gbs_each_way": [round(h2d_bytes / (v * 1e-3) / 1e9, 2)
+                                              for v in e2e_stats["per_rank_ms_per_step"]],
+                    "copy_only_ceiling": pcie, "cpu_affinity": affinity,
                     "how": "HostPipeline: H2D copy, forward and D2H copy of consecutive steps overlap on 3 streams"},
-            "gpu_launches": args.steps * (3 if "block_size" in wl else 1),
-            "clocks": clocks.report(),
+            "gpu_launches": args.steps * stats["regions"] * (3 if "block_size" in wl else 1),
+            "clocks": clk,
         }
-        if world == 1:
-            line["extra"] = {"decode_attention_config4_one_layer": decode_attention_probe(dev, peaks)}
+        if extra:
+            line["extra"] = extra
         if world == 1 and not args.no_cpu_baseline:
             sec, cflops, cores, desc = cpu_reference_sample(wl, iters=5, warmup=1)
             line["cpu_baseline"] = {"value": cflops / sec / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": desc}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def decode_attention_probe(dev, peaks, batch=256, heads=10, dh=64, window=512, n_persistent=16, layers=4, iters=10):
@@ -415,37 +567,16 @@ def decode_attention_probe(dev, peaks, batch=256, heads=10, dh=64, window=512, n
             "algorithmic_bytes_per_launch": nbytes, "peak_source": f"{peaks['source']} copy bandwidth"}
 
 
-def _dist_setup(args):
-    import torch.distributed as dist
+def random_model(wl: dict, dev, max_seq_len: int):
+    """The 16-layer default model with every weight N(0, 0.02), biases 0, norm scales 1 (seeded, CPU generator)."""
+    from titanmac_b200 import TitanMAC, TitanMACConfig
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in the product)")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    return dist, world, rank, local, dev
-
-
-def run_decode(args, wl_name: str, wl: dict) -> None:
-    """benchmark configuration 4: prompt through the 16-layer model once, then `--steps` decode steps (CUDA graph)."""
-    from titanmac_b200 import TitanMAC, TitanMACConfig, _native
-
-    dist, world, rank, local, dev = _dist_setup(args)
-    if wl["batch"] % world:
-        raise SystemExit("the batch must divide by the number of GPUs")
-    B = wl["batch"] // world
     cfg = TitanMACConfig(vocab_size=wl["vocab"], d_model=wl["d_model"], n_heads=wl["heads"], n_layers=wl["layers"],
-                         d_ff=wl["d_ff"], max_seq_len=4096, window_size=wl["window"], n_persistent=wl["n_persistent"],
-                         use_block_sparse=False)
+                         d_ff=wl["d_ff"], max_seq_len=max_seq_len, window_size=wl["window"],
+                         n_persistent=wl["n_persistent"], use_block_sparse=False)
     g = torch.Generator(device="cpu").manual_seed(0)
     model = TitanMAC(cfg).eval()
-    with torch.no_grad():  # every weight N(0, 0.02), biases 0, norm scales 1
+    with torch.no_grad():
         for name, prm in model.named_parameters():
             if name.endswith("scale"):
                 prm.fill_(1.0)
@@ -453,13 +584,30 @@ def run_decode(args, wl_name: str, wl: dict) -> None:
                 prm.zero_()
             else:
                 prm.copy_(torch.randn(prm.shape, generator=g) * 0.02)
-    model = model.to(device=dev, dtype=torch.bfloat16)
+    return model.to(device=dev, dtype=torch.bfloat16)
+
+
+def measure_decode(wl_name: str, wl: dict, steps: int, warmup: int, ctx, min_seconds: float = MIN_TIMED_SECONDS):
+    """benchmark configuration 4: prompt through the 16-layer model once, then decode steps (CUDA graph).  Returns the
+    JSON line as a dict on rank 0, None elsewhere."""
+    from titanmac_b200 import _native
+
+    dist, world, rank, local, dev = ctx
+    barrier = make_barrier(dist, world)
+    if wl["batch"] % world:
+        raise SystemExit("the batch must divide by the number of GPUs")
+    B = wl["batch"] // world
+    max_regions = 8
+    e2e_steps = max(3, min(steps, 64))
+    # every replayed step moves the position on by one: the position table must cover all of them
+    model = random_model(wl, dev, wl["T"] + warmup + steps * max_regions + e2e_steps + 16)
     g = torch.Generator(device="cpu").manual_seed(1 + rank)
     prompt = torch.randint(0, wl["vocab"], (B, wl["T"]), generator=g).to(dev)
-    forced = torch.randint(0, wl["vocab"], (B, args.steps + args.warmup + 2), generator=g).to(dev)
+    forced = torch.randint(0, wl["vocab"], (B, steps + warmup + 2), generator=g).to(dev)
 
     chunk = max(1, min(B, 32))  # prompt in slices of the batch: bounds the activation footprint
     caches = model.new_caches(B, dev, torch.bfloat16)
+    torch.cuda.synchronize()
     t_pre = time.perf_counter()
     for b0 in range(0, B, chunk):
         sub = model.new_caches(min(chunk, B - b0), dev, torch.bfloat16)
@@ -481,83 +629,65 @@ def run_decode(args, wl_name: str, wl: dict) -> None:
     with torch.cuda.graph(graph):
         logits = model.decode_step(tok, pos, caches)
         pos += 1
-    step_i = 0
 
-    def one_step():
-        nonlocal step_i
-        tok.copy_(forced[:, step_i % forced.shape[1]], non_blocking=True)  # teacher-forced ids, already on the device
+    def one_step(i):
+        tok.copy_(forced[:, i % forced.shape[1]], non_blocking=True)  # teacher-forced ids, already on the device
         graph.replay()
-        step_i += 1
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        one_step()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(warmup):
+        one_step(i)
     with ClockSampler(physical_gpu_index(local)) as clocks:
-        barrier()
-        a.record()
-        for _ in range(args.steps):
-            one_step()
-        b.record()
-        barrier()
-    ms = a.elapsed_time(b)
+        regions = timed_regions(one_step, steps, barrier, world, dev, min_seconds=min_seconds,
+                                max_regions=max_regions)
+    stats = region_stats(regions, steps, world, dev)
     _native.poll_status(dev)
 
     # end to end: the step's token ids come from pinned host memory, the greedy choice goes back to the host
     tok_host = forced[:, :8].cpu().pin_memory()
     res_host = torch.empty((B,), dtype=torch.int64).pin_memory()
-    e2e_steps = max(3, min(args.steps, 64))
 
     def e2e_step(i):
         tok.copy_(tok_host[:, i % 8], non_blocking=True)
         graph.replay()
         res_host.copy_(logits.argmax(dim=-1), non_blocking=True)
 
-    for i in range(3):
-        e2e_step(i)
-    barrier()
-    a2, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a2.record()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    b2.record()
-    barrier()
-    e2e_ms = a2.elapsed_time(b2)
+    e2e_step(0)
+    e2e_stats = region_stats(timed_regions(e2e_step, e2e_steps, barrier, world, dev, min_seconds=0.0), e2e_steps,
+                             world, dev)
+    peaks = load_peaks()
+    L, D, H, w, Np = wl["layers"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
+    probe = decode_attention_probe(dev, peaks, batch=B, heads=H, dh=D // H, window=w, n_persistent=Np)
+    n_params = sum(p.numel() for p in model.parameters())
+    del graph, caches, model
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    kv_bytes = B * L * (w + 1) * D * 2 * 2
+    step_bytes = kv_bytes + n_params * 2
+    ms_step = stats["ms_per_step"]
+    return {
+        "metric": "decode_tokens_per_s", "value": wl["batch"] / (ms_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": dict(workload=wl_name, **wl, batch_per_gpu=B, parallelism=f"batch-sharded x{world}",
+                       decode="CUDA-graph step, teacher-forced ids", prefill_seconds=prefill_s,
+                       l2="ring caches 10.8 GB per 256 sequences >> 126 MB L2",
+                       algorithmic_bytes_per_step_per_gpu=step_bytes),
+        "timing": stats,
+        "roofline": dict(probe, note="decode attention kernel timed alone on this geometry",
+                         step_hbm_frac=step_bytes / (ms_step * 1e-3) / 1e9 / peaks["hbm_gbs"]),
+        "e2e": {"value": wl["batch"] / (e2e_stats["ms_per_step"] * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8, "steps": e2e_steps,
+                "ms_per_step": e2e_stats["ms_per_step"]},
+        "gpu_launches": steps * stats["regions"] * L,
+        "clocks": clocks.report(),
+    }
 
-    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = (float(v) for v in t.cpu())
-    if rank == 0:
-        peaks = load_peaks()
-        L, D, H, w, Np = wl["layers"], wl["d_model"], wl["heads"], wl["window"], wl["n_persistent"]
-        kv_bytes = B * L * (w + 1) * D * 2 * 2
-        weight_bytes = sum(p.numel() for p in model.parameters()) * 2
-        step_bytes = kv_bytes + weight_bytes
-        probe = decode_attention_probe(dev, peaks, batch=B, heads=H, dh=D // H, window=w, n_persistent=Np)
-        line = {
-            "metric": "decode_tokens_per_s", "value": wl["batch"] * args.steps / (ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(workload=wl_name, **wl, batch_per_gpu=B, parallelism=f"batch-sharded x{world}",
-                           decode="CUDA-graph step, teacher-forced ids", prefill_seconds=prefill_s,
-                           l2="ring caches 10.8 GB per 256 sequences >> 126 MB L2",
-                           algorithmic_bytes_per_step_per_gpu=step_bytes),
-            "roofline": dict(probe, note="decode attention kernel timed alone on this geometry",
-                             step_hbm_frac=step_bytes / (ms / args.steps * 1e-3) / 1e9 / peaks["hbm_gbs"]),
-            "e2e": {"value": wl["batch"] * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8, "steps": e2e_steps,
-                    "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": args.steps * L,
-            "clocks": clocks.report(),
-        }
+
+def run_decode(args, wl_name: str, wl: dict) -> None:
+    line = measure_decode(wl_name, wl, args.steps, args.warmup, _dist_setup(args))
+    if line is not None:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def run_model_prefill(args, wl_name: str, wl: dict) -> None:
@@ -656,8 +786,6 @@ def run_model_prefill(args, wl_name: str, wl: dict) -> None:
             "clocks": clocks.report(),
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def train_flops(wl: dict) -> dict:
@@ -796,104 +924,187 @@ def run_train(args, wl_name: str, wl: dict) -> None:
             "clocks": clocks.report(),
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
 
 
-def run_long(args, wl_name: str, wl: dict) -> None:
-    """benchmark configuration 5: attention core over one long sequence, rows sharded over the GPUs with a K/V halo."""
-    from oracle import windowed_oracle as wo
+def measure_long(wl_name: str, wl: dict, steps: int, warmup: int, ctx, shard_overlap: int = 0,
+                 min_seconds: float = MIN_TIMED_SECONDS, with_e2e: bool = True):
+    """benchmark configuration 5: attention core over one long sequence, rows sharded over the GPUs with a K/V halo.
+
+    Every rank draws the SAME whole-length Q, K, V on its own GPU (seeded device generator) and keeps its rows,
+    so that after the timed region sampled row blocks of the sharded output - the first rows behind the shard
+    boundary, an interior block, the last rows - can be held against the CPU oracle, for both forms of the
+    exchange.  The unsharded kernel is timed on the same data (efficiency = its time / (N x the sharded step))."""
+    from oracle import windowed_oracle as wo  # checker for the sampled row blocks (outside the timed region)
     from titanmac_b200 import _native, shard
 
-    dist, world, rank, local, dev = _dist_setup(args)
+    dist, world, rank, local, dev = ctx
+    barrier = make_barrier(dist, world)
     H, w, Np = wl["heads"], wl["window"], wl["n_persistent"]
     dh = wl["d_model"] // H
     Ltot = Np + wl["T"]
     bounds = shard.shard_bounds(Ltot, Np, world)
     r0, r1 = bounds[rank]
-    g = torch.Generator(device="cpu").manual_seed(100 + rank)
     own = r1 - r0
-    q, k, v = (torch.randn(1, own, H, dh, generator=g).to(torch.bfloat16).to(dev).permute(0, 2, 1, 3) for _ in range(3))
+    g = torch.Generator(device=dev).manual_seed(100)
+    whole = [torch.randn(1, Ltot, H, dh, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+             .permute(0, 2, 1, 3) for _ in range(3)]
+    q, k, v = (t[:, :, r0:r1] for t in whole)
     flops = H * live_pairs(Ltot, w, Np) * 4 * dh
+
+    # the whole sequence on one GPU: the N = 1 kernel time that the sharded step is held against
+    for _ in range(2):
+        _native.prefill(*whole, w, Np)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(5):
+        _native.prefill(*whole, w, Np)
+    b.record()
+    torch.cuda.synchronize()
+    n1_ms = float(gather_ranks([a.elapsed_time(b) / 5], world, dev)[:, 0].median())
+
     kv = None
     if world > 1:
         # K and V of this rank live in the sharded buffers from the start (the producer writes them there):
-        # a step is then the persistent broadcast, the halo exchange and two kernel launches
+        # a step is then the persistent broadcast, the halo exchange and the kernel launch(es)
         kv = shard.ShardedKV.allocate(1, H, dh, Ltot, w, Np, torch.bfloat16, dev)
         kv.k_own.copy_(k)
         kv.v_own.copy_(v)
 
-    def step():
+    def run(overlap):
         if world == 1:
             return _native.prefill(q, k, v, w, Np)
-        return shard.sharded_prefill(q, None, None, Ltot, w, Np, kv=kv, overlap=bool(args.shard_overlap))
+        return shard.sharded_prefill(q, None, None, Ltot, w, Np, kv=kv, overlap=bool(overlap))
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(warmup):
+        run(shard_overlap)
     with ClockSampler(physical_gpu_index(local)) as clocks:
-        barrier()
-        a.record()
-        for _ in range(args.steps):
-            step()
-        b.record()
-        barrier()
-    ms = a.elapsed_time(b)
+        regions = timed_regions(lambda i: run(shard_overlap), steps, barrier, world, dev, min_seconds=min_seconds,
+                                max_regions=20)
+    stats = region_stats(regions, steps, world, dev)
     _native.poll_status(dev)
 
-    # end to end: this rank's rows of Q, K, V from pinned host memory, its rows of O back
-    hosts = [x.contiguous().cpu().pin_memory() for x in (q, k, v)]
-    devs = [torch.empty_like(x.contiguous()) for x in (q, k, v)]
-    o_host = torch.empty((1, H, own, dh), dtype=torch.bfloat16).pin_memory()
-    e2e_steps = max(2, min(args.steps, 5))
+    # ---- parity of the sharded output (outside the timed region) -------------------------
+    worst = 0.0
+    blocks = sorted({0, max(0, min(own - 64, w)), max(0, own // 2), max(0, own - 64)})
+    kc_pers = [t[:, :, :Np].float().cpu() for t in whole[1:]]
+    for overlap in ((0, 1) if world > 1 else (0,)):
+        o = run(overlap)
+        torch.cuda.synchronize()
+        for b0 in blocks:
+            row0, n = r0 + b0, min(64, own - b0)
+            lo = max(Np, row0 - w)
+            # the oracle is given [persistent | the window of these rows]: rows renumbered from Np + (row0 - lo)
+            kk, vv = (torch.cat([pers, t[:, :, lo:row0 + n].float().cpu()], dim=2)
+                      for pers, t in zip(kc_pers, whole[1:]))
+            qq = whole[0][:, :, row0:row0 + n].float().cpu()
+            ref = wo.attention_core_rows(qq, kk, vv, Np + (row0 - lo), w, Np) if row0 >= Np else \
+                wo.attention_core_rows(qq, kk, vv, row0, w, Np)
+            worst = max(worst, (o[:, :, b0:b0 + n].float().cpu() - ref).abs().max().item())
+    worst = float(gather_ranks([worst], world, dev)[:, 0].max())
 
-    def e2e_step():
-        for d_, h_ in zip(devs, hosts):
-            d_.copy_(h_, non_blocking=True)
-        o = _native.prefill(*devs, w, Np) if world == 1 else shard.sharded_prefill(*devs, Ltot, w, Np)  # copying form
-        o_host.copy_(o, non_blocking=True)
+    e2e = None
+    if with_e2e:
+        # end to end: this rank's rows of Q, K, V from pinned host memory, its rows of O back
+        hosts = [x.contiguous().cpu().pin_memory() for x in (q, k, v)]
+        devs = [torch.empty_like(x.contiguous()) for x in (q, k, v)]
+        o_host = torch.empty((1, H, own, dh), dtype=torch.bfloat16).pin_memory()
+        e2e_steps = max(2, min(steps, 5))
 
-    e2e_step()
-    barrier()
-    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s2.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e2.record()
-    barrier()
-    e2e_ms = s2.elapsed_time(e2)
-    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = (float(x) for x in t.cpu())
-    if rank == 0:
-        peaks = load_peaks()
-        value = flops * args.steps / (ms * 1e-3) / 1e12
-        line = {
-            "metric": "windowed_attn_core_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(workload=wl_name, **wl, parallelism=f"sequence-sharded x{world}, halo {w} rows",
-                           shard_overlap=bool(args.shard_overlap),
-                           l2="Q+K+V+O = 2.1 GB per step > 126 MB L2", algorithmic_flops_per_step=flops),
-            "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill)", "achieved": value / world,
-                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
-                         "peak_source": f"{peaks['source']} bf16 burst", "traffic": None,
-                         "note": "per GPU, halo exchange included when sharded"},
-            "e2e": {"value": flops * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": 3 * hosts[0].numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2,
-                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-            "gpu_launches": args.steps * (1 if world == 1 else 2),
-            "clocks": clocks.report(),
-        }
+        def e2e_step(i):
+            for d_, h_ in zip(devs, hosts):
+                d_.copy_(h_, non_blocking=True)
+            o = _native.prefill(*devs, w, Np) if world == 1 else shard.sharded_prefill(*devs, Ltot, w, Np)
+            o_host.copy_(o, non_blocking=True)
+
+        e2e_step(0)
+        es = region_stats(timed_regions(e2e_step, e2e_steps, barrier, world, dev, min_seconds=0.0), e2e_steps,
+                          world, dev)
+        e2e = {"value": flops / (es["ms_per_step"] * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": 3 * hosts[0].numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2,
+               "steps": e2e_steps, "ms_per_step": es["ms_per_step"]}
+    del whole, kv
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    peaks = load_peaks()
+    ms_step = stats["ms_per_step"]
+    value = flops / (ms_step * 1e-3) / 1e12
+    line = {
+        "metric": "windowed_attn_core_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": dict(workload=wl_name, **wl, parallelism=f"sequence-sharded x{world}, halo {w} rows",
+                       shard_overlap=bool(shard_overlap),
+                       l2="Q+K+V+O = 2.1 GB per step > 126 MB L2", algorithmic_flops_per_step=flops),
+        "timing": stats,
+        "unsharded_kernel_ms": n1_ms, "efficiency_vs_unsharded_kernel": n1_ms / (world * ms_step),
+        "check": {"what": "sampled 64-row blocks of every rank (first rows of the shard, behind the halo, middle, "
+                          "last) against the CPU oracle, exchange forms " + ("0 and 1" if world > 1 else "none"),
+                  "max_abs_err": worst, "tolerance": 2e-2, "pass": bool(worst <= 2e-2)},
+        "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill)", "achieved": value / world,
+                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
+                     "peak_source": f"{peaks['source']} bf16 burst", "traffic": None,
+                     "note": "per GPU, halo exchange included when sharded"},
+        "gpu_launches": steps * stats["regions"] * (1 if world == 1 or not shard_overlap else 2),
+        "clocks": clocks.report(),
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    return line
+
+
+def run_long(args, wl_name: str, wl: dict) -> None:
+    line = measure_long(wl_name, wl, args.steps, args.warmup, _dist_setup(args), args.shard_overlap)
+    if line is not None:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+
+
+def measure_strong_config2(steps: int, warmup: int, ctx) -> dict:
+    """benchmark configuration 2 as it is stated: ONE batch of 8 sequences split over the GPUs (8 / N per GPU)."""
+    from titanmac_b200 import _native
+
+    dist, world, rank, local, dev = ctx
+    barrier = make_barrier(dist, world)
+    wl = dict(WORKLOADS["config2_layer_prefill"])
+    if wl["batch"] % world:
+        return {"unavailable": f"batch {wl['batch']} does not divide by {world} GPUs"}
+    whole_flops = layer_flops(wl)["total"]
+    wl["batch"] //= world
+    mod, x_cpu = make_layer(wl, rank, dev, torch.bfloat16)
+    n_sets = max(4, 4 * world)  # 210 MB / N per set: keep the rotation larger than L2
+    xs = [(x_cpu.to(torch.bfloat16) + 0.001 * i).to(dev) for i in range(n_sets)]
+    for i in range(warmup):
+        mod(xs[i % n_sets])
+    stats = region_stats(timed_regions(lambda i: mod(xs[i % n_sets]), steps, barrier, world, dev, min_seconds=0.2),
+                         steps, world, dev)
+    _native.poll_status(dev)
+    return {"metric": METRIC, "value": whole_flops / (stats["ms_per_step"] * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "scaling": "strong", "global_batch": 8, "batch_per_gpu": wl["batch"], "timing": stats}
+
+
+def measure_extras(args, dist, world, rank, local, dev, barrier) -> dict:
+    """The benchmark's other configurations, measured after the headline workload and carried in its line."""
+    ctx = (dist, world, rank, local, dev)
+    extra = {}
+    d = measure_decode("config4_decode", WORKLOADS["config4_decode"], 64, 5, ctx, min_seconds=0.0)
+    lg = measure_long("config5_long_prefill", WORKLOADS["config5_long_prefill"], 10, 3, ctx, min_seconds=0.0,
+                      with_e2e=False)
+    st = measure_strong_config2(20, 5, ctx)
+    if rank == 0:
+        extra["config4_decode"] = {"value": d["value"], "unit": d["unit"], "ms_per_step": d["ms_per_step"],
+                                   "scaling": "strong", "batch_per_gpu": d["config"]["batch_per_gpu"],
+                                   "step_hbm_frac": d["roofline"]["step_hbm_frac"],
+                                   "attention_kernel": {k_: d["roofline"][k_] for k_ in
+                                                        ("achieved", "peak", "unit", "frac", "avg_launch_ms")},
+                                   "timing": d["timing"], "e2e": d["e2e"]}
+        key = "config5_core" if world == 1 else "config5_sequence_sharded"
+        extra[key] = {"value": lg["value"], "unit": lg["unit"], "ms_per_step": lg["ms_per_step"],
+                      "scaling": "strong", "frac_of_bf16_peak_per_gpu": lg["roofline"]["frac"],
+                      "unsharded_kernel_ms": lg["unsharded_kernel_ms"],
+                      "efficiency_vs_unsharded_kernel": lg["efficiency_vs_unsharded_kernel"],
+                      "check": lg["check"], "timing": lg["timing"]}
+        extra["config2_strong"] = st
+    return extra
 
 
 def main() -> None:
@@ -904,6 +1115,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="config2_layer_prefill")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1 only)")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="default workload only: skip the decode, long-context and strong-scaling measurements")
     ap.add_argument("--shard-overlap", type=int, choices=[0, 1], default=0,
                     help="config5_long_prefill on several GPUs: 1 = rows that need no halo are launched before the "
                          "halo exchange (two launches), 0 = one exchange, then one launch")
@@ -928,6 +1141,8 @@ def main() -> None:
         run_long(args, args.workload, wl)
     else:
         run_ours(args, args.workload, wl)
+    if _DIST is not None and _DIST[1] > 1:
+        _DIST[0].destroy_process_group()
 
 
 if __name__ == "__main__":
