@@ -102,3 +102,30 @@ def test_reference_error_behaviour(golden):
         wo.band_mask(16, -1, 2)
     with pytest.raises(ValueError):
         wo.module_forward(torch.zeros(1, 3, 16), torch.zeros(48, 16), torch.zeros(16, 16), 2, 4, 3)
+
+
+def _sd(golden_model, prefix):
+    keys = [k[len(prefix) + 4:] for k in golden_model._z.files if k.startswith(prefix + "/sd/")]
+    return {k: golden_model[prefix, "sd/" + k] for k in keys}
+
+
+def test_model_oracle_block_matches_reference_block(golden_model):
+    """oracle/model_oracle.py against the output the reference's TitanBlock produced."""
+    from oracle import model_oracle as mo
+
+    d_model, n_heads, d_ff, w, Np = (int(v) for v in golden_model.np("block", "cfg"))
+    y = mo.block_forward(golden_model["block", "x"], _sd(golden_model, "block"), "", n_heads, w, Np)
+    assert (y - golden_model["block", "y"]).abs().max().item() <= 2e-6
+
+
+def test_model_oracle_logits_match_reference_model(golden_model):
+    """... and against the logits of the reference's TitanMAC, whole and at sampled positions."""
+    from oracle import model_oracle as mo
+
+    V, d_model, n_heads, n_layers, d_ff, max_len, w, Np = (int(v) for v in golden_model.np("model", "cfg"))
+    sd, ids, want = _sd(golden_model, "model"), golden_model["model", "ids"], golden_model["model", "logits"]
+    got = mo.model_forward(sd, ids, n_layers, n_heads, w, Np)
+    assert got.shape == want.shape
+    assert (got - want).abs().max().item() <= 5e-6
+    some = [0, 7, 41, ids.shape[1] - 1]
+    assert (mo.model_forward(sd, ids, n_layers, n_heads, w, Np, positions=some) - want[:, some]).abs().max().item() <= 5e-6

@@ -11,6 +11,10 @@ pytestmark = pytest.mark.gpu
 
 FP32_TOL = 1e-5   # fp32 contract: max-abs against the reference
 BF16_TOL = 2e-2   # bf16 contract: max-abs against the fp32 reference on the same (rounded) inputs
+# Module outputs with N(0, 0.02) weights have magnitude ~0.2, where 2e-2 would let a wrong window edge pass: the
+# second, tighter bound is what the kernels have been observed to stay under on these cases (the reference's own
+# bf16-against-fp32 difference is about 1e-3).
+MODULE_REGRESSION_TOL = 5e-3
 DEV = "cuda:0"
 ALGOS = [_native.ALGO_SIMT, _native.ALGO_TCGEN05]
 ALGO_IDS = ["simt", "tcgen05"]
@@ -73,7 +77,9 @@ def test_module_16bit_matches_fp32_reference(golden, dtype, algo):
         mod = make_module(m, dtype, w_qkv, w_out, algo)
         y = mod(xr.to(DEV))
         assert y.dtype == dtype
-        assert (y.float().cpu() - ref).abs().max().item() <= BF16_TOL, case
+        err = (y.float().cpu() - ref).abs().max().item()
+        assert err <= BF16_TOL, f"{case}: observed max-abs error {err:.3e}"
+        assert err <= MODULE_REGRESSION_TOL, f"{case}: observed max-abs error {err:.3e} above the regression bound"
 
 
 @pytest.mark.parametrize("algo", ALGOS, ids=ALGO_IDS)
