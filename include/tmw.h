@@ -156,6 +156,28 @@ TMW_API int tmw_causal_dwconv_backward(int32_t dtype, int32_t batch, int32_t row
                                        void* stream);
 
 /*
+ * Linear layer on the tensor cores: c[m, n] = sum_k a[m, k] * w[n, k] (+ bias[n]) (then the exact, erf-based GELU
+ * when epilogue is TMW_EPILOGUE_GELU) - torch.nn.functional.linear with its [out_features, in_features] weight.
+ * a: [m, k] row-major with leading dimension lda, w: [n, k] with ldw, c: [m, n] with ldc (elements); bias: [n]
+ * or NULL; everything in dtype (TMW_BF16 or TMW_F16), accumulation in fp32.  k, n and the leading dimensions
+ * must be multiples of 8 and the pointers 16-byte aligned (TMW_ERR_INVALID_ARGUMENT otherwise).
+ * Replaces the library GEMMs behind the module's two projections (windowed_attention.py:295 qkv_proj, :331
+ * out_proj, both without bias) and behind the block's MLP, whose bias add and GELU ride in the epilogue
+ * (titans_core/blocks/mlp.py:58-65: fc1 + bias -> GELU -> fc2 + bias).
+ */
+typedef enum tmw_epilogue { TMW_EPILOGUE_NONE = 0, TMW_EPILOGUE_GELU = 1 } tmw_epilogue;
+
+typedef struct tmw_linear_desc {
+    int32_t dtype;    /* tmw_dtype of a, w, bias and c: TMW_BF16 or TMW_F16 */
+    int32_t m, n, k;
+    int32_t epilogue; /* tmw_epilogue, applied after the bias */
+    int64_t lda, ldw, ldc;
+} tmw_linear_desc;
+
+TMW_API int tmw_linear(const tmw_linear_desc* desc, const void* a, const void* w, const void* bias, void* c,
+                       void* stream);
+
+/*
  * Decode: one new token per sequence against a ring cache of the last window+1
  * keys.  The reference has no incremental decode (its generation helper re-runs
  * the full forward per token, examples/train_math.py:146-161); this entry point

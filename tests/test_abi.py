@@ -43,6 +43,8 @@ def test_struct_layouts_match_the_header():
                offsetof(tmw_prefill_desc, k_pos0));
         printf("%zu %zu %zu %zu\n", sizeof(tmw_cache_desc), offsetof(tmw_cache_desc, k_ring),
                offsetof(tmw_cache_desc, v_pers), offsetof(tmw_cache_desc, scale));
+        printf("%zu %zu %zu %zu\n", sizeof(tmw_linear_desc), offsetof(tmw_linear_desc, epilogue),
+               offsetof(tmw_linear_desc, lda), offsetof(tmw_linear_desc, ldc));
         return 0;
     }
     """
@@ -56,6 +58,8 @@ def test_struct_layouts_match_the_header():
     assert [int(v) for v in lines[0].split()] == [ctypes.sizeof(P), P.scale.offset, P.q_stride.offset,
                                                   P.o_stride.offset, P.k_pos0.offset]
     assert [int(v) for v in lines[1].split()] == [ctypes.sizeof(C), C.k_ring.offset, C.v_pers.offset, C.scale.offset]
+    G = _native.LinearDesc
+    assert [int(v) for v in lines[2].split()] == [ctypes.sizeof(G), G.epilogue.offset, G.lda.offset, G.ldc.offset]
 
 
 def test_version_and_error_text():

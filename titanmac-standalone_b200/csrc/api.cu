@@ -57,6 +57,27 @@ SideStream* side_stream_of_current_device() {
     return &table[dev];
 }
 
+// the opt-in to more than 48 KB of dynamic shared memory is per kernel and per device: made once
+int allow_shared_memory(const void* kern, int bytes) {
+    constexpr int kMaxDevices = 64, kMaxKernels = 32;
+    struct Entry { const void* kern; int allowed[kMaxDevices]; };
+    static std::mutex mutex;
+    static Entry table[kMaxKernels] = {};
+    int dev = 0;
+    TMW_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mutex);
+    Entry* e = nullptr;
+    for (int i = 0; i < kMaxKernels && e == nullptr; ++i) {
+        if (table[i].kern == kern) e = &table[i];
+        else if (table[i].kern == nullptr) { table[i].kern = kern; e = &table[i]; }
+    }
+    if (e == nullptr || dev < 0 || dev >= kMaxDevices || e->allowed[dev] < bytes) {
+        TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        if (e != nullptr && dev >= 0 && dev < kMaxDevices) e->allowed[dev] = bytes;
+    }
+    return TMW_OK;
+}
+
 namespace {
 
 bool dtype_ok(int dtype) { return dtype == TMW_F32 || dtype == TMW_BF16 || dtype == TMW_F16; }
@@ -282,6 +303,26 @@ int tmw_prefill_block_sparse_lse(const tmw_prefill_desc* desc, int32_t block_siz
     const int st2 = launch(seq, q_seq, o_seq, s, false);
     TMW_CUDA_TRY(cudaStreamWaitEvent(s, side->join, 0));
     return st != TMW_OK ? st : st2;
+}
+
+int tmw_linear(const tmw_linear_desc* d, const void* a, const void* w, const void* bias, void* c, void* stream) {
+    if (d == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (d->dtype != TMW_BF16 && d->dtype != TMW_F16) return TMW_ERR_UNSUPPORTED;
+    if (d->epilogue != TMW_EPILOGUE_NONE && d->epilogue != TMW_EPILOGUE_GELU) return TMW_ERR_INVALID_ARGUMENT;
+    if (d->m < 0 || d->n < 0 || d->k <= 0) return TMW_ERR_INVALID_ARGUMENT;
+    if (d->k % 8 != 0 || d->n % 8 != 0 || d->lda % 8 != 0 || d->ldw % 8 != 0 || d->ldc % 8 != 0 || d->lda < d->k ||
+        d->ldw < d->k || d->ldc < d->n) {
+        tmw::set_error_text("tmw_linear: k, n and the leading dimensions must be multiples of 8 (16 bytes)");
+        return TMW_ERR_INVALID_ARGUMENT;
+    }
+    if (d->m == 0 || d->n == 0) return TMW_OK;
+    if (a == nullptr || w == nullptr || c == nullptr) return TMW_ERR_INVALID_ARGUMENT;
+    if (!tmw::aligned16(a) || !tmw::aligned16(w) || !tmw::aligned16(c) || (bias != nullptr && !tmw::aligned16(bias)))
+        return TMW_ERR_INVALID_ARGUMENT;
+    // tensor-map limits: leading dimensions below 2^40 bytes (extents are 32-bit already)
+    const int64_t limit = ((int64_t)1 << 40) / 2;
+    if (d->lda >= limit || d->ldw >= limit || d->ldc >= limit) return TMW_ERR_UNSUPPORTED;
+    return tmw::launch_linear(*d, a, w, bias, c, static_cast<cudaStream_t>(stream));
 }
 
 size_t tmw_cache_ring_bytes(int32_t dtype, int32_t batch, int32_t heads, int32_t head_dim, int32_t window) {

@@ -988,27 +988,6 @@ bool make_map(CUtensorMap* map, const void* base, int dtype, int batch, int head
 
 int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
 
-// the opt-in to more than 48 KB of dynamic shared memory is per kernel and per device: made once
-int allow_shared_memory(const void* kern, int bytes) {
-    constexpr int kMaxDevices = 64, kMaxKernels = 32;
-    struct Entry { const void* kern; int allowed[kMaxDevices]; };
-    static std::mutex mutex;
-    static Entry table[kMaxKernels] = {};
-    int dev = 0;
-    TMW_CUDA_TRY(cudaGetDevice(&dev));
-    std::lock_guard<std::mutex> lock(mutex);
-    Entry* e = nullptr;
-    for (int i = 0; i < kMaxKernels && e == nullptr; ++i) {
-        if (table[i].kern == kern) e = &table[i];
-        else if (table[i].kern == nullptr) { table[i].kern = kern; e = &table[i]; }
-    }
-    if (e == nullptr || dev < 0 || dev >= kMaxDevices || e->allowed[dev] < bytes) {
-        TMW_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-        if (e != nullptr && dev >= 0 && dev < kMaxDevices) e->allowed[dev] = bytes;
-    }
-    return TMW_OK;
-}
-
 template <int DH, int KS, int VS, int TILES>
 int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream,
               int window_block, bool all_keys, float* lse) {

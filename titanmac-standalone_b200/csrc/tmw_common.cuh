@@ -107,6 +107,8 @@ __host__ __device__ inline int first_visible_pos(int pos, int np, int window, in
 void set_cuda_error(cudaError_t e, const char* where);
 void set_error_text(const char* text);
 int* device_status_word();  // per-device int in global memory, 0 = fine
+// opt-in of a kernel to `bytes` of dynamic shared memory, made once per kernel and device
+int allow_shared_memory(const void* kern, int bytes);
 
 // a library-owned stream for work that may overlap the caller's stream, with the events of the fork / join
 struct SideStream {
@@ -159,6 +161,8 @@ inline size_t decode_partials_bytes(int batch, int heads, int head_dim, int spli
     const size_t n = (size_t)batch * heads * splits * ((size_t)head_dim + 2) * sizeof(float);
     return (n + 15) & ~(size_t)15;
 }
+int launch_linear(const tmw_linear_desc& d, const void* a, const void* w, const void* bias, void* c,
+                  cudaStream_t stream);
 int launch_cache_fill(const tmw_cache_desc& c, const void* k, const void* v, const int64_t ks[3],
                       const int64_t vs[3], int rows, int t0, cudaStream_t stream);
 

@@ -78,6 +78,21 @@ class CacheDesc(ctypes.Structure):
     ]
 
 
+class LinearDesc(ctypes.Structure):
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("m", ctypes.c_int32),
+        ("n", ctypes.c_int32),
+        ("k", ctypes.c_int32),
+        ("epilogue", ctypes.c_int32),
+        ("lda", ctypes.c_int64),
+        ("ldw", ctypes.c_int64),
+        ("ldc", ctypes.c_int64),
+    ]
+
+
+EPILOGUE_NONE, EPILOGUE_GELU = 0, 1
+
 # name -> (restype, argtypes); the CPU test-suite checks that every symbol here is
 # declared in include/tmw.h and exported by the library, and vice versa.
 SIGNATURES = {
@@ -144,6 +159,7 @@ SIGNATURES = {
          ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
          ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p],
     ),
+    "tmw_linear": (ctypes.c_int, [ctypes.POINTER(LinearDesc)] + [ctypes.c_void_p] * 5),
     "tmw_gelu": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "tmw_add_rmsnorm": (
         ctypes.c_int,
@@ -445,6 +461,43 @@ def gelu(x: torch.Tensor, inplace: bool = False) -> torch.Tensor:
     with torch.cuda.device(x.device):
         check(lib().tmw_gelu(_DTYPES[x.dtype], x.numel(), x.data_ptr(), y.data_ptr(), _stream_ptr(x.device)))
     return y
+
+
+def linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``linear`` takes these operands: 16-bit CUDA tensors, rows of x contiguous, sizes multiples of 8."""
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and weight.dtype == x.dtype and x.dim() >= 2
+            and weight.dim() == 2 and x.shape[-1] == weight.shape[1] and x.shape[-1] % 8 == 0
+            and weight.shape[0] % 8 == 0 and weight.is_contiguous() and x.numel() > 0)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, gelu: bool = False,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weight.T (+ bias)`` and, with ``gelu``, the exact GELU of that — ``torch.nn.functional.linear`` on
+    the library's own tensor-core kernel (the projections of windowed_attention.py:295, 331 and the MLP of
+    titans_core/blocks/mlp.py:58-65 with bias and activation in the epilogue)."""
+    _require_cuda(x, weight)
+    if not linear_supported(x, weight):
+        raise TypeError("linear: bf16 / fp16 CUDA operands, contiguous weight [n, k], k and n multiples of 8")
+    k, n = x.shape[-1], weight.shape[0]
+    x2 = x.reshape(-1, k)
+    if x2.stride(1) != 1 or x2.stride(0) % 8 != 0 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    if bias is not None:
+        if bias.dtype != x.dtype or bias.shape != (n,) or not bias.is_cuda:
+            raise TypeError("linear: bias must be a vector of n elements in the dtype of x")
+        bias = bias if bias.is_contiguous() else bias.contiguous()
+    m = x2.shape[0]
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (n,), dtype=x.dtype, device=x.device)
+    elif out.shape != x.shape[:-1] + (n,) or out.dtype != x.dtype or not out.is_contiguous():
+        raise ValueError("linear: out must be contiguous, of x's dtype and shaped like x with n columns")
+    desc = LinearDesc(dtype=_DTYPES[x.dtype], m=m, n=n, k=k, epilogue=EPILOGUE_GELU if gelu else EPILOGUE_NONE,
+                      lda=x2.stride(0), ldw=weight.stride(0), ldc=n)
+    with torch.cuda.device(x.device):
+        check(lib().tmw_linear(ctypes.byref(desc), x2.data_ptr(), weight.data_ptr(),
+                               bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                               _stream_ptr(x.device)))
+    return out
 
 
 def add_rmsnorm_supported(x: torch.Tensor) -> bool:
