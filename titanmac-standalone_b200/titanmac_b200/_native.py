@@ -500,6 +500,29 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
+# Products with at most this many rows (a decode step's: one row per sequence) stay with the library GEMM of
+# torch.nn.functional.linear: they are launch- and latency-bound, and the tensor-core kernel above, built to
+# stream tiles of 128 / 256 rows, measures about twice the library's few microseconds there.
+LINEAR_MIN_ROWS = 257
+
+
+def project(lin: "torch.nn.Linear", x: torch.Tensor, gelu: bool = False) -> torch.Tensor:
+    """Forward of an ``nn.Linear`` (optionally followed by the exact GELU) on the inference path: the library's
+    tensor-core kernel with bias and activation in its epilogue where it applies (16-bit CUDA operands, no
+    gradient wanted, more rows than a decode step has), otherwise the module's own forward."""
+    rows = x.numel() // x.shape[-1] if x.shape[-1] else 0
+    if (rows >= LINEAR_MIN_ROWS and linear_supported(x, lin.weight)
+            and (lin.bias is None or lin.bias.dtype == x.dtype)
+            and not (torch.is_grad_enabled() and (x.requires_grad or lin.weight.requires_grad))):
+        return linear(x, lin.weight, lin.bias, gelu=gelu)
+    y = lin(x)
+    if not gelu:
+        return y
+    if gelu_supported(y) and not (torch.is_grad_enabled() and y.requires_grad):
+        return globals()["gelu"](y, inplace=True)
+    return torch.nn.functional.gelu(y)
+
+
 def add_rmsnorm_supported(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype in _DTYPES and x.shape[-1] % 8 == 0
 

@@ -134,7 +134,7 @@ class BlockSparseAttention(nn.Module):
         B, L, D = x.shape
         if self.n_persistent >= L:
             raise ValueError(f"n_persistent ({self.n_persistent}) must be < seq_len ({L})")
-        qkv = self.qkv_proj(x)
+        qkv = _native.project(self.qkv_proj, x)
         if self.use_conv:
             qkv = _native.causal_dwconv(qkv, self.stacked_conv_weight())
         v5 = qkv.view(B, L, 3, self.n_heads, self.d_head)
@@ -148,7 +148,7 @@ class BlockSparseAttention(nn.Module):
         if self.core_events is not None:
             end.record()
             self.core_events.append((start, end))
-        return self.dropout(self.out_proj(o.view(B, L, D)))
+        return self.dropout(_native.project(self.out_proj, o.view(B, L, D)))
 
 
 def create_block_sparse_attention(config) -> BlockSparseAttention:

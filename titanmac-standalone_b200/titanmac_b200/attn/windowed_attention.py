@@ -132,7 +132,7 @@ class WindowedAttention(nn.Module):
 
     def _forward_no_grad(self, x: torch.Tensor) -> torch.Tensor:
         B, L, D = x.shape
-        qkv = self.qkv_proj(x)
+        qkv = _native.project(self.qkv_proj, x)  # tmw_linear: [B, L, 3, H, dh] is just its row-major output
         q, k, v = self.split_qkv(qkv)
         # the output is allocated as [B, L, H, dh] so that "concat heads" is a view
         o = torch.empty((B, L, self.n_heads, self.d_head), dtype=qkv.dtype, device=qkv.device)
@@ -144,4 +144,4 @@ class WindowedAttention(nn.Module):
         if self.core_events is not None:
             end.record()
             self.core_events.append((start, end))
-        return self.dropout(self.out_proj(o.view(B, L, D)))
+        return self.dropout(_native.project(self.out_proj, o.view(B, L, D)))

@@ -4,7 +4,8 @@ Mirrors titans_core/blocks/titan_block.py:41-102, blocks/norms.py:39-60 and
 blocks/mlp.py:28-67 of the reference (same submodule names, so checkpoints load
 unchanged).  The attention is this package's own code, and so is the element-wise work around
 it on a GPU: RMSNorm with the preceding residual add folded in is one kernel
-(``tmw_add_rmsnorm``) and the exact GELU is another (``tmw_gelu``); the linears stay library calls.
+(``tmw_add_rmsnorm``); the linears are the library's tensor-core product ``tmw_linear`` with bias and the exact GELU
+in its epilogue (a decode step's few rows: library GEMM plus the one-pass ``tmw_gelu``).
 ``use_block_sparse`` selects the attention class exactly as in the reference.
 Under ``torch.no_grad()`` the fused kernels run; with grad mode on, norm and GELU fall back to the
 differentiable PyTorch formulas and the windowed attention core uses its own backward kernel.
@@ -61,12 +62,12 @@ class MLPBlock(nn.Module):
         self.dropout = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        h = self.fc1(x)
-        if _native.gelu_supported(h) and not (torch.is_grad_enabled() and h.requires_grad):
-            h = _native.gelu(h, inplace=True)  # same exact-erf GELU in one pass bound by HBM
-        else:
-            h = self.activation(h)
-        return self.dropout(self.fc2(h))
+        if torch.is_grad_enabled() and (x.requires_grad or self.fc1.weight.requires_grad):
+            return self.dropout(self.fc2(self.activation(self.fc1(x))))
+        # inference: bias and the exact-erf GELU ride in the epilogue of the library's tensor-core product
+        # (tmw_linear); few rows (a decode step) take the library GEMM and the one-pass GELU kernel
+        h = _native.project(self.fc1, x, gelu=True)
+        return self.dropout(_native.project(self.fc2, h))
 
 
 class TitanBlock(nn.Module):

@@ -87,7 +87,7 @@ class TitanMAC(nn.Module):
             x, h = layer.norm_mlp.add_forward(x, a, inplace=True)
             pending = layer.mlp(h)
         h = self.norm(x) if pending is None else self.norm.add_forward(x, pending, inplace=True)[1]
-        logits = self.lm_head(h)
+        logits = _native.project(self.lm_head, h)
         logits = logits[:, Np:, :] if Np > 0 else logits
         out = {"logits": logits}
         if labels is not None:
@@ -129,7 +129,7 @@ class TitanMAC(nn.Module):
             L = h.shape[1]
             attn._check_lengths(L)
             attn._check_supported(h, None)
-            qkv = attn.qkv_proj(h)
+            qkv = _native.project(attn.qkv_proj, h)
             q, k, v = attn.split_qkv(qkv)
             o = torch.empty((B, L, attn.n_heads, attn.d_head), dtype=qkv.dtype, device=qkv.device)
             _native.prefill(q, k, v, attn.window_size, attn.num_persistent, out=o.permute(0, 2, 1, 3), algo=attn.algo)
@@ -137,7 +137,7 @@ class TitanMAC(nn.Module):
             if Np > 0:
                 cache.set_persistent(k[0, :, :Np], v[0, :, :Np])
             cache.fill(k[:, :, Np:], v[:, :, Np:], t0=0)
-            x, h = layer.norm_mlp.add_forward(x, attn.out_proj(o.view(B, L, -1)), inplace=True)
+            x, h = layer.norm_mlp.add_forward(x, _native.project(attn.out_proj, o.view(B, L, -1)), inplace=True)
             pending = layer.mlp(h)
         last = self.norm(x[:, -1]) if pending is None else self.norm.add_forward(x[:, -1], pending[:, -1])[1]
         logits = self.lm_head(last)
