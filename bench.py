@@ -962,34 +962,54 @@ def measure_long(wl_name: str, wl: dict, steps: int, warmup: int, ctx, shard_ove
     torch.cuda.synchronize()
     n1_ms = float(gather_ranks([a.elapsed_time(b) / 5], world, dev)[:, 0].median())
 
-    kv = None
+    kv = pkv = None
     if world > 1:
-        # K and V of this rank live in the sharded buffers from the start (the producer writes them there):
-        # a step is then the persistent broadcast, the halo exchange and the kernel launch(es)
+        # K and V of this rank live in the sharded buffers from the start (the producer writes them there).
+        # Two forms of the step: "push" - every rank's GPU writes the halo / persistent rows into its neighbours'
+        # buffers and the attention kernel polls a flag (no host-side collective; the timed form) - and "nccl" -
+        # one batch of in-place sends / receives, then the launch(es).
         kv = shard.ShardedKV.allocate(1, H, dh, Ltot, w, Np, torch.bfloat16, dev)
         kv.k_own.copy_(k)
         kv.v_own.copy_(v)
+        try:
+            pkv = shard.PeerShardedKV.allocate(1, H, dh, Ltot, w, Np, torch.bfloat16, dev)
+            pkv.k_own.copy_(k)
+            pkv.v_own.copy_(v)
+        except ValueError:  # shards shorter than the window
+            pkv = None
+    form = "single GPU" if world == 1 else ("push" if pkv is not None and not shard_overlap else "nccl")
 
-    def run(overlap):
+    def run(which):
         if world == 1:
             return _native.prefill(q, k, v, w, Np)
-        return shard.sharded_prefill(q, None, None, Ltot, w, Np, kv=kv, overlap=bool(overlap))
+        if which == "push":
+            return shard.pushed_prefill(q, pkv)
+        return shard.sharded_prefill(q, None, None, Ltot, w, Np, kv=kv, overlap=(which == "nccl-overlap"))
 
+    timed = form if form != "nccl" else ("nccl-overlap" if shard_overlap else "nccl")
     for _ in range(warmup):
-        run(shard_overlap)
+        run(timed)
     with ClockSampler(physical_gpu_index(local)) as clocks:
-        regions = timed_regions(lambda i: run(shard_overlap), steps, barrier, world, dev, min_seconds=min_seconds,
+        regions = timed_regions(lambda i: run(timed), steps, barrier, world, dev, min_seconds=min_seconds,
                                 max_regions=20)
     stats = region_stats(regions, steps, world, dev)
     _native.poll_status(dev)
+    other = None
+    if world > 1 and form == "push":  # the collective form beside it
+        for _ in range(2):
+            run("nccl")
+        other = region_stats(timed_regions(lambda i: run("nccl"), steps, barrier, world, dev, min_seconds=0.0), steps,
+                             world, dev)["ms_per_step"]
 
     # ---- parity of the sharded output (outside the timed region) -------------------------
     worst = 0.0
     blocks = sorted({0, max(0, min(own - 64, w)), max(0, own // 2), max(0, own - 64)})
     kc_pers = [t[:, :, :Np].float().cpu() for t in whole[1:]]
-    for overlap in ((0, 1) if world > 1 else (0,)):
-        o = run(overlap)
+    forms = ["single GPU"] if world == 1 else (["push"] if pkv is not None else []) + ["nccl", "nccl-overlap"]
+    for which in forms:
+        o = run(which)
         torch.cuda.synchronize()
+        _native.poll_status(dev)
         for b0 in blocks:
             row0, n = r0 + b0, min(64, own - b0)
             lo = max(Np, row0 - w)
@@ -1022,7 +1042,10 @@ def measure_long(wl_name: str, wl: dict, steps: int, warmup: int, ctx, shard_ove
         e2e = {"value": flops / (es["ms_per_step"] * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": 3 * hosts[0].numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2,
                "steps": e2e_steps, "ms_per_step": es["ms_per_step"]}
-    del whole, kv
+    if pkv is not None:
+        pkv.close()
+    barrier()
+    del whole, kv, pkv
     torch.cuda.empty_cache()
     if rank != 0:
         return None
@@ -1034,18 +1057,21 @@ def measure_long(wl_name: str, wl: dict, steps: int, warmup: int, ctx, shard_ove
         "steps": steps, "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": dict(workload=wl_name, **wl, parallelism=f"sequence-sharded x{world}, halo {w} rows",
-                       shard_overlap=bool(shard_overlap),
+                       shard_overlap=bool(shard_overlap), exchange=form,
+                       exchange_forms="push: tmw_halo_push into the neighbours' buffers + flag polling in the "
+                                      "attention kernel; nccl: batch_isend_irecv, then the launch",
                        l2="Q+K+V+O = 2.1 GB per step > 126 MB L2", algorithmic_flops_per_step=flops),
         "timing": stats,
         "unsharded_kernel_ms": n1_ms, "efficiency_vs_unsharded_kernel": n1_ms / (world * ms_step),
+        "nccl_exchange_ms_per_step": other,
         "check": {"what": "sampled 64-row blocks of every rank (first rows of the shard, behind the halo, middle, "
-                          "last) against the CPU oracle, exchange forms " + ("0 and 1" if world > 1 else "none"),
+                          "last) against the CPU oracle, exchange forms: " + ", ".join(forms),
                   "max_abs_err": worst, "tolerance": 2e-2, "pass": bool(worst <= 2e-2)},
         "roofline": {"bound": "tensor", "kernel": "attention core (tmw_prefill)", "achieved": value / world,
                      "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / world / peaks["bf16_tflops"],
                      "peak_source": f"{peaks['source']} bf16 burst", "traffic": None,
                      "note": "per GPU, halo exchange included when sharded"},
-        "gpu_launches": steps * stats["regions"] * (1 if world == 1 or not shard_overlap else 2),
+        "gpu_launches": steps * stats["regions"] * (1 if world == 1 else 3 if form == "push" else 2 if shard_overlap else 1),
         "clocks": clocks.report(),
     }
     if e2e is not None:
@@ -1102,6 +1128,7 @@ def measure_extras(args, dist, world, rank, local, dev, barrier) -> dict:
                       "scaling": "strong", "frac_of_bf16_peak_per_gpu": lg["roofline"]["frac"],
                       "unsharded_kernel_ms": lg["unsharded_kernel_ms"],
                       "efficiency_vs_unsharded_kernel": lg["efficiency_vs_unsharded_kernel"],
+                      "exchange": lg["config"]["exchange"], "nccl_exchange_ms_per_step": lg["nccl_exchange_ms_per_step"],
                       "check": lg["check"], "timing": lg["timing"]}
         extra["config2_strong"] = st
     return extra

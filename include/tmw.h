@@ -156,6 +156,75 @@ TMW_API int tmw_causal_dwconv_backward(int32_t dtype, int32_t batch, int32_t row
                                        void* stream);
 
 /*
+ * Sequence-sharded prefill without a host-side collective on the step.  The reference has no distributed code;
+ * this is the multi-GPU form of its attention core (windowed_attention.py:113-150: a row needs its window
+ * predecessors and the persistent rows, nothing else), for one process per GPU with the neighbours' buffers
+ * mapped into this process (CUDA IPC / peer access; how the pointers are exchanged is the caller's business).
+ *
+ * tmw_halo_push - one launch per destination rank, on `stream`:
+ *   1. waits (bounded) until *wait_flag >= wait_value (wait_flag: in THIS GPU's memory, raised by the destination
+ *      when it has finished reading what the previous push wrote; NULL = no wait),
+ *   2. copies every src -> dst (dst: the destination rank's K/V buffer through its peer mapping; plain stores),
+ *   3. stores signal_value to *signal_flag (in the destination's memory) with release semantics at system scope
+ *      (signal_flag NULL = none; n_copies = 0 with a signal_flag makes the call a pure signal).
+ * Pointers and sizes are multiples of 16 bytes; at most TMW_HALO_MAX_COPIES copies per call.  Launches of one
+ * process must be ordered on one stream (they share a completion counter).  wait_limit_cycles <= 0 selects
+ * about one second; an expired wait skips copies and signal and is reported by tmw_poll_status
+ * (TMW_ERR_DEVICE_TIMEOUT).
+ *
+ * tmw_prefill_halo - tmw_prefill on the tensor-core kernel (TMW_ERR_UNSUPPORTED where that kernel does not
+ * apply) for a K/V buffer [persistent | halo | own rows] whose first two parts are written by other GPUs: the
+ * kernel's loader warps poll *pers_flag (key rows [0, n_persistent)) and *halo_flag (key rows [n_persistent,
+ * n_persistent + halo_rows)) until they reach `value`, right before the first TMA load that touches those rows -
+ * query tiles whose window lies in the rank's own rows never wait for the halo.  The flags live in this GPU's
+ * memory; a NULL flag is not waited for.  Waits are bounded by wait_limit_cycles (<= 0: about one second).
+ */
+#define TMW_HALO_MAX_COPIES 8
+
+typedef struct tmw_halo_copy {
+    const void* src; /* local memory */
+    void* dst;       /* local or peer-mapped memory */
+    size_t bytes;
+} tmw_halo_copy;
+
+typedef struct tmw_halo_wait {
+    const int32_t* pers_flag;
+    const int32_t* halo_flag;
+    int32_t value;
+    int32_t halo_rows;
+    int64_t wait_limit_cycles;
+} tmw_halo_wait;
+
+TMW_API int tmw_halo_push(const tmw_halo_copy* copies, int32_t n_copies, const int32_t* wait_flag, int32_t wait_value,
+                          int32_t* signal_flag, int32_t signal_value, int64_t wait_limit_cycles, void* stream);
+
+/*
+ * Mapping a buffer of another process of the same node (one process per GPU), for the destinations and flags of
+ * tmw_halo_push.  tmw_ipc_export describes the device allocation that holds ptr (allocations of cudaMalloc, which
+ * is what PyTorch's default allocator hands out); the 80-byte description travels to the other process by any
+ * means (the host side uses torch.distributed.all_gather_object).  tmw_ipc_open maps it with the CALLER'S current
+ * device as the one whose kernels will use the address, and returns the address of the same byte as ptr.  Every
+ * allocation is mapped once per process and device; tmw_ipc_close_all unmaps everything (call it, on every rank,
+ * before any rank frees an exported buffer).
+ */
+typedef struct tmw_ipc_mem {
+    unsigned char handle[64];
+    uint64_t offset; /* of the buffer inside its allocation */
+    uint64_t size;   /* of the allocation */
+} tmw_ipc_mem;
+
+TMW_API int tmw_ipc_export(const void* ptr, tmw_ipc_mem* out);
+TMW_API int tmw_ipc_open(const tmw_ipc_mem* mem, void** ptr);
+TMW_API int tmw_ipc_close_all(void);
+
+/* Enables peer access from the current device to peer_device (needed before tmw_halo_push stores into that GPU's
+ * memory through a mapping); already enabled is fine.  TMW_ERR_UNSUPPORTED when the devices have no peer path. */
+TMW_API int tmw_enable_peer_access(int32_t peer_device);
+
+TMW_API int tmw_prefill_halo(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v, void* o,
+                             const tmw_halo_wait* wait, void* stream);
+
+/*
  * Linear layer on the tensor cores: c[m, n] = sum_k a[m, k] * w[n, k] (+ bias[n]) (then the exact, erf-based GELU
  * when epilogue is TMW_EPILOGUE_GELU) - torch.nn.functional.linear with its [out_features, in_features] weight.
  * a: [m, k] row-major with leading dimension lda, w: [n, k] with ldw, c: [m, n] with ldc (elements); bias: [n]

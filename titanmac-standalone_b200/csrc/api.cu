@@ -194,6 +194,20 @@ int tmw_prefill(const tmw_prefill_desc* desc, const void* q, const void* k, cons
     return tmw::launch_prefill_simt(*desc, q, k, v, o, s);
 }
 
+int tmw_prefill_halo(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v, void* o,
+                     const tmw_halo_wait* wait, void* stream) {
+    const int rc = tmw::validate_prefill(desc, q, k, v, o);
+    if (rc != TMW_OK) return rc;
+    if (wait == nullptr || wait->halo_rows < 0 || wait->halo_rows > desc->k_rows - desc->n_persistent)
+        return TMW_ERR_INVALID_ARGUMENT;
+    if (desc->batch == 0 || desc->heads == 0 || desc->q_rows == 0) return TMW_OK;
+    if (desc->algo == TMW_ALGO_SIMT || !tmw::prefill_tc_supports(*desc, q, k, v, o)) {
+        tmw::set_error_text("tmw_prefill_halo: only the tensor-core kernel polls the flags (bf16 / f16, head_dim 64 or 128)");
+        return TMW_ERR_UNSUPPORTED;
+    }
+    return tmw::launch_prefill_tc(*desc, q, k, v, o, static_cast<cudaStream_t>(stream), 0, false, nullptr, wait);
+}
+
 int tmw_prefill_lse(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v, void* o, float* lse,
                     void* stream) {
     const int rc = tmw::validate_prefill(desc, q, k, v, o);
@@ -383,9 +397,13 @@ int tmw_poll_status(void* stream) {
         const int zero[4] = {0, 0, 0, 0};
         TMW_CUDA_TRY(cudaMemcpy(word, zero, sizeof(zero), cudaMemcpyHostToDevice));
         char text[160];
-        std::snprintf(text, sizeof(text), "device wait expired: barrier at shared offset %d parity %d, block (%d,%d,%d), warp %d",
-                      value[1] & 0xffff, (value[1] >> 16) & 1, value[2] & 0xffff, (value[2] >> 16) & 0xffff,
-                      value[3] & 0xffff, (value[3] >> 16) & 0xffff);
+        if (value[1] == -1)
+            std::snprintf(text, sizeof(text), "device wait expired: a halo flag that another GPU should have raised (block %d, detail %d)",
+                          value[2] & 0xffff, value[3]);
+        else
+            std::snprintf(text, sizeof(text), "device wait expired: barrier at shared offset %d parity %d, block (%d,%d,%d), warp %d",
+                          value[1] & 0xffff, (value[1] >> 16) & 1, value[2] & 0xffff, (value[2] >> 16) & 0xffff,
+                          value[3] & 0xffff, (value[3] >> 16) & 0xffff);
         tmw::set_error_text(text);
         return TMW_ERR_DEVICE_TIMEOUT;
     }

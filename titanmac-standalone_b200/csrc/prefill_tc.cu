@@ -90,7 +90,42 @@ struct TcParams {
     float scale_log2;
     int* status;
     float* lse;  // optional [batch, heads, q_rows]: log2 of the row's softmax denominator, in the scaled-by-log2(e) domain
+    // Sequence-sharded call whose K/V buffer is filled by other GPUs (tmw_halo_push): key rows [0, np) may be read
+    // once *pers_flag >= flag_value, key rows [np, np + halo_rows) once *halo_flag >= flag_value.  nullptr: no wait.
+    const int* pers_flag;
+    const int* halo_flag;
+    int flag_value;
+    int halo_rows;
+    long long flag_wait_limit;
 };
+
+// Bounded wait of a producer warp for a flag that another GPU raises in this GPU's memory after it has written
+// rows of the K/V buffer (release at system scope).  The rows are then read by TMA, i.e. through the asynchronous
+// proxy, hence the proxy fence after the acquire.  On expiry: TMW_ERR_DEVICE_TIMEOUT in the status word
+// (status[1] = -1 marks a flag, not an mbarrier), and nobody in the CTA waits any more.
+__device__ __forceinline__ void flag_wait(const int* flag, int value, long long limit, volatile int* abort_flag,
+                                          int* status) {
+    if ((threadIdx.x & 31) == 0) {
+        const long long t0 = clock64();
+        for (;;) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v >= value || *abort_flag) break;
+            if (clock64() - t0 > limit) {
+                *abort_flag = 1;
+                if (atomicCAS(status, 0, (int)TMW_ERR_DEVICE_TIMEOUT) == 0) {
+                    status[1] = -1;
+                    status[2] = (int)(blockIdx.x | (blockIdx.y << 16));
+                    status[3] = (int)(blockIdx.z | ((threadIdx.x >> 5) << 16));
+                }
+                break;
+            }
+            __nanosleep(100);
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");
+    }
+    __syncwarp();
+}
 
 // ---------------------------------------------------------------------------------
 // PTX wrappers
@@ -448,8 +483,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                                 bar(BAR_Q_FULL + t), s * 64, c1, c2, batch);
             }
             int n = 0;
+            bool halo_seen = p.halo_flag == nullptr;
             for (int x = plan.x_begin; x < plan.x_end; ++x, ++n) {
                 const int s = n % KS;
+                if (!halo_seen && p.np + plan.anchor + x * BN - p.k_pos0 < p.np + p.halo_rows) {
+                    flag_wait(p.halo_flag, p.flag_value, p.flag_wait_limit, abort_flag, p.status);
+                    halo_seen = true;
+                }
                 mbar_wait(bar(BAR_K_EMPTY + s), ((n / KS) & 1) ^ 1, abort_flag, p.status);
                 if (leader) {
                     mbar_expect_tx(bar(BAR_K_FULL + s), L::kTileBytes);
@@ -464,6 +504,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         } else if (warp == 1) {
             // ---------------- producer: persistent K/V, then V tiles ----------------
             // (the persistent maps end at row np: rows np .. np_pad - 1 of the tile arrive as zeros)
+            if (p.np > 0 && p.pers_flag != nullptr)
+                flag_wait(p.pers_flag, p.flag_value, p.flag_wait_limit, abort_flag, p.status);
             if (p.np > 0 && leader) {
                 mbar_expect_tx(bar(BAR_KP_FULL), 2 * pers_bytes);
                 int c1, c2;
@@ -476,8 +518,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                                 c1, c2, batch);
             }
             int n = 0;
+            bool halo_seen = p.halo_flag == nullptr;
             for (int x = plan.x_begin; x < plan.x_end; ++x, ++n) {
                 const int s = n % VS;
+                if (!halo_seen && p.np + plan.anchor + x * BN - p.k_pos0 < p.np + p.halo_rows) {
+                    flag_wait(p.halo_flag, p.flag_value, p.flag_wait_limit, abort_flag, p.status);
+                    halo_seen = true;
+                }
                 mbar_wait(bar(BAR_V_EMPTY + s), ((n / VS) & 1) ^ 1, abort_flag, p.status);
                 if (leader) {
                     mbar_expect_tx(bar(BAR_V_FULL + s), L::kTileBytes);
@@ -990,7 +1037,7 @@ int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
 
 template <int DH, int KS, int VS, int TILES>
 int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream,
-              int window_block, bool all_keys, float* lse) {
+              int window_block, bool all_keys, float* lse, const tmw_halo_wait* wait) {
     using L = TcSmem<DH, KS, VS, TILES>;
     const int np_pad = np_pad_of(d.n_persistent);
     CUtensorMap mq, mk, mv, mo, mkp, mvp;
@@ -1015,6 +1062,11 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     p.window_plan = d.window + (window_block > 0 ? window_block - 1 : 0);
     p.all_keys = all_keys ? 1 : 0;
     p.lse = lse;
+    p.pers_flag = wait != nullptr ? wait->pers_flag : nullptr;
+    p.halo_flag = wait != nullptr ? wait->halo_flag : nullptr;
+    p.flag_value = wait != nullptr ? wait->value : 0;
+    p.halo_rows = wait != nullptr ? wait->halo_rows : 0;
+    p.flag_wait_limit = wait != nullptr && wait->wait_limit_cycles > 0 ? wait->wait_limit_cycles : kWaitLimitCycles;
     p.q_pos0 = d.q_pos0; p.k_pos0 = d.k_pos0;
     p.dim_order = (sq.heads_first ? 1 : 0) | (sk.heads_first ? 2 : 0) | (sv.heads_first ? 4 : 0) | (so.heads_first ? 8 : 0);
     const float scale = d.scale != 0.f ? d.scale : 1.0f / sqrtf((float)DH);
@@ -1066,16 +1118,16 @@ bool prefill_tc_supports(const tmw_prefill_desc& d, const void*, const void*, co
 }
 
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                      cudaStream_t stream, int window_block, bool all_keys, float* lse) {
+                      cudaStream_t stream, int window_block, bool all_keys, float* lse, const tmw_halo_wait* wait) {
     if (d.head_dim == 64) {
         // One query tile per CTA and two CTAs per SM when two such CTAs fit into shared memory (they do
         // unless there are many persistent keys): independent CTAs drift apart, so one CTA's exponentials,
         // start-up and output phase overlap the other's matrix products.
         if (TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem)
-            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block, all_keys, lse);
-        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block, all_keys, lse);
+            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
+        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
     }
-    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream, window_block, all_keys, lse);
+    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
 }
 
 }  // namespace tmw

@@ -140,7 +140,8 @@ int validate_decode_call(const tmw_cache_desc* cache, const void* q, const void*
 int launch_prefill_simt(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
                         cudaStream_t stream, int window_block = 0, bool all_keys = false, float* lse = nullptr);
 int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o,
-                      cudaStream_t stream, int window_block = 0, bool all_keys = false, float* lse = nullptr);
+                      cudaStream_t stream, int window_block = 0, bool all_keys = false, float* lse = nullptr,
+                      const tmw_halo_wait* wait = nullptr);
 // window_block / pers_global select the mask of the block-sparse class (see first_visible_pos; pers_global: the
 // persistent query rows see every key, and lse comes as [batch, heads, rows - np] followed by [batch, heads, np])
 int launch_prefill_backward(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,

@@ -92,6 +92,26 @@ class LinearDesc(ctypes.Structure):
 
 
 EPILOGUE_NONE, EPILOGUE_GELU = 0, 1
+HALO_MAX_COPIES = 8
+
+
+class HaloCopy(ctypes.Structure):
+    _fields_ = [("src", ctypes.c_void_p), ("dst", ctypes.c_void_p), ("bytes", ctypes.c_size_t)]
+
+
+class IpcMem(ctypes.Structure):
+    _fields_ = [("handle", ctypes.c_ubyte * 64), ("offset", ctypes.c_uint64), ("size", ctypes.c_uint64)]
+
+
+class HaloWait(ctypes.Structure):
+    _fields_ = [
+        ("pers_flag", ctypes.c_void_p),
+        ("halo_flag", ctypes.c_void_p),
+        ("value", ctypes.c_int32),
+        ("halo_rows", ctypes.c_int32),
+        ("wait_limit_cycles", ctypes.c_int64),
+    ]
+
 
 # name -> (restype, argtypes); the CPU test-suite checks that every symbol here is
 # declared in include/tmw.h and exported by the library, and vice versa.
@@ -158,6 +178,19 @@ SIGNATURES = {
         [ctypes.POINTER(CacheDesc), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
          ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64),
          ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p],
+    ),
+    "tmw_halo_push": (
+        ctypes.c_int,
+        [ctypes.POINTER(HaloCopy), ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int32,
+         ctypes.c_int64, ctypes.c_void_p],
+    ),
+    "tmw_enable_peer_access": (ctypes.c_int, [ctypes.c_int32]),
+    "tmw_ipc_export": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(IpcMem)]),
+    "tmw_ipc_open": (ctypes.c_int, [ctypes.POINTER(IpcMem), ctypes.POINTER(ctypes.c_void_p)]),
+    "tmw_ipc_close_all": (ctypes.c_int, []),
+    "tmw_prefill_halo": (
+        ctypes.c_int,
+        [ctypes.POINTER(PrefillDesc)] + [ctypes.c_void_p] * 4 + [ctypes.POINTER(HaloWait), ctypes.c_void_p],
     ),
     "tmw_linear": (ctypes.c_int, [ctypes.POINTER(LinearDesc)] + [ctypes.c_void_p] * 5),
     "tmw_gelu": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
@@ -232,8 +265,12 @@ def prefill(
     algo: int = ALGO_AUTO,
     window_block: int = 0,
     lse: Optional[torch.Tensor] = None,
+    halo_wait: Optional[HaloWait] = None,
 ) -> torch.Tensor:
     """``tmw_prefill`` on ``[B, H, rows, dh]`` tensors (any strides with a contiguous last axis).
+
+    ``halo_wait`` selects ``tmw_prefill_halo``: the kernel polls the given flags before it reads the persistent /
+    halo rows of the K/V buffer (sequence-sharded ranks whose neighbours push those rows, see ``halo_push``).
 
     ``window_block > 0`` selects ``tmw_prefill_block_sparse``: the mask of the reference's
     BlockSparseAttention with that block size (whole sequences only).  ``lse`` (fp32 ``[B, H, rows]``,
@@ -259,7 +296,12 @@ def prefill(
     d.v_stride[:] = _bhrd_strides(v)
     d.o_stride[:] = _bhrd_strides(out)
     with torch.cuda.device(q.device):
-        if lse is not None:
+        if halo_wait is not None:
+            if lse is not None or window_block > 0:
+                raise ValueError("halo_wait goes with the plain windowed prefill only")
+            check(lib().tmw_prefill_halo(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                         ctypes.byref(halo_wait), _stream_ptr(q.device)))
+        elif lse is not None:
             if lse.dtype != torch.float32 or lse.numel() != B * H * rq or not lse.is_contiguous() or lse.device != q.device:
                 raise ValueError("lse must be a contiguous fp32 tensor of B * H * rows elements on the same device")
             if window_block > 0:  # two planes: [B, H, rows - Np] then [B, H, Np]
@@ -461,6 +503,52 @@ def gelu(x: torch.Tensor, inplace: bool = False) -> torch.Tensor:
     with torch.cuda.device(x.device):
         check(lib().tmw_gelu(_DTYPES[x.dtype], x.numel(), x.data_ptr(), y.data_ptr(), _stream_ptr(x.device)))
     return y
+
+
+def enable_peer_access(device, peer_device) -> None:
+    """Kernels running on ``device`` may then store into ``peer_device``'s memory (``tmw_enable_peer_access``)."""
+    with torch.cuda.device(device):
+        check(lib().tmw_enable_peer_access(torch.device(peer_device).index))
+
+
+def ipc_export(t: torch.Tensor) -> bytes:
+    """Description of the allocation behind a CUDA tensor for another process of this node (``tmw_ipc_export``)."""
+    _require_cuda(t)
+    mem = IpcMem()
+    with torch.cuda.device(t.device):
+        check(lib().tmw_ipc_export(t.data_ptr(), ctypes.byref(mem)))
+    return bytes(mem)
+
+
+def ipc_open(blob: bytes, device) -> int:
+    """Address, valid for kernels running on ``device``, of the buffer another process exported (``tmw_ipc_open``)."""
+    mem = IpcMem.from_buffer_copy(blob)
+    out = ctypes.c_void_p()
+    with torch.cuda.device(device):
+        check(lib().tmw_ipc_open(ctypes.byref(mem), ctypes.byref(out)))
+    return int(out.value)
+
+
+def ipc_close_all() -> None:
+    check(lib().tmw_ipc_close_all())
+
+
+def halo_push(copies, device, wait_flag: int = 0, wait_value: int = 0, signal_flag: int = 0, signal_value: int = 0,
+              wait_limit_cycles: int = 0) -> None:
+    """``tmw_halo_push`` on the current stream of ``device``.  ``copies``: a list of ``(src_ptr, dst_ptr, nbytes)``
+    (device addresses; ``dst`` may be a peer mapping); ``wait_flag`` / ``signal_flag``: device addresses of int32
+    flags or 0.  More than ``HALO_MAX_COPIES`` copies are spread over several launches: the first one waits, the
+    last one signals."""
+    groups = [copies[i:i + HALO_MAX_COPIES] for i in range(0, len(copies), HALO_MAX_COPIES)] or [[]]
+    with torch.cuda.device(device):
+        for gi, group in enumerate(groups):
+            arr = (HaloCopy * max(1, len(group)))()
+            for j, (s, d_, n) in enumerate(group):
+                arr[j].src, arr[j].dst, arr[j].bytes = s, d_, n
+            first, last = gi == 0, gi == len(groups) - 1
+            check(lib().tmw_halo_push(arr, len(group), wait_flag if first and wait_flag else None, wait_value,
+                                      signal_flag if last and signal_flag else None, signal_value, wait_limit_cycles,
+                                      _stream_ptr(device)))
 
 
 def linear_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:

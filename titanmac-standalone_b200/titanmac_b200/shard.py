@@ -232,3 +232,156 @@ def sharded_prefill(q_own: torch.Tensor, k_own: Optional[torch.Tensor], v_own: O
                     q_pos0=kv.q_pos0, k_pos0=kv.k_pos0, algo=algo)
     main.wait_stream(side)
     return out
+
+
+# ------------------------------------------------------------------------------------------------------------
+# The same step without a host-side collective: producers push, the attention kernel polls
+# ------------------------------------------------------------------------------------------------------------
+class _PeerBuffers:
+    """Addresses (valid for kernels on this rank's GPU) of another rank's K rows, V rows and flag words, and the
+    number of rows of its buffers."""
+
+    def __init__(self, k_addr: int, v_addr: int, flags_addr: int, rows: int):
+        self.k, self.v, self.flags, self.rows = k_addr, v_addr, flags_addr, rows
+
+
+class PeerShardedKV(ShardedKV):
+    """``ShardedKV`` whose persistent and halo regions are written by the OTHER ranks' GPUs.
+
+    Every rank maps the buffers and flag words of the ranks it writes to (``tmw_ipc_export`` / ``tmw_ipc_open``,
+    once at set-up; one process per GPU on one node).  A step is then, on each rank's stream and with no host-side collective:
+
+      1. ``push()``     - the rank's last ``window`` rows of K and V go into the right neighbour's halo region
+                          and (rank 0) the persistent rows into every other rank's buffer: ``tmw_halo_push``,
+                          plain stores through the peer mapping, then a release store of the step number to the
+                          destination's "ready" flag.  A push first waits until the destination has acknowledged
+                          the previous step (it may still be reading the rows about to be overwritten).
+      2. the attention launch with ``wait()`` - ``tmw_prefill_halo`` polls the ready flags right before the first
+                          TMA load that touches pushed rows; tiles whose window is local start at once.
+      3. ``ack()``      - after the attention kernel (stream order) the rank tells its producers that the step's
+                          rows have been read.
+
+    Restricted to shards at least one window long (the halo then comes from exactly one neighbour); shorter
+    shards use the collective form (``ShardedKV.exchange``).  All device-side waits are bounded and surface
+    as ``TMW_ERR_DEVICE_TIMEOUT`` through ``_native.poll_status``.
+    """
+
+    # flag words in every rank's own memory
+    READY_PERS, READY_HALO, ACK_HALO, ACK_PERS0 = 0, 1, 2, 3  # ACK_PERS0 + d: rank d has read the persistent rows
+
+    @classmethod
+    def allocate(cls, batch: int, heads: int, head_dim: int, total_rows: int, window: int, n_persistent: int,
+                 dtype: torch.dtype, device, group: Optional[dist.ProcessGroup] = None,
+                 wait_limit_cycles: int = 0) -> "PeerShardedKV":
+        self = cls.__new__(cls)
+        self._layout(total_rows, window, n_persistent, group)
+        for r in range(1, self.world):
+            if halo_rows(self.bounds, r, window, n_persistent) > self.bounds[r - 1][1] - max(self.bounds[r - 1][0],
+                                                                                            n_persistent):
+                raise ValueError("PeerShardedKV needs shards of at least `window` rows (one halo source per rank)")
+        self._buffers(batch, heads, head_dim, dtype, device)
+        self.device = torch.device(device)
+        self.wait_limit_cycles = wait_limit_cycles
+        self.flags = torch.zeros(self.ACK_PERS0 + self.world, dtype=torch.int32, device=device)
+        self.step = 0
+        # exchange the mappings: every rank publishes its two buffers and its flags (tmw_ipc_export), and maps
+        # those of the ranks it writes to with its own GPU current (tmw_ipc_open)
+        from . import _native
+
+        mine = (_native.ipc_export(self._k_rows), _native.ipc_export(self._v_rows), _native.ipc_export(self.flags),
+                self._k_rows.shape[1])
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=group)
+        self._peer = {}
+        need = set()
+        if self.rank + 1 < self.world:
+            need.add(self.rank + 1)           # halo goes to the right neighbour
+        if self.rank > 0:
+            need.update({self.rank - 1, 0})   # acknowledgements go to the left neighbour and to rank 0
+        if self.rank == 0:
+            need.update(range(1, self.world))  # persistent rows go to everyone
+        for r in sorted(need):
+            kb, vb, fb, rows = everyone[r]
+            self._peer[r] = _PeerBuffers(_native.ipc_open(kb, self.device), _native.ipc_open(vb, self.device),
+                                         _native.ipc_open(fb, self.device), rows)
+        dist.barrier(group=group)
+        return self
+
+    def close(self) -> None:
+        """Collective: every rank drops its mappings of the others' memory before anybody frees its own."""
+        from . import _native
+
+        torch.cuda.synchronize(self.device)
+        self._peer.clear()
+        _native.ipc_close_all()
+        dist.barrier(group=self.group)
+
+    def push(self) -> None:
+        from . import _native
+
+        self.step += 1
+        e, Np = self.step, self.n_persistent
+        row_bytes = self._k_rows.shape[2] * self._k_rows.shape[3] * self._k_rows.element_size()
+        B, my_rows = self._k_rows.shape[0], self._k_rows.shape[1]
+        my_flags = self.flags.data_ptr()
+
+        def copies(dst: _PeerBuffers, src_row: int, dst_row: int, n: int):
+            # buffer rows [src_row, src_row + n) of every batch element of K and V -> the destination's rows
+            # [dst_row, dst_row + n)
+            return [(base.data_ptr() + (b * my_rows + src_row) * row_bytes,
+                     dst_base + (b * dst.rows + dst_row) * row_bytes, n * row_bytes)
+                    for base, dst_base in ((self._k_rows, dst.k), (self._v_rows, dst.v)) for b in range(B)]
+
+        if self.rank + 1 < self.world:
+            dst = self._peer[self.rank + 1]
+            n = halo_rows(self.bounds, self.rank + 1, self.window, Np)
+            _native.halo_push(copies(dst, my_rows - n, Np, n), self.device,
+                              wait_flag=my_flags + 4 * self.ACK_HALO, wait_value=e - 1,
+                              signal_flag=dst.flags + 4 * self.READY_HALO, signal_value=e,
+                              wait_limit_cycles=self.wait_limit_cycles)
+        if self.rank == 0 and Np > 0:
+            for d in range(1, self.world):
+                dst = self._peer[d]
+                _native.halo_push(copies(dst, 0, 0, Np), self.device,
+                                  wait_flag=my_flags + 4 * (self.ACK_PERS0 + d), wait_value=e - 1,
+                                  signal_flag=dst.flags + 4 * self.READY_PERS, signal_value=e,
+                                  wait_limit_cycles=self.wait_limit_cycles)
+
+    def wait(self):
+        """The ``halo_wait`` argument of ``_native.prefill`` for the current step (None on rank 0)."""
+        from . import _native
+
+        if self.rank == 0:
+            return None
+        w = _native.HaloWait()
+        w.pers_flag = self.flags.data_ptr() + 4 * self.READY_PERS if self.n_persistent > 0 else None
+        w.halo_flag = self.flags.data_ptr() + 4 * self.READY_HALO if self.halo > 0 else None
+        w.value, w.halo_rows, w.wait_limit_cycles = self.step, self.halo, self.wait_limit_cycles
+        return w
+
+    def ack(self) -> None:
+        from . import _native
+
+        if self.rank == 0:
+            return
+        e = self.step
+        if self.halo > 0:
+            _native.halo_push([], self.device, signal_flag=self._peer[self.rank - 1].flags + 4 * self.ACK_HALO,
+                              signal_value=e)
+        if self.n_persistent > 0:
+            _native.halo_push([], self.device, signal_flag=self._peer[0].flags + 4 * (self.ACK_PERS0 + self.rank),
+                              signal_value=e)
+
+
+def pushed_prefill(q_own: torch.Tensor, kv: PeerShardedKV, algo: int = 0) -> torch.Tensor:
+    """Attention output for this rank's rows with the halo pushed by the neighbours' GPUs: push, one attention
+    launch that polls the flags, acknowledgement.  ``kv.k_own`` / ``kv.v_own`` hold this rank's rows."""
+    from . import _native
+
+    B, H, own, dh = q_own.shape
+    out = torch.empty((B, own, H, dh), dtype=q_own.dtype, device=q_own.device).permute(0, 2, 1, 3)
+    kv.push()
+    _native.prefill(q_own, kv.k, kv.v, kv.window, kv.n_persistent, out=out, q_pos0=kv.q_pos0, k_pos0=kv.k_pos0,
+                    algo=algo, halo_wait=kv.wait())
+    kv.ack()
+    return out
