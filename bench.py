@@ -371,22 +371,37 @@ def region_stats(regions, steps: int, world: int, dev) -> dict:
 
 
 def pcie_ceiling(nbytes: int, world: int, dev, barrier, iters: int = 10) -> dict:
-    """Plain pinned-memory copies of `nbytes`, every rank at the same time and nothing else running: what the
-    host links give when all GPUs copy at once - the ceiling of the end-to-end leg."""
-    host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
-    devb = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    """Plain pinned-memory copies of `nbytes`, every rank at the same time and nothing else running: each
+    direction alone, then both directions at once on two streams (what the end-to-end leg does in steady state).
+    What the host links and the host memory give when all GPUs copy at once is the ceiling of that leg."""
+    hosts = [torch.empty(nbytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
+    devs = [torch.empty(nbytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    streams = [torch.cuda.Stream(dev) for _ in range(2)]
     out = {}
-    for name, (dst, src) in (("h2d", (devb, host)), ("d2h", (host, devb))):
-        dst.copy_(src, non_blocking=True)
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(directions):
+        for d_ in directions:
+            with torch.cuda.stream(streams[d_]):
+                (devs[0].copy_(hosts[0], non_blocking=True) if d_ == 0 else hosts[1].copy_(devs[1], non_blocking=True))
         barrier()
-        a.record()
-        for _ in range(iters):
-            dst.copy_(src, non_blocking=True)
-        b.record()
+        evs = []
+        for d_ in directions:
+            with torch.cuda.stream(streams[d_]):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(iters):
+                    (devs[0].copy_(hosts[0], non_blocking=True) if d_ == 0 else hosts[1].copy_(devs[1], non_blocking=True))
+                b.record()
+                evs.append((a, b))
         barrier()
-        gbs = nbytes * iters / (a.elapsed_time(b) * 1e-3) / 1e9
-        out[name + "_gbs_per_rank"] = [round(float(v), 2) for v in gather_ranks([gbs], world, dev)[:, 0]]
+        return [nbytes * iters / (a.elapsed_time(b) * 1e-3) / 1e9 for a, b in evs]
+
+    per_rank = lambda v: [round(float(x), 2) for x in gather_ranks([v], world, dev)[:, 0]]  # noqa: E731
+    out["h2d_alone_gbs_per_rank"] = per_rank(timed([0])[0])
+    out["d2h_alone_gbs_per_rank"] = per_rank(timed([1])[0])
+    both = timed([0, 1])
+    out["h2d_with_d2h_gbs_per_rank"] = per_rank(both[0])
+    out["d2h_with_h2d_gbs_per_rank"] = per_rank(both[1])
     return out
 
 

@@ -283,7 +283,9 @@ TMW_API int tmw_cache_fill(const tmw_cache_desc* cache, const void* k, const voi
 /*
  * One decode step.  q, k_new, v_new, o: [batch, heads, head_dim] through
  * {batch, head} strides.  pos: device array [batch] of int32, the sequence index
- * t of the new token.  The call stores k_new/v_new into slot t % (window+1) and
+ * t >= 0 of the new token (the host cannot see a device array: a negative entry is
+ * treated as 0 by the kernels and reported by tmw_poll_status as
+ * TMW_ERR_INVALID_ARGUMENT).  The call stores k_new/v_new into slot t % (window+1) and
  * attends over the persistent keys and the min(t+1, window+1) newest slots.
  */
 TMW_API int tmw_decode(const tmw_cache_desc* cache, const void* q, const void* k_new, const void* v_new, void* o,

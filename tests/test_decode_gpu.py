@@ -145,3 +145,24 @@ def test_split_and_unsplit_decode_agree(splits):
     for b, t in enumerate(ts):
         want = wo.attention_core_rows(q[b:b + 1, :, Np + t:Np + t + 1], k[b:b + 1], v[b:b + 1], Np + t, w, Np)
         assert (outs[0][0][b] - want[0, :, 0]).abs().max().item() <= 2e-2
+
+
+def test_negative_position_is_reported_not_written_out_of_bounds():
+    """pos is a device array the host cannot check: a negative entry is treated as position 0 by the kernels and
+    comes back from tmw_poll_status as an invalid argument."""
+    B, H, dh, w, Np = 3, 2, 64, 16, 4
+    cache = _native.RingCache(B, H, dh, w, Np, torch.bfloat16, DEV)
+    for t_ in (cache.k_ring, cache.v_ring, cache.k_pers, cache.v_pers):
+        t_.normal_()
+    guard_k = cache.k_ring.clone()
+    x = torch.randn(B, 3, H, dh, device=DEV).to(torch.bfloat16)
+    pos = torch.tensor([5, -7, 2], dtype=torch.int32, device=DEV)
+    out = cache.decode(x[:, 0], x[:, 1], x[:, 2], pos)
+    with pytest.raises(_native.TmwError) as e:
+        _native.poll_status(torch.device(DEV))
+    assert e.value.status == _native.TMW_ERR_INVALID_ARGUMENT
+    assert torch.isfinite(out.float()).all()
+    # only the slots of positions 5, 0 (the negative one) and 2 changed
+    changed = (cache.k_ring != guard_k).any(dim=-1).any(dim=1)  # [B, slots]
+    assert changed.nonzero().tolist() == [[0, 5], [1, 0], [2, 2]]
+    _native.poll_status(torch.device(DEV))  # the status word was cleared

@@ -79,6 +79,47 @@ def test_static_scratch_decode_matches_caller_scratch_decode_twice():
         assert (got[b].float().cpu() - ref[0, :, 0]).abs().max().item() <= 2e-2
 
 
+def test_static_calls_follow_one_another_on_a_stream_without_synchronising():
+    """Two calls with different geometries (6 splits over 6 pairs, then 3 splits over 2 pairs) issued back to back:
+    the second reuses the built-in array as soon as the first has finished on the stream - the host does not
+    wait in between."""
+    dh, w, Np = 64, 1200, 8
+
+    def case(B, H, t, seed):
+        q, k, v = (x.to(torch.bfloat16) for x in wo.qkv_inputs(B, H, Np + t + 1, dh, seed=seed))
+        k[1:, :, :Np] = k[:1, :, :Np]
+        v[1:, :, :Np] = v[:1, :, :Np]
+
+        def cache():
+            c = _native.RingCache(B, H, dh, w, Np, torch.bfloat16, DEV)
+            c.set_persistent(k[0, :, :Np].to(DEV), v[0, :, :Np].to(DEV))
+            c.fill(k[:, :, Np:Np + t].to(DEV), v[:, :, Np:Np + t].to(DEV))
+            return c
+
+        new = tuple(x[:, :, Np + t].to(DEV) for x in (q, k, v))
+        return cache, new, torch.full((B,), t, dtype=torch.int32, device=DEV)
+
+    cases = [case(2, 3, 1500, 41) + (6,), case(1, 2, 1300, 42) + (3,)]
+    want = []
+    for cache, (qn, kn, vn), pos, splits in cases:
+        c = cache()
+        nbytes = _native.lib().tmw_decode_split_scratch_bytes(ctypes.byref(c.desc()), splits)
+        scratch = torch.zeros(nbytes // 4, dtype=torch.float32, device=DEV)
+        rc, out = _call(c, "tmw_decode_split", qn, kn, vn, pos, splits, scratch)
+        assert rc == _native.TMW_OK
+        want.append(out)
+    caches = [cache() for cache, _, _, _ in cases]
+    torch.cuda.synchronize()
+    got = []
+    for c, (_, (qn, kn, vn), pos, splits) in zip(caches, cases):  # no synchronisation between the two calls
+        rc, out = _call(c, "tmw_decode_split_static", qn, kn, vn, pos, splits)
+        assert rc == _native.TMW_OK
+        got.append(out)
+    torch.cuda.synchronize()
+    for g, w_ in zip(got, want):
+        assert (g.float() - w_.float()).abs().max().item() <= 4e-3
+
+
 def test_static_scratch_decode_refuses_what_does_not_fit():
     lib = _native.lib()
     big = _native.RingCache(512, 10, 64, 8, 0, torch.bfloat16, DEV)  # 5120 pairs > 4096

@@ -1,5 +1,6 @@
 // C-ABI entry points of libtmw: argument validation, kernel selection, error text.
 // Everything that can be rejected is rejected here, on the host, before a launch.
+#include <atomic>
 #include <cstdio>
 #include <mutex>
 #include <cstring>
@@ -25,15 +26,16 @@ __device__ int g_device_status[4] = {0, 0, 0, 0};  // [0] status, [1..3] where t
 
 int* device_status_word() {
     constexpr int kMaxDevices = 64;
-    static int* cache[kMaxDevices] = {nullptr};
+    // written once per device; two host threads making the first call on a device store the same value
+    static std::atomic<int*> cache[kMaxDevices];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-    if (cache[dev] == nullptr) {
+    if (cache[dev].load(std::memory_order_acquire) == nullptr) {
         void* ptr = nullptr;
         if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
-        cache[dev] = static_cast<int*>(ptr);
+        cache[dev].store(static_cast<int*>(ptr), std::memory_order_release);
     }
-    return cache[dev];
+    return cache[dev].load(std::memory_order_acquire);
 }
 
 // One side stream and two events per device, made on first use and kept for the life of the process (make
@@ -397,6 +399,10 @@ int tmw_poll_status(void* stream) {
         const int zero[4] = {0, 0, 0, 0};
         TMW_CUDA_TRY(cudaMemcpy(word, zero, sizeof(zero), cudaMemcpyHostToDevice));
         char text[160];
+        if (value[0] == TMW_ERR_INVALID_ARGUMENT) {
+            tmw::set_error_text("a kernel met an invalid device-side argument (a negative entry of pos in a decode call)");
+            return TMW_ERR_INVALID_ARGUMENT;
+        }
         if (value[1] == -1)
             std::snprintf(text, sizeof(text), "device wait expired: a halo flag that another GPU should have raised (block %d, detail %d)",
                           value[2] & 0xffff, value[3]);

@@ -19,6 +19,8 @@
 
 #include <cstdio>
 
+#include <atomic>
+
 #include "tmw_common.cuh"
 
 #ifndef TMW_DECODE_STREAM
@@ -130,7 +132,13 @@ decode_kernel(const DecodeParams p) {
     const int sub = lane % LPK;  // which 8-element slice of the row
     const int grp = lane / LPK;  // which row of the warp's RPW rows
 
-    const int t = p.pos[b];
+    int t = p.pos[b];
+    if (t < 0) {
+        // a negative position would put the new row in front of the ring: treated as position 0 (nothing is
+        // written out of bounds) and reported through the status word as an invalid argument
+        if (lane == 0) atomicCAS(p.status, 0, (int)TMW_ERR_INVALID_ARGUMENT);
+        t = 0;
+    }
     const int slot_new = t % p.slots;
     const int count = min(t + 1, p.slots);
     const long long ring_bh = ((long long)b * p.heads + h) * p.slots * DH;
@@ -408,7 +416,13 @@ decode_stream_kernel(const DecodeParams p) {
 
     const int b = pair / p.heads, h = pair % p.heads;
     const int sub = lane % LPK, grp = lane / LPK;
-    const int t = p.pos[b];
+    int t = p.pos[b];
+    if (t < 0) {
+        // a negative position would put the new row in front of the ring: treated as position 0 (nothing is
+        // written out of bounds) and reported through the status word as an invalid argument
+        if (lane == 0) atomicCAS(p.status, 0, (int)TMW_ERR_INVALID_ARGUMENT);
+        t = 0;
+    }
     const int slot_new = t % p.slots;
     const int count = min(t + 1, p.slots);
     const long long ring_bh = ((long long)b * p.heads + h) * p.slots * DH;
@@ -791,23 +805,24 @@ static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticSc
 // device address of the array on the current device; nullptr (and the CUDA error recorded) on failure
 unsigned char* static_scratch_on_current_device() {
     constexpr int kMaxDevices = 64;
-    static unsigned char* address[kMaxDevices] = {nullptr};
+    // written once per device; two host threads making the first call on a device store the same value
+    static std::atomic<unsigned char*> address[kMaxDevices];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
         tmw::set_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidDevice, "cudaGetDevice");
         return nullptr;
     }
-    if (address[dev] == nullptr) {
+    if (address[dev].load(std::memory_order_acquire) == nullptr) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
         if (e != cudaSuccess) {
             tmw::set_cuda_error(e, "cudaGetSymbolAddress(g_decode_static_scratch)");
             return nullptr;
         }
-        address[dev] = static_cast<unsigned char*>(ptr);
+        address[dev].store(static_cast<unsigned char*>(ptr), std::memory_order_release);
     }
-    return address[dev];
+    return address[dev].load(std::memory_order_acquire);
 }
 
 }  // namespace
