@@ -80,9 +80,7 @@ WORKLOADS = {
 # exactly the geometry of the workload (config 2: batch 8, L = 4112, 10 heads x 64, window 512: Q + K + V read
 # once = 126.4 MB, 24.8 MB of the 42.1 MB of O written back before the kernel ends).  None = not captured for
 # the kernel as it is now.
-NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126459392 + 24759296,
-                     # backward: the dQ kernel plus the dK/dV kernel (one call launches both)
-                     "config2_layer_train": (211887360 + 32490752) + (235155200 + 69292800)}
+NCU_TRAFFIC_BYTES = {"config2_layer_prefill": 126459392 + 24759296}
 
 MIN_TIMED_SECONDS = 0.5  # the --steps region is repeated until at least this much device time has been timed
 
@@ -927,8 +925,8 @@ def run_train(args, wl_name: str, wl: dict) -> None:
             "config": dict(workload=wl_name, **wl, global_batch=B * world, parallelism=f"batch-sharded x{world}",
                            l2="inputs rotate over 4 sets; activations + gradients per step > 126 MB L2",
                            flops_per_step_per_gpu=flops),
-            "roofline": {"bound": "tensor", "kernel": "attention-core backward (tmw_prefill_backward: dQ and dK/dV "
-                         "kernels, warp-level tensor cores)", "achieved": achieved, "peak": peaks["bf16_tflops"],
+            "roofline": {"bound": "tensor", "kernel": "attention-core backward (tmw_prefill_backward: dK/dV and dQ "
+                         "launches of the tcgen05 kernel; the block-sparse class: warp-level tensor cores)", "achieved": achieved, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                          "peak_source": f"{peaks['source']} bf16 burst", "avg_launch_ms": core_ms, "traffic": NCU_TRAFFIC_BYTES.get(wl_name),
                          "algorithmic_flops_per_launch": flops["core_bwd"]},

@@ -55,7 +55,8 @@ typedef enum tmw_dtype { TMW_F32 = 0, TMW_BF16 = 1, TMW_F16 = 2 } tmw_dtype;
 typedef enum tmw_algo {
     TMW_ALGO_AUTO = 0,   /* tcgen05 kernel when it applies, otherwise the CUDA-core kernel       */
     TMW_ALGO_SIMT = 1,   /* CUDA-core kernel (every dtype, head_dim 8/16/32/64/96/128/256)       */
-    TMW_ALGO_TCGEN05 = 2 /* tensor-core kernel (bf16/f16, head_dim 64 or 128)                    */
+    TMW_ALGO_TCGEN05 = 2,/* tensor-core kernel (bf16/f16, head_dim 64 or 128)                    */
+    TMW_ALGO_MMA = 3     /* backward only: the warp-level tensor-core kernels (mma.sync class)   */
 } tmw_algo;
 
 /*
@@ -103,8 +104,10 @@ TMW_API int tmw_prefill_lse(const tmw_prefill_desc* desc, const void* q, const v
  * given d_o (gradient of o, addressed like o) and the o and lse of tmw_prefill_lse, writes dq, dk, dv
  * (addressed like q, k, v: the same strides).  Replaces what autograd does through the reference's mask
  * conversion and scaled-dot-product call (windowed_attention.py:307-323) - there over all L x L pairs,
- * here over the visible pairs only.  Warp-level tensor cores (fp32 accumulation) for bf16 / f16 with head_dim
- * 64 or 128; fp32 arithmetic on CUDA cores otherwise, or for every case when desc->algo is TMW_ALGO_SIMT.
+ * here over the visible pairs only.  For bf16 / f16 with head_dim 64 or 128: tcgen05 kernels (products and the
+ * 16-bit intermediates in tensor memory; desc->algo TMW_ALGO_AUTO or TMW_ALGO_TCGEN05), or the older warp-level
+ * tensor-core kernels (TMW_ALGO_MMA); fp32 arithmetic on CUDA cores otherwise, or for every case with
+ * TMW_ALGO_SIMT.  All of them accumulate in fp32.
  */
 TMW_API int tmw_prefill_backward(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v,
                                  const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,

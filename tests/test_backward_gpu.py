@@ -43,7 +43,11 @@ def test_module_gradients_match_reference_fp32(bz):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 4e-2)])
 @pytest.mark.parametrize("dh,H,B,L,w,Np", [(64, 2, 2, 16 + 500, 128, 16), (128, 1, 1, 8 + 300, 64, 8),
-                                           (32, 3, 1, 90, 200, 0), (16, 1, 2, 5 + 70, 0, 5)])
+                                           (32, 3, 1, 90, 200, 0), (16, 1, 2, 5 + 70, 0, 5),
+                                           (64, 1, 1, 16 + 1500, 300, 16),   # windows over several tiles, ragged tail
+                                           (64, 2, 1, 700, 256, 0),          # no persistent keys
+                                           (64, 1, 1, 130 + 400, 100, 130),  # persistent keys over two tiles
+                                           (128, 2, 1, 16 + 900, 512, 16)])
 def test_core_gradients_against_oracle_autograd(dtype, tol, dh, H, B, L, w, Np):
     q, k, v = (t.to(dtype) for t in wo.qkv_inputs(B, H, L, dh, seed=dh + L))
     g = torch.randn(B, H, L, dh, generator=torch.Generator().manual_seed(1)).to(dtype)
@@ -53,7 +57,8 @@ def test_core_gradients_against_oracle_autograd(dtype, tol, dh, H, B, L, w, Np):
 
     qd, kd, vd = (t.to(DEV) for t in (q, k, v))
     lse = torch.empty(B, H, L, dtype=torch.float32, device=DEV)
-    for algo in ([_native.ALGO_SIMT] if dtype == torch.float32 or dh not in (64, 128)
+    # (the tensor-core FORWARD kernel keeps the persistent keys in one tile of at most 128)
+    for algo in ([_native.ALGO_SIMT] if dtype == torch.float32 or dh not in (64, 128) or Np > 128
                  else [_native.ALGO_SIMT, _native.ALGO_TCGEN05]):
         o = _native.prefill(qd, kd, vd, w, Np, algo=algo, lse=lse)      # [B, H, L, dh] view of [B, L, H, dh]
         # lse is log2-domain: log2 sum_j exp2(s * scale * log2 e)
@@ -63,7 +68,11 @@ def test_core_gradients_against_oracle_autograd(dtype, tol, dh, H, B, L, w, Np):
         assert (lse.cpu() - want_lse).abs().max().item() <= (1e-4 if dtype == torch.float32 else 3e-2), algo
         d_o = torch.empty_like(o)
         d_o.copy_(g.to(DEV))
-        for bwd_algo in (_native.ALGO_SIMT, _native.ALGO_AUTO):  # CUDA-core kernels, then tensor cores where they apply
+        # CUDA-core kernels; for 16-bit types and head_dim 64 / 128 also the warp-level tensor-core kernels and the
+        # tcgen05 kernels (which is what the library picks by itself there)
+        tensor_core = dtype != torch.float32 and dh in (64, 128)
+        for bwd_algo in ((_native.ALGO_SIMT, _native.ALGO_MMA, _native.ALGO_TCGEN05, _native.ALGO_AUTO) if tensor_core
+                         else (_native.ALGO_SIMT, _native.ALGO_AUTO)):
             dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
             _native.prefill_backward(qd, kd, vd, o, d_o, lse, dq, dk, dv, w, Np, algo=bwd_algo)
             for got, want, nm in ((dq, qr.grad, "dq"), (dk, kr.grad, "dk"), (dv, vr.grad, "dv")):

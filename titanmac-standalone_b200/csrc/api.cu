@@ -96,7 +96,7 @@ bool strides_ok(const int64_t* s, int n, int dtype) {
 int validate_prefill(const tmw_prefill_desc* d, const void* q, const void* k, const void* v, const void* o) {
     if (d == nullptr) return TMW_ERR_INVALID_ARGUMENT;
     if (!dtype_ok(d->dtype)) return TMW_ERR_UNSUPPORTED;
-    if (d->algo < TMW_ALGO_AUTO || d->algo > TMW_ALGO_TCGEN05) return TMW_ERR_INVALID_ARGUMENT;
+    if (d->algo < TMW_ALGO_AUTO || d->algo > TMW_ALGO_MMA) return TMW_ERR_INVALID_ARGUMENT;
     if (d->batch < 0 || d->heads < 0 || d->head_dim <= 0 || d->q_rows < 0 || d->k_rows < 0 ||
         d->n_persistent < 0 || d->q_pos0 < 0)
         return TMW_ERR_INVALID_ARGUMENT;
@@ -187,6 +187,7 @@ int tmw_prefill(const tmw_prefill_desc* desc, const void* q, const void* k, cons
     if (rc != TMW_OK) return rc;
     if (desc->batch == 0 || desc->heads == 0 || desc->q_rows == 0) return TMW_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (desc->algo == TMW_ALGO_MMA) return TMW_ERR_UNSUPPORTED;  // a backward-only choice
     const bool tc_ok = tmw::prefill_tc_supports(*desc, q, k, v, o);
     if (desc->algo == TMW_ALGO_TCGEN05) {
         if (!tc_ok) return TMW_ERR_UNSUPPORTED;
@@ -235,7 +236,13 @@ int tmw_prefill_backward(const tmw_prefill_desc* desc, const void* q, const void
     if (d_o == nullptr || lse == nullptr || dq == nullptr || dk == nullptr || dv == nullptr) return TMW_ERR_INVALID_ARGUMENT;
     if (!tmw::aligned16(d_o) || !tmw::aligned16(dq) || !tmw::aligned16(dk) || !tmw::aligned16(dv))
         return TMW_ERR_INVALID_ARGUMENT;
-    // desc->algo: TMW_ALGO_SIMT pins the CUDA-core kernels; otherwise the tensor-core kernels where they apply
+    // desc->algo: TMW_ALGO_SIMT pins the CUDA-core kernels, TMW_ALGO_MMA the warp-level tensor-core kernels,
+    // TMW_ALGO_TCGEN05 the tcgen05 kernels; TMW_ALGO_AUTO takes the fastest path that applies, in that order backwards
+    const bool tc_ok = tmw::prefill_backward_tc_supports(*desc);
+    if (desc->algo == TMW_ALGO_TCGEN05 && !tc_ok) return TMW_ERR_UNSUPPORTED;
+    if ((desc->algo == TMW_ALGO_AUTO || desc->algo == TMW_ALGO_TCGEN05) && tc_ok)
+        return tmw::launch_prefill_backward_tc(*desc, q, k, v, o, d_o, lse, dq, dk, dv, static_cast<cudaStream_t>(stream));
+    if (desc->algo == TMW_ALGO_MMA && !tmw::prefill_backward_mma_supports(*desc)) return TMW_ERR_UNSUPPORTED;
     if (desc->algo != TMW_ALGO_SIMT && tmw::prefill_backward_mma_supports(*desc))
         return tmw::launch_prefill_backward_mma(*desc, q, k, v, o, d_o, lse, dq, dk, dv, static_cast<cudaStream_t>(stream));
     return tmw::launch_prefill_backward(*desc, q, k, v, o, d_o, lse, dq, dk, dv, static_cast<cudaStream_t>(stream));

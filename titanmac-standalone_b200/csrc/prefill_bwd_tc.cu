@@ -1,0 +1,589 @@
+// Backward of the windowed attention core on tcgen05: dQ, dK, dV over the visible pairs only, every matrix
+// product on the 5th-generation tensor cores with accumulators AND the 16-bit intermediates (P, dS) in tensor
+// memory, tiles staged by TMA.  Whole sequences (q_pos0 = 0, k_pos0 = n_persistent), 16-bit types, head_dim 64
+// or 128, the plain windowed mask.
+//
+// Same mathematics as the other backward paths of this library (c = scale * log2 e, lse from the forward):
+//   S = Q Kᵀ,  P = exp2(S c - lse) o mask,  dP = dO Vᵀ,  D_i = dO_i · O_i,  dS = P o (dP - D)
+//   dV = Pᵀ dO,  dK = scale · dSᵀ Q,  dQ = scale · dS K
+// and the same split into two launches of ONE kernel template - no atomics, results independent of the schedule:
+//   ROWS_ARE_KEYS  : a CTA owns 128 keys and walks over the 128-query tiles that can see them  -> dK, dV
+//   !ROWS_ARE_KEYS : a CTA owns 128 queries and walks over the 128-key tiles of their windows -> dQ
+// The rows a CTA owns sit on the 128 lanes of tensor memory.  Per (row tile, column tile):
+//   X = R1 C1ᵀ and Y = R2 C2ᵀ                (R1,R2 = K,V or Q,dO of the rows;  C1,C2 = Q,dO or K,V of the columns)
+//   four warps, one thread per row, turn X into P and Y into dS (32 columns at a time) and write both back into
+//   tensor memory as 16-bit values OVER X and Y,
+//   then  acc += Pᵀ-or-dS (from tensor memory) · column tile (from shared memory, read as an MN-major operand).
+// Warps: 0 TMA producer, 1 issues every tcgen05.mma (one elected thread; allocates tensor memory), 2-5 the
+// element-wise work and the output.  Every mbarrier wait is bounded (TMW_ERR_DEVICE_TIMEOUT in the status word).
+#include <cuda.h>
+
+#include <cstdio>
+#include <mutex>
+#include <type_traits>
+
+#include "tc_ptx.cuh"
+#include "tmw_common.cuh"
+
+namespace tmw {
+namespace {
+
+using namespace ptx;
+
+constexpr int BT = 128;          // rows of a tile (the lanes of tensor memory)
+constexpr int kBwdThreads = 192;
+// Columns per tile and depth of the column-tile ring.  head_dim 64: 64 columns, so that X | Y | accumulators fit
+// into 256 tensor-memory columns and TWO CTAs share an SM - the chain of a tile pair (products, hand-over, load
+// from tensor memory, exponentials, hand-over, products) is serial inside a CTA, and a second CTA is what fills
+// its gaps.  head_dim 128: 128 columns, one CTA per SM (the accumulators alone take 256 columns).
+template <int DH>
+struct Geo {
+    static constexpr int kCW = DH == 64 ? 64 : 128;
+    static constexpr int kStages = DH == 64 ? 4 : 2;
+    static constexpr int kCtasPerSm = DH == 64 ? 2 : 1;
+};
+
+struct BwdParams {
+    int rows, window, np;        // L, w, Np
+    int dim_order;               // bit i: tensor i (0=q 1=k 2=v 3=o/dO 4=dq 5=dk 6=dv) has its head axis before its row axis
+    float scale, scale_log2;
+    const void* o;               // for D_i = dO_i . O_i
+    const void* d_o;
+    long long os[3];             // {batch, head, row} strides of o and d_o, elements
+    const float* lse;            // [batch, heads, rows]
+    int* status;
+};
+
+template <int DH>
+struct BwdSmem {
+    static constexpr int CW = Geo<DH>::kCW, S = Geo<DH>::kStages;
+    static constexpr int kTile = BT * DH * 2;                   // a row tile
+    static constexpr int kSub = BT * 128;                       // its 64-column sub-tiles: 128 rows x 128 bytes
+    static constexpr int kCTile = CW * DH * 2;                  // a column tile
+    static constexpr int kCSub = CW * 128;
+    static constexpr int kR1 = 0, kR2 = kTile;                  // row tiles (later: staging of the outputs)
+    static constexpr int kC = 2 * kTile;                        // S x (C1 | C2)
+    static constexpr int kVec = kC + S * 2 * kCTile;            // per column: lse and D, two parities
+    static constexpr int kBars = kVec + 2 * 2 * CW * 4;
+    static constexpr int kTotal = kBars + 256 + 1024;
+};
+
+// barrier slots: R_FULL | C_FULL[4] | C_EMPTY[4] | XY_FULL | PDS_READY | ACC_DONE
+enum { BAR_R_FULL = 0, BAR_C_FULL = 1, BAR_C_EMPTY = 5, BAR_XY_FULL = 9, BAR_PDS_READY = 10, BAR_ACC_DONE = 11, BAR_N = 12 };
+
+// column tiles [first, first + count) that the rows [r0, r1) of a tile interact with, in two segments
+struct ColPlan {
+    int a0, n0;  // first segment (tiles that hold persistent rows / all query tiles)
+    int a1, n1;  // second segment
+};
+
+template <bool ROWS_ARE_KEYS, int CW>
+__device__ __forceinline__ ColPlan col_plan(int r0, int L, int w, int np) {
+    ColPlan c = {0, 0, 0, 0};
+    const int r1 = min(L, r0 + BT);
+    const int n_tiles = (L + CW - 1) / CW;
+    if (ROWS_ARE_KEYS) {
+        if (r0 < np) {  // the tile holds persistent keys: every query sees them
+            c.n0 = n_tiles;
+            return c;
+        }
+        c.a1 = r0 / CW;
+        c.n1 = min(L - 1, r1 - 1 + w) / CW - c.a1 + 1;
+        return c;
+    }
+    const int np_tiles = (np + CW - 1) / CW;
+    c.n0 = np_tiles;  // persistent keys
+    if (r1 > np) {
+        const int lo = max(np, max(r0, np) - w);
+        c.a1 = max(lo / CW, np_tiles);
+        c.n1 = max(0, (r1 - 1) / CW - c.a1 + 1);
+    }
+    return c;
+}
+
+// (bitwise on purpose: short-circuit operators would put branches between the elements of a row, and the compiler
+// then cannot interleave their arithmetic)
+__device__ __forceinline__ bool visible(int pq, int pk, int L, int w, int np) {
+    const bool inside = (pq < L) & (pk < L);
+    const bool pers_key = pk < np;
+    const bool in_window = (pq >= np) & (pk <= pq) & (pq - pk <= w);
+    return inside & (pers_key | in_window);
+}
+
+template <int DH, bool BF16, bool ROWS_ARE_KEYS>
+__global__ void __launch_bounds__(kBwdThreads, Geo<DH>::kCtasPerSm)
+bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant__ CUtensorMap map_r2,
+              const __grid_constant__ CUtensorMap map_c1, const __grid_constant__ CUtensorMap map_c2,
+              const __grid_constant__ CUtensorMap map_out1, const __grid_constant__ CUtensorMap map_out2,
+              const BwdParams p) {
+    using L = BwdSmem<DH>;
+    constexpr int NSUB = DH / 64;
+    constexpr int CW = Geo<DH>::kCW, kColStages = Geo<DH>::kStages;
+    constexpr uint32_t kX = 0, kY = CW, kAcc1 = 2 * CW, kAcc2 = 2 * CW + DH;
+    constexpr uint32_t kNeed = 2 * CW + (ROWS_ARE_KEYS ? 2 : 1) * DH;
+    constexpr uint32_t kTmemCols = kNeed <= 256 ? 256 : 512;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    uint8_t* bar_area = smem + L::kBars;
+    const uint32_t bar_base = smem_base + L::kBars;
+    auto bar = [&](int slot) -> uint32_t { return bar_base + slot * 8; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_area + BAR_N * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_area + BAR_N * 8 + 8);
+    float* vec = reinterpret_cast<float*>(smem + L::kVec);  // [parity][lse | D][column]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y, batch = blockIdx.z;
+    const int r0 = blockIdx.x * BT;
+    const ColPlan plan = col_plan<ROWS_ARE_KEYS, CW>(r0, p.rows, p.window, p.np);
+    const int n_cols = plan.n0 + plan.n1;
+    auto col_tile = [&](int n) -> int { return n < plan.n0 ? plan.a0 + n : plan.a1 + (n - plan.n0); };
+    // coordinate order of a tensor map: (dh, rows, heads, batch) or (dh, heads, rows, batch)
+    auto coords = [&](int which, int row, int& c1, int& c2) {
+        if ((p.dim_order >> which) & 1) { c1 = head; c2 = row; } else { c1 = row; c2 = head; }
+    };
+    // which tensors play which role
+    constexpr int kR1 = ROWS_ARE_KEYS ? 1 : 0, kR2 = ROWS_ARE_KEYS ? 2 : 3;   // K,V | Q,dO
+    constexpr int kC1 = ROWS_ARE_KEYS ? 0 : 1, kC2 = ROWS_ARE_KEYS ? 3 : 2;   // Q,dO | K,V
+    constexpr int kO1 = ROWS_ARE_KEYS ? 6 : 4, kO2 = 5;                       // dV,dK | dQ
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_r1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_r2) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c2) : "memory");
+        mbar_init(bar(BAR_R_FULL), 1);
+        for (int s = 0; s < kColStages; ++s) {
+            mbar_init(bar(BAR_C_FULL + s), 1);
+            mbar_init(bar(BAR_C_EMPTY + s), 1);
+        }
+        mbar_init(bar(BAR_XY_FULL), 1);
+        mbar_init(bar(BAR_PDS_READY), 4);
+        mbar_init(bar(BAR_ACC_DONE), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32((const void*)tmem_slot), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            mbar_expect_tx(bar(BAR_R_FULL), 2 * L::kTile);
+            int c1, c2;
+            coords(kR1, r0, c1, c2);
+            for (int u = 0; u < NSUB; ++u)
+                tma_load_4d(smem_base + L::kR1 + u * L::kSub, &map_r1, bar(BAR_R_FULL), u * 64, c1, c2, batch);
+            coords(kR2, r0, c1, c2);
+            for (int u = 0; u < NSUB; ++u)
+                tma_load_4d(smem_base + L::kR2 + u * L::kSub, &map_r2, bar(BAR_R_FULL), u * 64, c1, c2, batch);
+        }
+        for (int n = 0; n < n_cols; ++n) {
+            const int s = n % kColStages;
+            mbar_wait(bar(BAR_C_EMPTY + s), ((n / kColStages) & 1) ^ 1, abort_flag, p.status);
+            if (lane == 0) {
+                mbar_expect_tx(bar(BAR_C_FULL + s), 2 * L::kCTile);
+                const uint32_t dst = smem_base + L::kC + s * 2 * L::kCTile;
+                const int row = col_tile(n) * CW;
+                int c1, c2;
+                coords(kC1, row, c1, c2);
+                for (int u = 0; u < NSUB; ++u)
+                    tma_load_4d(dst + u * L::kCSub, &map_c1, bar(BAR_C_FULL + s), u * 64, c1, c2, batch);
+                coords(kC2, row, c1, c2);
+                for (int u = 0; u < NSUB; ++u)
+                    tma_load_4d(dst + L::kCTile + u * L::kCSub, &map_c2, bar(BAR_C_FULL + s), u * 64, c1, c2, batch);
+            }
+            __syncwarp();
+        }
+    } else if (warp == 1) {
+        // ---------------- tensor-core issue ----------------
+        // (the whole warp runs the loop and computes the operands; one lane issues - a lone lane inside a
+        // divergent branch issues these instructions markedly slower)
+        const bool leader = lane == 0;
+        const uint32_t fmt = BF16 ? 1u : 0u;
+        const uint32_t idesc_xy = idesc_kmajor(fmt, CW);
+        const uint32_t idesc_acc = idesc_b_mnmajor(fmt, DH);
+        mbar_wait(bar(BAR_R_FULL), 0, abort_flag, p.status);
+        for (int n = 0; n < n_cols; ++n) {
+            const int s = n % kColStages;
+            const uint32_t c_addr = smem_base + L::kC + s * 2 * L::kCTile;
+            mbar_wait(bar(BAR_C_FULL + s), (n / kColStages) & 1, abort_flag, p.status);
+            tc_fence_after();
+            // X = R1 C1^T, Y = R2 C2^T (both operands K-major over head_dim).  They overwrite the P and dS of
+            // the previous column tile, which the products issued before them have consumed in issue order.
+#pragma unroll
+            for (int kk = 0; kk < DH / 16; ++kk) {
+                const uint64_t ad = kmajor_desc(smem_base + L::kR1 + (kk / 4) * L::kSub + (kk % 4) * 32);
+                const uint64_t bd = kmajor_desc(c_addr + (kk / 4) * L::kCSub + (kk % 4) * 32);
+                if (leader) mma_ss(tmem_base + kX, ad, bd, idesc_xy, kk > 0 ? 1u : 0u);
+            }
+#pragma unroll
+            for (int kk = 0; kk < DH / 16; ++kk) {
+                const uint64_t ad = kmajor_desc(smem_base + L::kR2 + (kk / 4) * L::kSub + (kk % 4) * 32);
+                const uint64_t bd = kmajor_desc(c_addr + L::kCTile + (kk / 4) * L::kCSub + (kk % 4) * 32);
+                if (leader) mma_ss(tmem_base + kY, ad, bd, idesc_xy, kk > 0 ? 1u : 0u);
+            }
+            if (leader) tc_commit(bar(BAR_XY_FULL));
+            __syncwarp();
+            mbar_wait(bar(BAR_PDS_READY), n & 1, abort_flag, p.status);
+            tc_fence_after();
+            const uint32_t acc = n > 0 ? 1u : 0u;
+            if (ROWS_ARE_KEYS) {
+                // dV += P^T dO : A = P (over X), B = the dO tile read MN-major
+#pragma unroll
+                for (int kk = 0; kk < CW / 16; ++kk) {
+                    const uint64_t bd = mnmajor_desc(c_addr + L::kCTile, L::kCSub) + kk * 128;
+                    if (leader) mma_ts(tmem_base + kAcc1, tmem_base + kX + kk * 8, bd, idesc_acc, kk > 0 ? 1u : acc);
+                }
+                // dK += dS^T Q : A = dS (over Y), B = the Q tile read MN-major
+#pragma unroll
+                for (int kk = 0; kk < CW / 16; ++kk) {
+                    const uint64_t bd = mnmajor_desc(c_addr, L::kCSub) + kk * 128;
+                    if (leader) mma_ts(tmem_base + kAcc2, tmem_base + kY + kk * 8, bd, idesc_acc, kk > 0 ? 1u : acc);
+                }
+            } else {
+                // dQ += dS K : A = dS (over Y), B = the K tile read MN-major
+#pragma unroll
+                for (int kk = 0; kk < CW / 16; ++kk) {
+                    const uint64_t bd = mnmajor_desc(c_addr, L::kCSub) + kk * 128;
+                    if (leader) mma_ts(tmem_base + kAcc1, tmem_base + kY + kk * 8, bd, idesc_acc, kk > 0 ? 1u : acc);
+                }
+            }
+            if (leader) {
+                tc_commit(bar(BAR_C_EMPTY + s));
+                if (n == n_cols - 1) tc_commit(bar(BAR_ACC_DONE));
+            }
+            __syncwarp();
+        }
+    } else {
+        // ---------------- element-wise warps: one thread per row of the tile ----------------
+        const int g = warp & 3;                    // lane group of tensor memory this warp may touch
+        const int row = g * 32 + lane;
+        const int tid128 = (warp - 2) * 32 + lane;  // 0 .. 127 among the four warps
+        const int pos_row = r0 + row;              // position of this thread's key (ROWS_ARE_KEYS) or query
+        const uint32_t t_row = tmem_base + ((uint32_t)(g * 32) << 16);
+        const long long bh = (long long)batch * gridDim.y + head;
+        const float* lse_bh = p.lse + bh * p.rows;
+
+        // D = dO . O of query row `qrow` (fp32), straight from global memory (two rows of head_dim 16-bit values)
+        auto delta_of = [&](int qrow) -> float {
+            if (qrow >= p.rows) return 0.f;
+            const long long off = (long long)batch * p.os[0] + (long long)head * p.os[1] + (long long)qrow * p.os[2];
+            float acc = 0.f;
+#pragma unroll
+            for (int c = 0; c < DH; c += 8) {
+                float a[8], b[8];
+                if (BF16) {
+                    load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.o) + off + c, a);
+                    load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.d_o) + off + c, b);
+                } else {
+                    load8<__half>(static_cast<const __half*>(p.o) + off + c, a);
+                    load8<__half>(static_cast<const __half*>(p.d_o) + off + c, b);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc = fmaf(a[e], b[e], acc);
+            }
+            return acc;
+        };
+        // rows are queries: this thread's own statistics, once
+        float lse_own = 0.f, d_own = 0.f;
+        if (!ROWS_ARE_KEYS) {
+            lse_own = pos_row < p.rows ? lse_bh[pos_row] : 0.f;
+            d_own = delta_of(pos_row);
+        }
+
+        for (int n = 0; n < n_cols; ++n) {
+            const int c0 = col_tile(n) * CW;  // position of column 0
+            float* v_lse = vec + (n & 1) * 2 * CW;
+            float* v_d = v_lse + CW;
+            if (ROWS_ARE_KEYS) {
+                // columns are queries: the first CW threads fetch the statistics of query c0 + i for everybody
+                if (tid128 < CW) {
+                    const int qrow = c0 + tid128;
+                    v_lse[tid128] = qrow < p.rows ? lse_bh[qrow] : 0.f;
+                    v_d[tid128] = delta_of(qrow);
+                }
+                named_barrier_sync(1, BT);
+            }
+            // every pair of the tile visible?  (then no per-element test)
+            const int rlo = r0, rhi = min(p.rows, r0 + BT) - 1, clo = c0, chi = min(p.rows, c0 + CW) - 1;
+            bool full;
+            if (ROWS_ARE_KEYS)  // rows = keys [rlo, rhi], columns = queries [clo, chi]
+                full = r0 + BT <= p.rows && c0 + CW <= p.rows &&
+                       (rhi < p.np || (rlo >= p.np && clo >= p.np && rhi <= clo && chi - rlo <= p.window));
+            else               // rows = queries, columns = keys
+                full = r0 + BT <= p.rows && c0 + CW <= p.rows &&
+                       (chi < p.np || (clo >= p.np && rlo >= p.np && chi <= rlo && rhi - clo <= p.window));
+
+            mbar_wait(bar(BAR_XY_FULL), n & 1, abort_flag, p.status);
+            tc_fence_after();
+            // 64 columns at a time: all loads of the step in flight together.  The body exists twice, with and
+            // without the per-element mask, as straight-line code (a run-time test inside it would split it into
+            // one basic block per element and serialise the elements' dependency chains).
+            auto process = [&](auto masked_tag) {
+                constexpr bool MASKED = decltype(masked_tag)::value;
+#pragma unroll 1
+                for (int c = 0; c < CW / 64; ++c) {
+                    uint32_t x[2][32], y[2][32];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        tmem_ld32(t_row + kX + c * 64 + u * 32, x[u]);
+                        tmem_ld32(t_row + kY + c * 64 + u * 32, y[u]);
+                    }
+                    tc_wait_ld();
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        uint32_t pp[16], ds[16];
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            float pv[2], dv[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int col = c * 64 + u * 32 + j + e;
+                                const float l = ROWS_ARE_KEYS ? v_lse[col] : lse_own;
+                                const float dd = ROWS_ARE_KEYS ? v_d[col] : d_own;
+                                const float pr = fast_exp2(fmaf(__uint_as_float(x[u][j + e]), p.scale_log2, -l));
+                                const float dsv = pr * (__uint_as_float(y[u][j + e]) - dd);
+                                if (MASKED) {
+                                    const bool vis = ROWS_ARE_KEYS ? visible(c0 + col, pos_row, p.rows, p.window, p.np)
+                                                                   : visible(pos_row, c0 + col, p.rows, p.window, p.np);
+                                    pv[e] = vis ? pr : 0.f;
+                                    dv[e] = vis ? dsv : 0.f;
+                                } else {
+                                    pv[e] = pr;
+                                    dv[e] = dsv;
+                                }
+                            }
+                            if (BF16) {
+                                const __nv_bfloat162 a2 = __floats2bfloat162_rn(pv[0], pv[1]);
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(dv[0], dv[1]);
+                                pp[j / 2] = *reinterpret_cast<const uint32_t*>(&a2);
+                                ds[j / 2] = *reinterpret_cast<const uint32_t*>(&b2);
+                            } else {
+                                const __half2 a2 = __floats2half2_rn(pv[0], pv[1]);
+                                const __half2 b2 = __floats2half2_rn(dv[0], dv[1]);
+                                pp[j / 2] = *reinterpret_cast<const uint32_t*>(&a2);
+                                ds[j / 2] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
+                        }
+                        // 16-bit results over the fp32 inputs: the packed columns lie inside columns already read
+                        if (ROWS_ARE_KEYS) tmem_st16(t_row + kX + c * 32 + u * 16, pp);
+                        tmem_st16(t_row + kY + c * 32 + u * 16, ds);
+                    }
+                }
+            };
+            if (full) process(std::false_type{}); else process(std::true_type{});
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(BAR_PDS_READY));
+        }
+
+        // ---------------- output: accumulators -> 16 bits -> shared memory (swizzled) -> TMA store ----------------
+        mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag, p.status);
+        tc_fence_after();
+        constexpr int kOutputs = ROWS_ARE_KEYS ? 2 : 1;
+#pragma unroll
+        for (int which = 0; which < kOutputs; ++which) {
+            // dV is taken as it is; dK and dQ carry the softmax scale
+            const float mul = (ROWS_ARE_KEYS && which == 0) ? 1.0f : p.scale;
+            uint8_t* stage = smem + (which == 0 ? L::kR1 : L::kR2);  // the row tiles are no longer needed
+#pragma unroll
+            for (int c = 0; c < DH / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(t_row + (which == 0 ? kAcc1 : kAcc2) + c * 32, o);
+                tc_wait_ld();
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float a = __uint_as_float(o[g8 * 8 + 2 * e]) * mul;
+                        const float b = __uint_as_float(o[g8 * 8 + 2 * e + 1]) * mul;
+                        if (BF16) {
+                            const __nv_bfloat162 hh = __floats2bfloat162_rn(a, b);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                        } else {
+                            const __half2 hh = __floats2half2_rn(a, b);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                        }
+                    }
+                    const int col = c * 32 + g8 * 8;
+                    uint8_t* dst = stage + (col / 64) * L::kSub + row * 128 + ((((col % 64) / 8) ^ (row & 7)) * 16);
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(2, BT);
+        if (tid128 == 0) {
+            int c1, c2;
+            coords(kO1, r0, c1, c2);
+            for (int u = 0; u < NSUB; ++u)
+                tma_store_4d(&map_out1, smem_u32(smem + L::kR1 + u * L::kSub), u * 64, c1, c2, batch);
+            if (ROWS_ARE_KEYS) {
+                coords(kO2, r0, c1, c2);
+                for (int u = 0; u < NSUB; ++u)
+                    tma_store_4d(&map_out2, smem_u32(smem + L::kR2 + u * L::kSub), u * 64, c1, c2, batch);
+            }
+            tma_store_commit();
+            tma_store_wait_all();
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        if (*abort_flag) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < 400000) __nanosleep(1000);
+        }
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+struct Strides4 {
+    int64_t row, head, batch;
+    bool heads_first;
+    bool ok;  // positive multiples of 16 bytes below 2^40 bytes: what a tensor map accepts
+};
+Strides4 strides_of(int batch, int heads, int rows, int dh, const int64_t stride[3]) {
+    Strides4 m;
+    m.row = rows > 1 ? stride[2] : dh;
+    m.head = heads > 1 ? stride[1] : m.row * rows;
+    const int64_t inner_span = m.head * heads > m.row * rows ? m.head * heads : m.row * rows;
+    m.batch = batch > 1 ? stride[0] : inner_span;
+    m.heads_first = m.head < m.row;
+    const int64_t limit = ((int64_t)1 << 40) / 2;
+    m.ok = m.row > 0 && m.head > 0 && m.batch > 0 && m.row < limit && m.head < limit && m.batch < limit &&
+           m.row % 8 == 0 && m.head % 8 == 0 && m.batch % 8 == 0;
+    return m;
+}
+
+// map over a [batch, heads, rows, dh] tensor: boxes of box_rows rows x 64 columns of one (batch, head), 128-byte swizzle
+bool make_map4(CUtensorMap* map, const void* base, int dtype, int batch, int heads, int rows, int dh, const Strides4& m,
+               int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[4], strides[3];
+    cuuint32_t box[4];
+    dims[0] = (cuuint64_t)dh;
+    box[0] = 64;
+    if (m.heads_first) {
+        dims[1] = (cuuint64_t)heads; strides[0] = (cuuint64_t)m.head * 2; box[1] = 1;
+        dims[2] = (cuuint64_t)rows;  strides[1] = (cuuint64_t)m.row * 2;  box[2] = (cuuint32_t)box_rows;
+    } else {
+        dims[1] = (cuuint64_t)rows;  strides[0] = (cuuint64_t)m.row * 2;  box[1] = (cuuint32_t)box_rows;
+        dims[2] = (cuuint64_t)heads; strides[1] = (cuuint64_t)m.head * 2; box[2] = 1;
+    }
+    dims[3] = (cuuint64_t)batch;
+    strides[2] = (cuuint64_t)m.batch * 2;
+    box[3] = 1;
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType dt = dtype == TMW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, elem_strides,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char text[96];
+        snprintf(text, sizeof(text), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        set_error_text(text);
+        return false;
+    }
+    return true;
+}
+
+template <int DH>
+int launch_bwd_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                  const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream) {
+    using L = BwdSmem<DH>;
+    const int B = d.batch, H = d.heads, R = d.q_rows;
+    const Strides4 sq = strides_of(B, H, R, DH, d.q_stride), sk = strides_of(B, H, R, DH, d.k_stride);
+    const Strides4 sv = strides_of(B, H, R, DH, d.v_stride), so = strides_of(B, H, R, DH, d.o_stride);
+    constexpr int CW = Geo<DH>::kCW;
+    // row-tile maps (boxes of 128 rows; also the outputs) and column-tile maps (boxes of CW rows)
+    CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv, cq, ck, cv, cdo;
+    if (!make_map4(&mq, q, d.dtype, B, H, R, DH, sq, BT) || !make_map4(&mk, k, d.dtype, B, H, R, DH, sk, BT) ||
+        !make_map4(&mv, v, d.dtype, B, H, R, DH, sv, BT) || !make_map4(&mdo, d_o, d.dtype, B, H, R, DH, so, BT) ||
+        !make_map4(&mdq, dq, d.dtype, B, H, R, DH, sq, BT) || !make_map4(&mdk, dk, d.dtype, B, H, R, DH, sk, BT) ||
+        !make_map4(&mdv, dv, d.dtype, B, H, R, DH, sv, BT) || !make_map4(&cq, q, d.dtype, B, H, R, DH, sq, CW) ||
+        !make_map4(&ck, k, d.dtype, B, H, R, DH, sk, CW) || !make_map4(&cv, v, d.dtype, B, H, R, DH, sv, CW) ||
+        !make_map4(&cdo, d_o, d.dtype, B, H, R, DH, so, CW))
+        return TMW_ERR_CUDA;
+    BwdParams p;
+    p.rows = R; p.window = d.window; p.np = d.n_persistent;
+    p.dim_order = (sq.heads_first ? 1 : 0) | (sk.heads_first ? 2 : 0) | (sv.heads_first ? 4 : 0) | (so.heads_first ? 8 : 0) |
+                  (sq.heads_first ? 16 : 0) | (sk.heads_first ? 32 : 0) | (sv.heads_first ? 64 : 0);
+    p.scale = d.scale != 0.f ? d.scale : 1.0f / sqrtf((float)DH);
+    p.scale_log2 = p.scale * 1.4426950408889634f;
+    p.o = o; p.d_o = d_o;
+    for (int i = 0; i < 3; ++i) p.os[i] = d.o_stride[i];
+    p.lse = lse;
+    p.status = device_status_word();
+    if (p.status == nullptr) return TMW_ERR_CUDA;
+    const dim3 grid((R + BT - 1) / BT, H, B);
+    auto run = [&](auto kern, const CUtensorMap& r1, const CUtensorMap& r2, const CUtensorMap& c1, const CUtensorMap& c2,
+                   const CUtensorMap& o1, const CUtensorMap& o2) -> int {
+        const int rc = allow_shared_memory(reinterpret_cast<const void*>(kern), L::kTotal);
+        if (rc != TMW_OK) return rc;
+        kern<<<grid, kBwdThreads, L::kTotal, stream>>>(r1, r2, c1, c2, o1, o2, p);
+        return TMW_OK;
+    };
+    int st;
+    // dK, dV: rows are keys (K, V), columns are queries (Q, dO)
+    st = d.dtype == TMW_BF16 ? run(bwd_tc_kernel<DH, true, true>, mk, mv, cq, cdo, mdv, mdk)
+                             : run(bwd_tc_kernel<DH, false, true>, mk, mv, cq, cdo, mdv, mdk);
+    if (st != TMW_OK) return st;
+    // dQ: rows are queries (Q, dO), columns are keys (K, V)
+    st = d.dtype == TMW_BF16 ? run(bwd_tc_kernel<DH, true, false>, mq, mdo, ck, cv, mdq, mdq)
+                             : run(bwd_tc_kernel<DH, false, false>, mq, mdo, ck, cv, mdq, mdq);
+    if (st != TMW_OK) return st;
+    TMW_CUDA_TRY(cudaGetLastError());
+    return TMW_OK;
+}
+
+}  // namespace
+
+// the plain windowed mask over whole sequences, 16-bit types, head_dim 64 or 128, layouts a tensor map can describe
+bool prefill_backward_tc_supports(const tmw_prefill_desc& d) {
+    if (d.dtype != TMW_BF16 && d.dtype != TMW_F16) return false;
+    if (d.head_dim != 64 && d.head_dim != 128) return false;
+    if (d.batch > 65535 || d.heads > 65535) return false;
+    if ((int64_t)d.q_rows + d.window + 2 * BT >= (int64_t)1 << 30) return false;
+    return strides_of(d.batch, d.heads, d.q_rows, d.head_dim, d.q_stride).ok &&
+           strides_of(d.batch, d.heads, d.q_rows, d.head_dim, d.k_stride).ok &&
+           strides_of(d.batch, d.heads, d.q_rows, d.head_dim, d.v_stride).ok &&
+           strides_of(d.batch, d.heads, d.q_rows, d.head_dim, d.o_stride).ok;
+}
+
+int launch_prefill_backward_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
+                               const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream) {
+    return d.head_dim == 64 ? launch_bwd_tc<64>(d, q, k, v, o, d_o, lse, dq, dk, dv, stream)
+                            : launch_bwd_tc<128>(d, q, k, v, o, d_o, lse, dq, dk, dv, stream);
+}
+
+}  // namespace tmw

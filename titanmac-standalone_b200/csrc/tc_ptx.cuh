@@ -114,6 +114,54 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+                 "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Descriptor of a 128-byte-swizzled tile of rows x 64 columns read as an MN-major B operand (the 64 columns are
+// the N direction, the rows the K direction): 16 rows (one K step) are two 8-row groups 1024 bytes apart; wider
+// N continues in the next 64-column sub-tile, `next_subtile` bytes further on.  A K step adds 2048 bytes (128
+// units of 16 bytes).
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t smem_addr, uint32_t next_subtile) {
+    constexpr uint32_t kHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    const uint32_t lo = ((smem_addr >> 4) & 0x3fffu) | ((next_subtile >> 4) << 16);
+    return ((uint64_t)kHi << 32) | lo;
+}
+// kind::f16 instruction descriptor with an MN-major B operand (M = 128)
+__device__ __forceinline__ uint32_t idesc_b_mnmajor(uint32_t fmt, uint32_t n) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
 // ---- CTA pairs (cta_group::2): two CTAs of a cluster share one matrix product ------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

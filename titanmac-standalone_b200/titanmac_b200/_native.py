@@ -28,7 +28,7 @@ TMW_ERR_DEVICE_TIMEOUT = -7
 TMW_ERR_TOO_LARGE = -8
 
 TMW_F32, TMW_BF16, TMW_F16 = 0, 1, 2
-ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05 = 0, 1, 2
+ALGO_AUTO, ALGO_SIMT, ALGO_TCGEN05, ALGO_MMA = 0, 1, 2, 3
 
 _DTYPES = {torch.float32: TMW_F32, torch.bfloat16: TMW_BF16, torch.float16: TMW_F16}
 
