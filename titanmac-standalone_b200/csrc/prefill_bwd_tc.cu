@@ -63,13 +63,36 @@ struct BwdSmem {
     static constexpr int kCSub = CW * 128;
     static constexpr int kR1 = 0, kR2 = kTile;                  // row tiles (later: staging of the outputs)
     static constexpr int kC = 2 * kTile;                        // S x (C1 | C2)
-    static constexpr int kVec = kC + S * 2 * kCTile;            // per column: lse and D, two parities
-    static constexpr int kBars = kVec + 2 * 2 * CW * 4;
+    static constexpr int kVec = kC + S * 2 * kCTile;            // per stage and column: lse and D (fp32)
+    static constexpr int kBars = kVec + S * 2 * CW * 4;
     static constexpr int kTotal = kBars + 256 + 1024;
 };
 
-// barrier slots: R_FULL | C_FULL[4] | C_EMPTY[4] | XY_FULL | PDS_READY | ACC_DONE
-enum { BAR_R_FULL = 0, BAR_C_FULL = 1, BAR_C_EMPTY = 5, BAR_XY_FULL = 9, BAR_PDS_READY = 10, BAR_ACC_DONE = 11, BAR_N = 12 };
+// barrier slots: R_FULL | C_FULL[4] | C_EMPTY[4] | XY_FULL | PDS_READY | ACC_DONE | V_FULL[4]
+enum { BAR_R_FULL = 0, BAR_C_FULL = 1, BAR_C_EMPTY = 5, BAR_XY_FULL = 9, BAR_PDS_READY = 10, BAR_ACC_DONE = 11, BAR_V_FULL = 12,
+       BAR_N = 16 };
+
+// D = dO . O of one query row (fp32), straight from global memory (two rows of head_dim 16-bit values)
+template <int DH, bool BF16>
+__device__ __forceinline__ float delta_of(const BwdParams& p, int batch, int head, int qrow) {
+    if (qrow >= p.rows) return 0.f;
+    const long long off = (long long)batch * p.os[0] + (long long)head * p.os[1] + (long long)qrow * p.os[2];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < DH; c += 8) {
+        float a[8], b[8];
+        if (BF16) {
+            load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.o) + off + c, a);
+            load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.d_o) + off + c, b);
+        } else {
+            load8<__half>(static_cast<const __half*>(p.o) + off + c, a);
+            load8<__half>(static_cast<const __half*>(p.d_o) + off + c, b);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e & 3] = fmaf(a[e], b[e], acc[e & 3]);
+    }
+    return (acc[0] + acc[1]) + (acc[2] + acc[3]);
+}
 
 // column tiles [first, first + count) that the rows [r0, r1) of a tile interact with, in two segments
 struct ColPlan {
@@ -130,7 +153,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
     auto bar = [&](int slot) -> uint32_t { return bar_base + slot * 8; };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_area + BAR_N * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_area + BAR_N * 8 + 8);
-    float* vec = reinterpret_cast<float*>(smem + L::kVec);  // [parity][lse | D][column]
+    float* vec = reinterpret_cast<float*>(smem + L::kVec);  // [stage][lse | D][column]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y, batch = blockIdx.z;
@@ -157,6 +180,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
             mbar_init(bar(BAR_C_FULL + s), 1);
             mbar_init(bar(BAR_C_EMPTY + s), 1);
         }
+        for (int s = 0; s < kColStages; ++s) mbar_init(bar(BAR_V_FULL + s), 1);
         mbar_init(bar(BAR_XY_FULL), 1);
         mbar_init(bar(BAR_PDS_READY), 4);
         mbar_init(bar(BAR_ACC_DONE), 1);
@@ -195,6 +219,19 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
                 coords(kC2, row, c1, c2);
                 for (int u = 0; u < NSUB; ++u)
                     tma_load_4d(dst + L::kCTile + u * L::kCSub, &map_c2, bar(BAR_C_FULL + s), u * 64, c1, c2, batch);
+            }
+            if (ROWS_ARE_KEYS) {
+                // columns are queries: their log-sum-exp and D = dO . O, a few tiles ahead of the warps that use
+                // them (the loads would otherwise sit on those warps' critical path once per column tile)
+                float* v_lse = vec + s * 2 * CW;
+                const long long bh = (long long)batch * gridDim.y + head;
+                for (int i = lane; i < CW; i += 32) {
+                    const int qrow = col_tile(n) * CW + i;
+                    v_lse[i] = qrow < p.rows ? p.lse[bh * p.rows + qrow] : 0.f;
+                    v_lse[CW + i] = delta_of<DH, BF16>(p, batch, head, qrow);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(BAR_V_FULL + s));
             }
             __syncwarp();
         }
@@ -268,46 +305,18 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
         const long long bh = (long long)batch * gridDim.y + head;
         const float* lse_bh = p.lse + bh * p.rows;
 
-        // D = dO . O of query row `qrow` (fp32), straight from global memory (two rows of head_dim 16-bit values)
-        auto delta_of = [&](int qrow) -> float {
-            if (qrow >= p.rows) return 0.f;
-            const long long off = (long long)batch * p.os[0] + (long long)head * p.os[1] + (long long)qrow * p.os[2];
-            float acc = 0.f;
-#pragma unroll
-            for (int c = 0; c < DH; c += 8) {
-                float a[8], b[8];
-                if (BF16) {
-                    load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.o) + off + c, a);
-                    load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.d_o) + off + c, b);
-                } else {
-                    load8<__half>(static_cast<const __half*>(p.o) + off + c, a);
-                    load8<__half>(static_cast<const __half*>(p.d_o) + off + c, b);
-                }
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc = fmaf(a[e], b[e], acc);
-            }
-            return acc;
-        };
         // rows are queries: this thread's own statistics, once
         float lse_own = 0.f, d_own = 0.f;
         if (!ROWS_ARE_KEYS) {
             lse_own = pos_row < p.rows ? lse_bh[pos_row] : 0.f;
-            d_own = delta_of(pos_row);
+            d_own = delta_of<DH, BF16>(p, batch, head, pos_row);
         }
 
         for (int n = 0; n < n_cols; ++n) {
             const int c0 = col_tile(n) * CW;  // position of column 0
-            float* v_lse = vec + (n & 1) * 2 * CW;
-            float* v_d = v_lse + CW;
-            if (ROWS_ARE_KEYS) {
-                // columns are queries: the first CW threads fetch the statistics of query c0 + i for everybody
-                if (tid128 < CW) {
-                    const int qrow = c0 + tid128;
-                    v_lse[tid128] = qrow < p.rows ? lse_bh[qrow] : 0.f;
-                    v_d[tid128] = delta_of(qrow);
-                }
-                named_barrier_sync(1, BT);
-            }
+            const float* v_lse = vec + (n % kColStages) * 2 * CW;  // written by the producer warp for this stage
+            const float* v_d = v_lse + CW;
+            if (ROWS_ARE_KEYS) mbar_wait(bar(BAR_V_FULL + n % kColStages), (n / kColStages) & 1, abort_flag, p.status);
             // every pair of the tile visible?  (then no per-element test)
             const int rlo = r0, rhi = min(p.rows, r0 + BT) - 1, clo = c0, chi = min(p.rows, c0 + CW) - 1;
             bool full;
