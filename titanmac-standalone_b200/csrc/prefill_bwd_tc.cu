@@ -51,6 +51,13 @@ struct BwdParams {
     const void* d_o;
     long long os[3];             // {batch, head, row} strides of o and d_o, elements
     const float* lse;            // [batch, heads, rows]
+    // Scratch memory [batch * heads][2][rows_pad] (fp32; rows_pad a multiple of 128), or nullptr.  The launch whose
+    // rows are queries computes every row's D anyway and leaves (lse, D) here; the launch whose rows are keys,
+    // run after it, then fetches its column statistics with one 16-byte load per lane instead of reading two
+    // rows of O and dO per column.
+    float* stats;
+    int rows_pad;
+    int n_bx, heads, batch;      // row tiles per (batch, head); grid = n_bx * heads * batch
     int* status;
 };
 
@@ -156,8 +163,24 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
     float* vec = reinterpret_cast<float*>(smem + L::kVec);  // [stage][lse | D][column]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y, batch = blockIdx.z;
-    const int r0 = blockIdx.x * BT;
+    // One-dimensional grid.  The row tile that holds the persistent keys walks over EVERY query tile (all queries
+    // see those keys), several times the work of any other tile: those CTAs get the first block indices, so they
+    // start first and the short ones fill in around them instead of the long ones forming the tail of the launch.
+    int tile_x, head, batch;
+    {
+        const int n_bh = p.heads * p.batch;
+        int id = (int)blockIdx.x, bh;
+        if (ROWS_ARE_KEYS && p.np > 0 && p.n_bx > 1) {
+            if (id < n_bh) { tile_x = 0; bh = id; }
+            else { id -= n_bh; tile_x = 1 + id % (p.n_bx - 1); bh = id / (p.n_bx - 1); }
+        } else {
+            tile_x = id % p.n_bx;
+            bh = id / p.n_bx;
+        }
+        head = bh % p.heads;
+        batch = bh / p.heads;
+    }
+    const int r0 = tile_x * BT;
     const ColPlan plan = col_plan<ROWS_ARE_KEYS, CW>(r0, p.rows, p.window, p.np);
     const int n_cols = plan.n0 + plan.n1;
     auto col_tile = [&](int n) -> int { return n < plan.n0 ? plan.a0 + n : plan.a1 + (n - plan.n0); };
@@ -224,11 +247,21 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
                 // columns are queries: their log-sum-exp and D = dO . O, a few tiles ahead of the warps that use
                 // them (the loads would otherwise sit on those warps' critical path once per column tile)
                 float* v_lse = vec + s * 2 * CW;
-                const long long bh = (long long)batch * gridDim.y + head;
-                for (int i = lane; i < CW; i += 32) {
-                    const int qrow = col_tile(n) * CW + i;
-                    v_lse[i] = qrow < p.rows ? p.lse[bh * p.rows + qrow] : 0.f;
-                    v_lse[CW + i] = delta_of<DH, BF16>(p, batch, head, qrow);
+                const long long bh = (long long)batch * p.heads + head;
+                if (p.stats != nullptr) {
+                    // [lse | D] of the tile's CW columns: 2 * CW / 4 loads of 16 bytes
+                    const float* src = p.stats + bh * 2 * p.rows_pad + col_tile(n) * CW;
+                    for (int i = lane; i < 2 * CW / 4; i += 32) {
+                        const int half = i / (CW / 4), c4 = i % (CW / 4);
+                        *reinterpret_cast<float4*>(v_lse + half * CW + c4 * 4) =
+                            *reinterpret_cast<const float4*>(src + (long long)half * p.rows_pad + c4 * 4);
+                    }
+                } else {
+                    for (int i = lane; i < CW; i += 32) {
+                        const int qrow = col_tile(n) * CW + i;
+                        v_lse[i] = qrow < p.rows ? p.lse[bh * p.rows + qrow] : 0.f;
+                        v_lse[CW + i] = delta_of<DH, BF16>(p, batch, head, qrow);
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(BAR_V_FULL + s));
@@ -302,7 +335,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
         const int tid128 = (warp - 2) * 32 + lane;  // 0 .. 127 among the four warps
         const int pos_row = r0 + row;              // position of this thread's key (ROWS_ARE_KEYS) or query
         const uint32_t t_row = tmem_base + ((uint32_t)(g * 32) << 16);
-        const long long bh = (long long)batch * gridDim.y + head;
+        const long long bh = (long long)batch * p.heads + head;
         const float* lse_bh = p.lse + bh * p.rows;
 
         // rows are queries: this thread's own statistics, once
@@ -310,6 +343,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
         if (!ROWS_ARE_KEYS) {
             lse_own = pos_row < p.rows ? lse_bh[pos_row] : 0.f;
             d_own = delta_of<DH, BF16>(p, batch, head, pos_row);
+            if (p.stats != nullptr) {  // rows beyond the sequence get (0, 0), like the bounds-checked path
+                p.stats[bh * 2 * p.rows_pad + pos_row] = lse_own;
+                p.stats[bh * 2 * p.rows_pad + p.rows_pad + pos_row] = d_own;
+            }
         }
 
         for (int n = 0; n < n_cols; ++n) {
@@ -349,11 +386,18 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 32; j += 2) {
                             float pv[2], dv[2];
+                            // the columns' statistics, four columns per shared-memory load
+                            float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
+                            if (ROWS_ARE_KEYS) {
+                                l4 = *reinterpret_cast<const float4*>(v_lse + c * 64 + u * 32 + (j & ~3));
+                                d4 = *reinterpret_cast<const float4*>(v_d + c * 64 + u * 32 + (j & ~3));
+                            }
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const int col = c * 64 + u * 32 + j + e;
-                                const float l = ROWS_ARE_KEYS ? v_lse[col] : lse_own;
-                                const float dd = ROWS_ARE_KEYS ? v_d[col] : d_own;
+                                const int k4 = (j + e) & 3;
+                                const float l = !ROWS_ARE_KEYS ? lse_own : k4 == 0 ? l4.x : k4 == 1 ? l4.y : k4 == 2 ? l4.z : l4.w;
+                                const float dd = !ROWS_ARE_KEYS ? d_own : k4 == 0 ? d4.x : k4 == 1 ? d4.y : k4 == 2 ? d4.z : d4.w;
                                 const float pr = fast_exp2(fmaf(__uint_as_float(x[u][j + e]), p.scale_log2, -l));
                                 const float dsv = pr * (__uint_as_float(y[u][j + e]) - dd);
                                 if (MASKED) {
@@ -554,7 +598,19 @@ int launch_bwd_tc(const tmw_prefill_desc& d, const void* q, const void* k, const
     p.lse = lse;
     p.status = device_status_word();
     if (p.status == nullptr) return TMW_ERR_CUDA;
-    const dim3 grid((R + BT - 1) / BT, H, B);
+    // scratch memory for the rows' (lse, D), ordered on the caller's stream; without it the launch whose rows are
+    // keys computes D itself
+    p.rows_pad = (R + BT - 1) / BT * BT;
+    p.stats = nullptr;
+    {
+        void* mem = nullptr;
+        if (cudaMallocAsync(&mem, (size_t)B * H * 2 * p.rows_pad * sizeof(float), stream) == cudaSuccess)
+            p.stats = static_cast<float*>(mem);
+        else
+            (void)cudaGetLastError();
+    }
+    p.n_bx = (R + BT - 1) / BT; p.heads = H; p.batch = B;
+    const dim3 grid(p.n_bx * H * B, 1, 1);
     auto run = [&](auto kern, const CUtensorMap& r1, const CUtensorMap& r2, const CUtensorMap& c1, const CUtensorMap& c2,
                    const CUtensorMap& o1, const CUtensorMap& o2) -> int {
         const int rc = allow_shared_memory(reinterpret_cast<const void*>(kern), L::kTotal);
@@ -562,16 +618,17 @@ int launch_bwd_tc(const tmw_prefill_desc& d, const void* q, const void* k, const
         kern<<<grid, kBwdThreads, L::kTotal, stream>>>(r1, r2, c1, c2, o1, o2, p);
         return TMW_OK;
     };
-    int st;
+    // dQ first: rows are queries (Q, dO), columns are keys (K, V); it also leaves the rows' statistics
+    int st = d.dtype == TMW_BF16 ? run(bwd_tc_kernel<DH, true, false>, mq, mdo, ck, cv, mdq, mdq)
+                                 : run(bwd_tc_kernel<DH, false, false>, mq, mdo, ck, cv, mdq, mdq);
     // dK, dV: rows are keys (K, V), columns are queries (Q, dO)
-    st = d.dtype == TMW_BF16 ? run(bwd_tc_kernel<DH, true, true>, mk, mv, cq, cdo, mdv, mdk)
-                             : run(bwd_tc_kernel<DH, false, true>, mk, mv, cq, cdo, mdv, mdk);
+    if (st == TMW_OK)
+        st = d.dtype == TMW_BF16 ? run(bwd_tc_kernel<DH, true, true>, mk, mv, cq, cdo, mdv, mdk)
+                                 : run(bwd_tc_kernel<DH, false, true>, mk, mv, cq, cdo, mdv, mdk);
+    const cudaError_t launched = cudaGetLastError();
+    if (p.stats != nullptr) (void)cudaFreeAsync(p.stats, stream);
     if (st != TMW_OK) return st;
-    // dQ: rows are queries (Q, dO), columns are keys (K, V)
-    st = d.dtype == TMW_BF16 ? run(bwd_tc_kernel<DH, true, false>, mq, mdo, ck, cv, mdq, mdq)
-                             : run(bwd_tc_kernel<DH, false, false>, mq, mdo, ck, cv, mdq, mdq);
-    if (st != TMW_OK) return st;
-    TMW_CUDA_TRY(cudaGetLastError());
+    TMW_CUDA_TRY(launched);
     return TMW_OK;
 }
 
