@@ -31,7 +31,7 @@ namespace {
 using namespace ptx;
 
 constexpr int BT = 128;          // rows of a tile (the lanes of tensor memory)
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 384;  // 12 warps: see the roles at the kernel
 // Columns per tile and depth of the column-tile ring.  head_dim 64: 64 columns, so that X | Y | accumulators fit
 // into 256 tensor-memory columns and TWO CTAs share an SM - the chain of a tile pair (products, hand-over, load
 // from tensor memory, exponentials, hand-over, products) is serial inside a CTA, and a second CTA is what fills
@@ -201,12 +201,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
         mbar_init(bar(BAR_R_FULL), 1);
         for (int s = 0; s < kColStages; ++s) {
             mbar_init(bar(BAR_C_FULL + s), 1);
-            mbar_init(bar(BAR_C_EMPTY + s), 1);
+            mbar_init(bar(BAR_C_EMPTY + s), 2);  // both issuing warps
         }
         for (int s = 0; s < kColStages; ++s) mbar_init(bar(BAR_V_FULL + s), 1);
-        mbar_init(bar(BAR_XY_FULL), 1);
-        mbar_init(bar(BAR_PDS_READY), 4);
-        mbar_init(bar(BAR_ACC_DONE), 1);
+        mbar_init(bar(BAR_XY_FULL), 2);    // X by one issuing warp, Y by the other
+        mbar_init(bar(BAR_PDS_READY), 8);  // the eight element-wise warps
+        mbar_init(bar(BAR_ACC_DONE), 2);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -268,58 +268,52 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
             }
             __syncwarp();
         }
-    } else if (warp == 1) {
-        // ---------------- tensor-core issue ----------------
-        // (the whole warp runs the loop and computes the operands; one lane issues - a lone lane inside a
-        // divergent branch issues these instructions markedly slower)
+    } else if (warp == 1 || warp == 2) {
+        // ---------------- tensor-core issue: two warps, each with its own chain of products ----------------
+        // warp 1:  X = R1 C1^T,  then (rows are keys)  dV += P^T dO          (P lies over X)
+        // warp 2:  Y = R2 C2^T,  then  dK += dS^T Q  or  dQ += dS K           (dS lies over Y)
+        // The products of one thread execute in issue order, so each warp's next X / Y overwrites the P / dS that
+        // its own earlier product has consumed.  Two issuing threads because one thread feeds the pipe with short
+        // products (N = 64, K = 16) at well below the rate the pipe runs them.  (The whole warp runs the loop and
+        // computes the operands; one lane issues - a lone lane inside a divergent branch issues markedly slower.)
         const bool leader = lane == 0;
+        const bool second = warp == 2;
         const uint32_t fmt = BF16 ? 1u : 0u;
         const uint32_t idesc_xy = idesc_kmajor(fmt, CW);
         const uint32_t idesc_acc = idesc_b_mnmajor(fmt, DH);
+        const bool has_acc = second || ROWS_ARE_KEYS;
+        // the 16-bit intermediates of 16 columns (one k-step) sit in 8 tensor-memory columns; each half of the
+        // column tile keeps its packed values inside its own half (see the element-wise warps)
+        auto packed_col = [](int kk) -> uint32_t { return (uint32_t)((kk / (CW / 32)) * (CW / 2) + (kk % (CW / 32)) * 8); };
         mbar_wait(bar(BAR_R_FULL), 0, abort_flag, p.status);
         for (int n = 0; n < n_cols; ++n) {
             const int s = n % kColStages;
             const uint32_t c_addr = smem_base + L::kC + s * 2 * L::kCTile;
             mbar_wait(bar(BAR_C_FULL + s), (n / kColStages) & 1, abort_flag, p.status);
             tc_fence_after();
-            // X = R1 C1^T, Y = R2 C2^T (both operands K-major over head_dim).  They overwrite the P and dS of
-            // the previous column tile, which the products issued before them have consumed in issue order.
+            // both operands K-major over head_dim
+            const uint32_t r_addr = smem_base + (second ? L::kR2 : L::kR1);
+            const uint32_t c_tile = c_addr + (second ? L::kCTile : 0);
 #pragma unroll
             for (int kk = 0; kk < DH / 16; ++kk) {
-                const uint64_t ad = kmajor_desc(smem_base + L::kR1 + (kk / 4) * L::kSub + (kk % 4) * 32);
-                const uint64_t bd = kmajor_desc(c_addr + (kk / 4) * L::kCSub + (kk % 4) * 32);
-                if (leader) mma_ss(tmem_base + kX, ad, bd, idesc_xy, kk > 0 ? 1u : 0u);
-            }
-#pragma unroll
-            for (int kk = 0; kk < DH / 16; ++kk) {
-                const uint64_t ad = kmajor_desc(smem_base + L::kR2 + (kk / 4) * L::kSub + (kk % 4) * 32);
-                const uint64_t bd = kmajor_desc(c_addr + L::kCTile + (kk / 4) * L::kCSub + (kk % 4) * 32);
-                if (leader) mma_ss(tmem_base + kY, ad, bd, idesc_xy, kk > 0 ? 1u : 0u);
+                const uint64_t ad = kmajor_desc(r_addr + (kk / 4) * L::kSub + (kk % 4) * 32);
+                const uint64_t bd = kmajor_desc(c_tile + (kk / 4) * L::kCSub + (kk % 4) * 32);
+                if (leader) mma_ss(tmem_base + (second ? kY : kX), ad, bd, idesc_xy, kk > 0 ? 1u : 0u);
             }
             if (leader) tc_commit(bar(BAR_XY_FULL));
             __syncwarp();
             mbar_wait(bar(BAR_PDS_READY), n & 1, abort_flag, p.status);
             tc_fence_after();
-            const uint32_t acc = n > 0 ? 1u : 0u;
-            if (ROWS_ARE_KEYS) {
-                // dV += P^T dO : A = P (over X), B = the dO tile read MN-major
+            if (has_acc) {
+                // A = P or dS from tensor memory, B = the other column tile read MN-major:
+                // warp 1: dV += P^T dO (B = C2);  warp 2: dK += dS^T Q  or  dQ += dS K (B = C1)
+                const uint32_t a_base = tmem_base + (second ? kY : kX);
+                const uint32_t d_acc = tmem_base + ((second && ROWS_ARE_KEYS) ? kAcc2 : kAcc1);
+                const uint64_t b0 = mnmajor_desc(second ? c_addr : c_addr + L::kCTile, L::kCSub);
+                const uint32_t acc = n > 0 ? 1u : 0u;
 #pragma unroll
                 for (int kk = 0; kk < CW / 16; ++kk) {
-                    const uint64_t bd = mnmajor_desc(c_addr + L::kCTile, L::kCSub) + kk * 128;
-                    if (leader) mma_ts(tmem_base + kAcc1, tmem_base + kX + kk * 8, bd, idesc_acc, kk > 0 ? 1u : acc);
-                }
-                // dK += dS^T Q : A = dS (over Y), B = the Q tile read MN-major
-#pragma unroll
-                for (int kk = 0; kk < CW / 16; ++kk) {
-                    const uint64_t bd = mnmajor_desc(c_addr, L::kCSub) + kk * 128;
-                    if (leader) mma_ts(tmem_base + kAcc2, tmem_base + kY + kk * 8, bd, idesc_acc, kk > 0 ? 1u : acc);
-                }
-            } else {
-                // dQ += dS K : A = dS (over Y), B = the K tile read MN-major
-#pragma unroll
-                for (int kk = 0; kk < CW / 16; ++kk) {
-                    const uint64_t bd = mnmajor_desc(c_addr, L::kCSub) + kk * 128;
-                    if (leader) mma_ts(tmem_base + kAcc1, tmem_base + kY + kk * 8, bd, idesc_acc, kk > 0 ? 1u : acc);
+                    if (leader) mma_ts(d_acc, a_base + packed_col(kk), b0 + kk * 128, idesc_acc, kk > 0 ? 1u : acc);
                 }
             }
             if (leader) {
@@ -328,22 +322,25 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
             }
             __syncwarp();
         }
-    } else {
-        // ---------------- element-wise warps: one thread per row of the tile ----------------
+    } else if (warp >= 4) {
+        // ---------------- element-wise warps: two threads per row of the tile, half of the columns each ----------------
         const int g = warp & 3;                    // lane group of tensor memory this warp may touch
+        const int half = (warp - 4) >> 2;          // which half of the column tile (and of the output columns)
         const int row = g * 32 + lane;
-        const int tid128 = (warp - 2) * 32 + lane;  // 0 .. 127 among the four warps
+        const int tid256 = (warp - 4) * 32 + lane;  // 0 .. 255 among the eight warps
         const int pos_row = r0 + row;              // position of this thread's key (ROWS_ARE_KEYS) or query
         const uint32_t t_row = tmem_base + ((uint32_t)(g * 32) << 16);
         const long long bh = (long long)batch * p.heads + head;
         const float* lse_bh = p.lse + bh * p.rows;
+        constexpr int HC = CW / 2;                 // columns per thread and tile
+        const int cbase = half * HC;
 
         // rows are queries: this thread's own statistics, once
         float lse_own = 0.f, d_own = 0.f;
         if (!ROWS_ARE_KEYS) {
             lse_own = pos_row < p.rows ? lse_bh[pos_row] : 0.f;
             d_own = delta_of<DH, BF16>(p, batch, head, pos_row);
-            if (p.stats != nullptr) {  // rows beyond the sequence get (0, 0), like the bounds-checked path
+            if (p.stats != nullptr && half == 0) {  // rows beyond the sequence get (0, 0), like the bounds-checked path
                 p.stats[bh * 2 * p.rows_pad + pos_row] = lse_own;
                 p.stats[bh * 2 * p.rows_pad + p.rows_pad + pos_row] = d_own;
             }
@@ -366,66 +363,64 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
 
             mbar_wait(bar(BAR_XY_FULL), n & 1, abort_flag, p.status);
             tc_fence_after();
-            // 64 columns at a time: all loads of the step in flight together.  The body exists twice, with and
-            // without the per-element mask, as straight-line code (a run-time test inside it would split it into
-            // one basic block per element and serialise the elements' dependency chains).
+            // 16 columns at a time.  The body exists twice, with and without the per-element mask, as straight-line
+            // code (a run-time test inside it would split it into one basic block per element and serialise the
+            // elements' dependency chains).  The 16-bit results go back OVER the fp32 inputs, each thread's inside
+            // its own half of the columns: chunk j's 8 packed columns lie in columns this thread has already read.
             auto process = [&](auto masked_tag) {
                 constexpr bool MASKED = decltype(masked_tag)::value;
-#pragma unroll 1
-                for (int c = 0; c < CW / 64; ++c) {
-                    uint32_t x[2][32], y[2][32];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        tmem_ld32(t_row + kX + c * 64 + u * 32, x[u]);
-                        tmem_ld32(t_row + kY + c * 64 + u * 32, y[u]);
-                    }
+                for (int j = 0; j < HC / 16; ++j) {
+                    uint32_t x[16], y[16];
+                    tmem_ld16(t_row + kX + cbase + j * 16, x);
+                    tmem_ld16(t_row + kY + cbase + j * 16, y);
                     tc_wait_ld();
+                    uint32_t pp[8], ds[8];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        uint32_t pp[16], ds[16];
+                    for (int e4 = 0; e4 < 16; e4 += 4) {
+                        float l[4], dd[4];
+                        if (ROWS_ARE_KEYS) {  // the columns' statistics, four columns per shared-memory load
+                            const float4 l4 = *reinterpret_cast<const float4*>(v_lse + cbase + j * 16 + e4);
+                            const float4 d4 = *reinterpret_cast<const float4*>(v_d + cbase + j * 16 + e4);
+                            l[0] = l4.x; l[1] = l4.y; l[2] = l4.z; l[3] = l4.w;
+                            dd[0] = d4.x; dd[1] = d4.y; dd[2] = d4.z; dd[3] = d4.w;
+                        } else {
+                            l[0] = l[1] = l[2] = l[3] = lse_own;
+                            dd[0] = dd[1] = dd[2] = dd[3] = d_own;
+                        }
+                        float pv[4], dv[4];
 #pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            float pv[2], dv[2];
-                            // the columns' statistics, four columns per shared-memory load
-                            float4 l4 = make_float4(0.f, 0.f, 0.f, 0.f), d4 = l4;
-                            if (ROWS_ARE_KEYS) {
-                                l4 = *reinterpret_cast<const float4*>(v_lse + c * 64 + u * 32 + (j & ~3));
-                                d4 = *reinterpret_cast<const float4*>(v_d + c * 64 + u * 32 + (j & ~3));
-                            }
-#pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int col = c * 64 + u * 32 + j + e;
-                                const int k4 = (j + e) & 3;
-                                const float l = !ROWS_ARE_KEYS ? lse_own : k4 == 0 ? l4.x : k4 == 1 ? l4.y : k4 == 2 ? l4.z : l4.w;
-                                const float dd = !ROWS_ARE_KEYS ? d_own : k4 == 0 ? d4.x : k4 == 1 ? d4.y : k4 == 2 ? d4.z : d4.w;
-                                const float pr = fast_exp2(fmaf(__uint_as_float(x[u][j + e]), p.scale_log2, -l));
-                                const float dsv = pr * (__uint_as_float(y[u][j + e]) - dd);
-                                if (MASKED) {
-                                    const bool vis = ROWS_ARE_KEYS ? visible(c0 + col, pos_row, p.rows, p.window, p.np)
-                                                                   : visible(pos_row, c0 + col, p.rows, p.window, p.np);
-                                    pv[e] = vis ? pr : 0.f;
-                                    dv[e] = vis ? dsv : 0.f;
-                                } else {
-                                    pv[e] = pr;
-                                    dv[e] = dsv;
-                                }
-                            }
-                            if (BF16) {
-                                const __nv_bfloat162 a2 = __floats2bfloat162_rn(pv[0], pv[1]);
-                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(dv[0], dv[1]);
-                                pp[j / 2] = *reinterpret_cast<const uint32_t*>(&a2);
-                                ds[j / 2] = *reinterpret_cast<const uint32_t*>(&b2);
+                        for (int e = 0; e < 4; ++e) {
+                            const int col = cbase + j * 16 + e4 + e;
+                            const float pr = fast_exp2(fmaf(__uint_as_float(x[e4 + e]), p.scale_log2, -l[e]));
+                            const float dsv = pr * (__uint_as_float(y[e4 + e]) - dd[e]);
+                            if (MASKED) {
+                                const bool vis = ROWS_ARE_KEYS ? visible(c0 + col, pos_row, p.rows, p.window, p.np)
+                                                               : visible(pos_row, c0 + col, p.rows, p.window, p.np);
+                                pv[e] = vis ? pr : 0.f;
+                                dv[e] = vis ? dsv : 0.f;
                             } else {
-                                const __half2 a2 = __floats2half2_rn(pv[0], pv[1]);
-                                const __half2 b2 = __floats2half2_rn(dv[0], dv[1]);
-                                pp[j / 2] = *reinterpret_cast<const uint32_t*>(&a2);
-                                ds[j / 2] = *reinterpret_cast<const uint32_t*>(&b2);
+                                pv[e] = pr;
+                                dv[e] = dsv;
                             }
                         }
-                        // 16-bit results over the fp32 inputs: the packed columns lie inside columns already read
-                        if (ROWS_ARE_KEYS) tmem_st16(t_row + kX + c * 32 + u * 16, pp);
-                        tmem_st16(t_row + kY + c * 32 + u * 16, ds);
+#pragma unroll
+                        for (int e = 0; e < 4; e += 2) {
+                            if (BF16) {
+                                const __nv_bfloat162 a2 = __floats2bfloat162_rn(pv[e], pv[e + 1]);
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(dv[e], dv[e + 1]);
+                                pp[(e4 + e) / 2] = *reinterpret_cast<const uint32_t*>(&a2);
+                                ds[(e4 + e) / 2] = *reinterpret_cast<const uint32_t*>(&b2);
+                            } else {
+                                const __half2 a2 = __floats2half2_rn(pv[e], pv[e + 1]);
+                                const __half2 b2 = __floats2half2_rn(dv[e], dv[e + 1]);
+                                pp[(e4 + e) / 2] = *reinterpret_cast<const uint32_t*>(&a2);
+                                ds[(e4 + e) / 2] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
+                        }
                     }
+                    if (ROWS_ARE_KEYS) tmem_st8(t_row + kX + cbase + j * 8, pp);
+                    tmem_st8(t_row + kY + cbase + j * 8, ds);
                 }
             };
             if (full) process(std::false_type{}); else process(std::true_type{});
@@ -436,6 +431,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
         }
 
         // ---------------- output: accumulators -> 16 bits -> shared memory (swizzled) -> TMA store ----------------
+        // (each of a row's two threads takes half of the output columns)
         mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag, p.status);
         tc_fence_after();
         constexpr int kOutputs = ROWS_ARE_KEYS ? 2 : 1;
@@ -446,11 +442,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
             uint8_t* stage = smem + (which == 0 ? L::kR1 : L::kR2);  // the row tiles are no longer needed
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
-                uint32_t o[32];
-                tmem_ld32(t_row + (which == 0 ? kAcc1 : kAcc2) + c * 32, o);
+                uint32_t o[16];
+                const int col0 = half * (DH / 2) + c * 16;
+                tmem_ld16(t_row + (which == 0 ? kAcc1 : kAcc2) + col0, o);
                 tc_wait_ld();
 #pragma unroll
-                for (int g8 = 0; g8 < 4; ++g8) {
+                for (int g8 = 0; g8 < 2; ++g8) {
                     uint32_t w[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
@@ -464,15 +461,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
                             w[e] = *reinterpret_cast<const uint32_t*>(&hh);
                         }
                     }
-                    const int col = c * 32 + g8 * 8;
+                    const int col = col0 + g8 * 8;
                     uint8_t* dst = stage + (col / 64) * L::kSub + row * 128 + ((((col % 64) / 8) ^ (row & 7)) * 16);
                     *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
         }
         fence_proxy_async_smem();
-        named_barrier_sync(2, BT);
-        if (tid128 == 0) {
+        named_barrier_sync(2, 2 * BT);
+        if (tid256 == 0) {
             int c1, c2;
             coords(kO1, r0, c1, c2);
             for (int u = 0; u < NSUB; ++u)
