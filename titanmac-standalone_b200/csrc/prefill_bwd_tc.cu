@@ -131,15 +131,6 @@ __device__ __forceinline__ ColPlan col_plan(int r0, int L, int w, int np) {
     return c;
 }
 
-// (bitwise on purpose: short-circuit operators would put branches between the elements of a row, and the compiler
-// then cannot interleave their arithmetic)
-__device__ __forceinline__ bool visible(int pq, int pk, int L, int w, int np) {
-    const bool inside = (pq < L) & (pk < L);
-    const bool pers_key = pk < np;
-    const bool in_window = (pq >= np) & (pk <= pq) & (pq - pk <= w);
-    return inside & (pers_key | in_window);
-}
-
 template <int DH, bool BF16, bool ROWS_ARE_KEYS>
 __global__ void __launch_bounds__(kBwdThreads, Geo<DH>::kCtasPerSm)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant__ CUtensorMap map_r2,
@@ -302,6 +293,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
             }
             if (leader) tc_commit(bar(BAR_XY_FULL));
             __syncwarp();
+            // (the next column tile has usually landed: seeing it now takes that wait off the path hand-over ->
+            // products of this tile -> X / Y of the next)
+            if (n + 1 < n_cols)
+                mbar_wait(bar(BAR_C_FULL + (n + 1) % kColStages), ((n + 1) / kColStages) & 1, abort_flag, p.status);
             mbar_wait(bar(BAR_PDS_READY), n & 1, abort_flag, p.status);
             tc_fence_after();
             if (has_acc) {
@@ -361,6 +356,23 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
                 full = r0 + BT <= p.rows && c0 + CW <= p.rows &&
                        (chi < p.np || (clo >= p.np && rlo >= p.np && chi <= rlo && rhi - clo <= p.window));
 
+            // Columns of this tile that this thread's row sees: [vlo, vhi] (relative to the tile) and, when the rows
+            // are queries, the persistent keys below column npc.  Same set as visible(), at two instructions per element.
+            int vlo = 1, vhi = 0, npc = 0;
+            if (pos_row < p.rows) {
+                if (ROWS_ARE_KEYS) {
+                    if (pos_row < p.np) { vlo = 0; vhi = p.rows - 1 - c0; }
+                    else { vlo = pos_row - c0; vhi = min(pos_row + p.window, p.rows - 1) - c0; }
+                } else {
+                    npc = p.np - c0;
+                    if (pos_row >= p.np) { vlo = max(p.np, pos_row - p.window) - c0; vhi = pos_row - c0; }
+                }
+            }
+            const int vbase = cbase - vlo;                 // column - vlo = vbase + (column - cbase)
+            const unsigned vspan = (unsigned)max(vhi - vlo, -1);   // vhi < vlo: empty (0xffffffff would mean everything)
+            const bool vnone = vhi < vlo;
+            const int pbase = npc - cbase;                 // column < npc  <=>  (column - cbase) < pbase
+
             mbar_wait(bar(BAR_XY_FULL), n & 1, abort_flag, p.status);
             tc_fence_after();
             // 16 columns at a time.  The body exists twice, with and without the per-element mask, as straight-line
@@ -391,12 +403,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
                         float pv[4], dv[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const int col = cbase + j * 16 + e4 + e;
                             const float pr = fast_exp2(fmaf(__uint_as_float(x[e4 + e]), p.scale_log2, -l[e]));
                             const float dsv = pr * (__uint_as_float(y[e4 + e]) - dd[e]);
                             if (MASKED) {
-                                const bool vis = ROWS_ARE_KEYS ? visible(c0 + col, pos_row, p.rows, p.window, p.np)
-                                                               : visible(pos_row, c0 + col, p.rows, p.window, p.np);
+                                const int rel = j * 16 + e4 + e;  // column - cbase, a compile-time constant
+                                bool vis = ((unsigned)(vbase + rel) <= vspan) & !vnone;
+                                if (!ROWS_ARE_KEYS) vis |= rel < pbase;
                                 pv[e] = vis ? pr : 0.f;
                                 dv[e] = vis ? dsv : 0.f;
                             } else {
