@@ -435,7 +435,22 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
                     tmem_st8(t_row + kY + cbase + j * 8, ds);
                 }
             };
-            if (full) process(std::false_type{}); else process(std::true_type{});
+            // a warp none of whose rows sees any of its columns (rows beyond the diagonal or the window's edge, or the
+            // sequence keys of a tile that far queries only reach through the persistent keys) writes zeros unread
+            const bool mine_empty = vnone || vhi < cbase || vlo >= cbase + HC;
+            const bool nothing = !full && __all_sync(0xffffffffu, mine_empty && (ROWS_ARE_KEYS || pbase <= 0 || pos_row >= p.rows));
+            if (nothing) {
+                const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+                for (int j = 0; j < HC / 16; ++j) {
+                    if (ROWS_ARE_KEYS) tmem_st8(t_row + kX + cbase + j * 8, zero);
+                    tmem_st8(t_row + kY + cbase + j * 8, zero);
+                }
+            } else if (full) {
+                process(std::false_type{});
+            } else {
+                process(std::true_type{});
+            }
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
