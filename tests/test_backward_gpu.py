@@ -81,6 +81,36 @@ def test_core_gradients_against_oracle_autograd(dtype, tol, dh, H, B, L, w, Np):
     _native.poll_status(torch.device(DEV))
 
 
+def test_tcgen05_backward_captured_in_a_cuda_graph_and_replayed():
+    """The tcgen05 backward takes its scratch memory (the rows' lse and D between its two launches) from a
+    stream-ordered pool: the call must also work while a stream is being captured, and every replay of the graph
+    must give the gradients of an eager call - bit for bit, the launches are deterministic."""
+    B, H, L, dh, w, Np = 2, 2, 16 + 700, 64, 200, 16
+    q, k, v = (t.to(torch.bfloat16).to(DEV) for t in wo.qkv_inputs(B, H, L, dh, seed=5))
+    lse = torch.empty(B, H, L, dtype=torch.float32, device=DEV)
+    o = _native.prefill(q, k, v, w, Np, lse=lse)
+    d_o = torch.randn(B, L, H, dh, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(DEV).permute(0, 2, 1, 3)
+    want = [torch.empty_like(q) for _ in range(3)]
+    _native.prefill_backward(q, k, v, o, d_o, lse, *want, w, Np, algo=_native.ALGO_TCGEN05)
+    got = [torch.zeros_like(q) for _ in range(3)]
+    side = torch.cuda.Stream(device=DEV)
+    side.wait_stream(torch.cuda.current_stream(DEV))
+    with torch.cuda.stream(side):
+        _native.prefill_backward(q, k, v, o, d_o, lse, *got, w, Np, algo=_native.ALGO_TCGEN05)  # warm-up
+    torch.cuda.current_stream(DEV).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        _native.prefill_backward(q, k, v, o, d_o, lse, *got, w, Np, algo=_native.ALGO_TCGEN05)
+    for _ in range(3):
+        for t in got:
+            t.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for a, b, nm in zip(got, want, ("dq", "dk", "dv")):
+            assert torch.equal(a, b), nm
+    _native.poll_status(torch.device(DEV))
+
+
 def test_block_trains_end_to_end():
     """One TitanBlock with the windowed class under grad mode: every parameter and the input get a gradient,
     and the forward value equals the inference path's."""

@@ -298,6 +298,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int n_tiles = (p.n + BN - 1) / BN, m_tiles = (p.m + 2 * GM - 1) / (2 * GM);
     const int tiles = n_tiles * m_tiles;
     const int k_blocks = (p.k + GK - 1) / GK;
+    // columns a tile multiplies: BN, or for the last tile of a row what is left of N (in steps of 32) - a product
+    // over columns that do not exist would cost its full time
+    auto n_of = [&](int tile) -> int {
+        const int rem = p.n - (tile % n_tiles) * BN;
+        return rem >= BN ? BN : (rem + 31) / 32 * 32;
+    };
 
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -326,7 +332,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int n = 0;
         for (int tile = pair; tile < tiles; tile += pairs) {
             const int row0 = (tile / n_tiles) * (2 * GM) + (int)rank * GM;
-            const int col0 = (tile % n_tiles) * BN + (int)rank * (BN / 2);
+            // each CTA supplies half of the tile's columns (the box is BN / 2 rows; a narrow tile uses its first rows)
+            const int col0 = (tile % n_tiles) * BN + (int)rank * (n_of(tile) / 2);
             for (int kb = 0; kb < k_blocks; ++kb, ++n) {
                 const int s = n % S;
                 mbar_wait(empty(s), ((n / S) & 1) ^ 1, abort_flag, p.status);
@@ -343,10 +350,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else if (warp == 1) {
         // ---------------- tensor-core issue (first CTA of the pair only) ----------------
         if (rank == 0) {
-            const uint32_t idesc = idesc_kmajor(BF16 ? 1u : 0u, BN, 2 * GM);
             int n = 0, t = 0;
             for (int tile = pair; tile < tiles; tile += pairs, ++t) {
                 const int buf = t & 1;
+                const uint32_t idesc = idesc_kmajor(BF16 ? 1u : 0u, (uint32_t)n_of(tile), 2 * GM);
                 mbar_wait(acc_empty(buf), ((t >> 1) & 1) ^ 1, abort_flag, p.status);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
@@ -373,15 +380,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int half = (warp - 2) >> 2;
         const int row = g * 32 + lane;
         constexpr int kPanels = BN / kPanel;
-        constexpr int kHalfPanels = (kPanels + 1) / 2;
-        const int panel0 = half == 0 ? 0 : kHalfPanels;
-        const int panel1 = half == 0 ? kHalfPanels : kPanels;
         uint8_t* stage = smem + S * L::kStage;
         const bool epi_leader = warp == 2 && lane == 0;
         int t = 0;
         for (int tile = pair; tile < tiles; tile += pairs, ++t) {
             const int buf = t & 1;
             const int row0 = (tile / n_tiles) * (2 * GM) + (int)rank * GM, col0 = (tile % n_tiles) * BN;
+            // the tile's panels of 32 columns, split between the two warps of a lane group
+            const int panels = n_of(tile) / kPanel, half_panels = (panels + 1) / 2;
+            const int panel0 = half == 0 ? 0 : half_panels;
+            const int panel1 = half == 0 ? half_panels : panels;
             mbar_wait(acc_full(buf), (t >> 1) & 1, abort_flag, p.status);
             tc_fence_after();
             if (epi_leader) tma_store_wait_read();

@@ -594,6 +594,36 @@ bool make_map4(CUtensorMap* map, const void* base, int dtype, int batch, int hea
     return true;
 }
 
+// Stream-ordered scratch memory comes from a pool of the library's own (one per device, created on first use,
+// kept for the life of the process): freed blocks stay in the pool, so a call costs no trip to the driver's
+// allocator after the first, and the device's default pool and its settings are left alone.
+cudaMemPool_t scratch_pool() {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mutex;
+    static cudaMemPool_t pools[kMaxDevices] = {};
+    static bool tried[kMaxDevices] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!tried[dev]) {
+        tried[dev] = true;
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = dev;
+        cudaMemPool_t pool = nullptr;
+        if (cudaMemPoolCreate(&pool, &props) == cudaSuccess) {
+            unsigned long long keep = ~0ull;
+            (void)cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+            pools[dev] = pool;
+        } else {
+            (void)cudaGetLastError();
+        }
+    }
+    return pools[dev];
+}
+
 template <int DH>
 int launch_bwd_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o, const void* d_o,
                   const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream) {
@@ -628,7 +658,9 @@ int launch_bwd_tc(const tmw_prefill_desc& d, const void* q, const void* k, const
     p.stats = nullptr;
     {
         void* mem = nullptr;
-        if (cudaMallocAsync(&mem, (size_t)B * H * 2 * p.rows_pad * sizeof(float), stream) == cudaSuccess)
+        cudaMemPool_t pool = scratch_pool();
+        if (pool != nullptr &&
+            cudaMallocFromPoolAsync(&mem, (size_t)B * H * 2 * p.rows_pad * sizeof(float), pool, stream) == cudaSuccess)
             p.stats = static_cast<float*>(mem);
         else
             (void)cudaGetLastError();
