@@ -107,7 +107,10 @@ TMW_API int tmw_prefill_lse(const tmw_prefill_desc* desc, const void* q, const v
  * here over the visible pairs only.  For bf16 / f16 with head_dim 64 or 128: tcgen05 kernels (products and the
  * 16-bit intermediates in tensor memory; desc->algo TMW_ALGO_AUTO or TMW_ALGO_TCGEN05), or the older warp-level
  * tensor-core kernels (TMW_ALGO_MMA); fp32 arithmetic on CUDA cores otherwise, or for every case with
- * TMW_ALGO_SIMT.  All of them accumulate in fp32.
+ * TMW_ALGO_SIMT.  All of them accumulate in fp32.  The tcgen05 path keeps 8 bytes per (batch, head, row) between
+ * its two launches in scratch memory that it takes, ordered on `stream`, from a memory pool of the library's own
+ * (created on first use per device, kept until the process ends; usable while `stream` is being captured); if the
+ * pool cannot be had it recomputes those numbers instead.
  */
 TMW_API int tmw_prefill_backward(const tmw_prefill_desc* desc, const void* q, const void* k, const void* v,
                                  const void* o, const void* d_o, const float* lse, void* dq, void* dk, void* dv,

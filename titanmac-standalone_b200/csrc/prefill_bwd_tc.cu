@@ -7,15 +7,17 @@
 //   S = Q Kᵀ,  P = exp2(S c - lse) o mask,  dP = dO Vᵀ,  D_i = dO_i · O_i,  dS = P o (dP - D)
 //   dV = Pᵀ dO,  dK = scale · dSᵀ Q,  dQ = scale · dS K
 // and the same split into two launches of ONE kernel template - no atomics, results independent of the schedule:
-//   ROWS_ARE_KEYS  : a CTA owns 128 keys and walks over the 128-query tiles that can see them  -> dK, dV
-//   !ROWS_ARE_KEYS : a CTA owns 128 queries and walks over the 128-key tiles of their windows -> dQ
+//   !ROWS_ARE_KEYS : a CTA owns 128 queries and walks over the 64-key tiles of their windows -> dQ   (runs first)
+//   ROWS_ARE_KEYS  : a CTA owns 128 keys and walks over the 64-query tiles that can see them  -> dK, dV
 // The rows a CTA owns sit on the 128 lanes of tensor memory.  Per (row tile, column tile):
 //   X = R1 C1ᵀ and Y = R2 C2ᵀ                (R1,R2 = K,V or Q,dO of the rows;  C1,C2 = Q,dO or K,V of the columns)
-//   four warps, one thread per row, turn X into P and Y into dS (32 columns at a time) and write both back into
+//   eight warps, two threads per row, turn X into P and Y into dS (16 columns at a time) and write both back into
 //   tensor memory as 16-bit values OVER X and Y,
 //   then  acc += Pᵀ-or-dS (from tensor memory) · column tile (from shared memory, read as an MN-major operand).
-// Warps: 0 TMA producer, 1 issues every tcgen05.mma (one elected thread; allocates tensor memory), 2-5 the
-// element-wise work and the output.  Every mbarrier wait is bounded (TMW_ERR_DEVICE_TIMEOUT in the status word).
+// Warps: 0 TMA producer (and the columns' statistics), 1 and 2 issue the tcgen05.mma (one elected thread each, each
+// its own chain of products; warp 1 allocates tensor memory), 3 idle, 4-11 the element-wise work and the output.
+// The first launch leaves every row's (log-sum-exp, D) in scratch memory for the second.  Every mbarrier wait is
+// bounded (TMW_ERR_DEVICE_TIMEOUT in the status word).
 #include <cuda.h>
 
 #include <cstdio>
