@@ -539,7 +539,10 @@ def run_ours(args, wl_name: str, wl: dict) -> None:
                                               for v in e2e_stats["per_rank_ms_per_step"]],
                     "copy_only_ceiling": pcie, "cpu_affinity": affinity,
                     "how": "HostPipeline: H2D copy, forward and D2H copy of consecutive steps overlap on 3 streams"},
-            "gpu_launches": args.steps * stats["regions"] * (3 if "block_size" in wl else 1),
+            # this library's kernels per step: the attention core (block-sparse: convolution + two core launches)
+            # and, for 16-bit types, the two projections (tmw_linear)
+            "gpu_launches": args.steps * stats["regions"] * ((3 if "block_size" in wl else 1) +
+                                                              (2 if wl["dtype"] in ("bf16", "fp16") else 0)),
             "clocks": clk,
         }
         if extra:
