@@ -10,6 +10,9 @@
 //   warps 4-7   softmax group of query tile 0      (one thread per query row)
 //   warps 8-11  softmax group of query tile 1
 // (the issuing warps come first so that they are the oldest warps of their schedulers)
+// head_dim 64 runs one query tile per CTA and two CTAs per SM instead (8 warps), or - windows of 192 keys and
+// more - with TWO threads per score row (12 warps: warps w and w + 4 share the 32 rows of their lane group,
+// take 64 of a key tile's 128 columns each and exchange the row maximum and sum through shared memory).
 // Key positions are cut into 128-key tiles anchored at (first query position - w), so
 // the second query tile always needs the same tiles shifted by one: both tiles share
 // every K/V tile that is loaded, and tiles that lie outside a query tile's window are
@@ -43,14 +46,17 @@ namespace {
 // producer / issuing warps shrink to kRegsService, the softmax warps grow to kRegsSoftmax; setmaxnreg.inc
 // blocks until the registers it asks for have been released INSIDE THE CTA and nothing bounds that wait, so
 // the numbers must add up.
-template <int TILES>
+template <int TILES, int RS>
 struct Budget {
-    static constexpr int kThreads = 128 + TILES * 128;
-    static constexpr int kRegsLaunch = TILES == 2 ? 168 : 128;
-    static constexpr int kRegsService = TILES == 2 ? 80 : 56;
-    static constexpr int kRegsSoftmax = TILES == 2 ? 208 : 200;
-    static_assert(kThreads * kRegsLaunch <= 65536 / (TILES == 2 ? 1 : 2), "register file");
-    static_assert(128 * (kRegsLaunch - kRegsService) >= TILES * 128 * (kRegsSoftmax - kRegsLaunch),
+    static_assert(RS == 1 || (RS == 2 && TILES == 1), "two threads per score row: one-tile CTAs only");
+    static constexpr int kThreads = 128 + TILES * 128 * RS;
+    static constexpr int kCtasPerSm = TILES == 2 ? 1 : 2;
+    // one thread per row: 168 | 80 | 208 (two tiles), 128 | 56 | 200 (one tile);  two threads per row: 80 | 40 | 96
+    static constexpr int kRegsLaunch = RS == 2 ? 80 : TILES == 2 ? 168 : 128;
+    static constexpr int kRegsService = RS == 2 ? 40 : TILES == 2 ? 80 : 56;
+    static constexpr int kRegsSoftmax = RS == 2 ? 96 : TILES == 2 ? 208 : 200;
+    static_assert(kThreads * kRegsLaunch <= 65536 / kCtasPerSm, "register file");
+    static_assert(128 * (kRegsLaunch - kRegsService) >= TILES * 128 * RS * (kRegsSoftmax - kRegsLaunch),
                   "setmaxnreg: the issuing warps must release what the softmax warps request");
 };
 constexpr int BM = 128;  // query rows per tile
@@ -273,6 +279,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : TMW_R8(r, 0), TMW_R8(r, 8)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+        ::"r"(taddr), TMW_I8(r, 0)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -370,7 +390,8 @@ struct TcSmem {
     static constexpr int kK = kQ + TILES * kTileBytes;   // KS tiles
     static constexpr int kV = kK + KS * kTileBytes;      // VS tiles
     static constexpr int kP = kV + VS * kTileBytes;      // persistent K then V: np_pad x DH x 2 bytes each
-    static int total_bytes(int np_pad) { return kP + 2 * np_pad * DH * 2 + 1024 /*barriers*/ + 1024 /*alignment*/; }
+    // after the tiles: barriers (512 bytes), then the exchange area of rows that two threads share (3 KB)
+    static int total_bytes(int np_pad) { return kP + 2 * np_pad * DH * 2 + 4096 + 1024 /*alignment*/; }
 };
 
 // barrier slots inside the barrier area
@@ -392,8 +413,8 @@ enum BarSlot {
 
 // GENERAL = false: the plain windowed mask (every mode parameter a compile-time constant);
 // GENERAL = true: block-granular window and / or the unmasked "all keys" mode, read from the parameters.
-template <int DH, int KS, int VS, bool BF16, int TILES, bool GENERAL>
-__global__ void __launch_bounds__(Budget<TILES>::kThreads, TILES == 2 ? 1 : 2)
+template <int DH, int KS, int VS, bool BF16, int TILES, bool GENERAL, int RS>
+__global__ void __launch_bounds__(Budget<TILES, RS>::kThreads, Budget<TILES, RS>::kCtasPerSm)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                   const __grid_constant__ CUtensorMap map_kp, const __grid_constant__ CUtensorMap map_vp,
@@ -431,9 +452,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         mbar_init(bar(BAR_KP_FULL), 1);
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar(BAR_S_FULL + t), 1);
-            mbar_init(bar(BAR_P_READY + t), BM / 32);  // one arrival per softmax warp
+            mbar_init(bar(BAR_P_READY + t), RS * BM / 32);  // one arrival per softmax warp
             mbar_init(bar(BAR_O_DONE + t), 1);
-            mbar_init(bar(BAR_S_FREE + t), BM / 32);
+            mbar_init(bar(BAR_S_FREE + t), RS * BM / 32);
             mbar_init(bar(BAR_PV_DONE + t), 1);
             mbar_init(bar(BAR_TURN + t), BM / 32);
         }
@@ -465,8 +486,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     };
 
     if (warp < 4) {
-        // register budget: see Budget<TILES>
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Budget<TILES>::kRegsService) : "memory");
+        // register budget: see Budget
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Budget<TILES, RS>::kRegsService) : "memory");
         // Every role warp runs its loop with all 32 lanes (so the warp never splits into a running
         // lane and 31 lanes parked at the final barrier); one lane issues the asynchronous operations.
         const bool leader = lane == 0;
@@ -674,9 +695,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
     } else {
         // ---------------- softmax groups ----------------
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Budget<TILES>::kRegsSoftmax) : "memory");
-        const int t = (warp >> 2) - 1;                 // query tile of this group
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Budget<TILES, RS>::kRegsSoftmax) : "memory");
+        // one thread per score row, or (RS == 2) two: warps w and w + 4 share the rows of their lane group and
+        // take 64 of a key tile's 128 columns each, half of the output columns, and exchange the row maxima
+        // and sums through shared memory
+        const int t = RS == 2 ? 0 : (warp >> 2) - 1;   // query tile of this group
+        const int half = RS == 2 ? (warp >> 2) - 1 : 0;
         const int row = threadIdx.x & (BM - 1);        // row of the tile == tensor-memory lane
+        constexpr int NCH = 4 / RS;                    // 32-column chunks per thread
+        const int c_first = half * NCH;                // this thread's first chunk
+        float* xmax = reinterpret_cast<float*>(bar_area + 512);        // [item parity][half][row]
+        float* xsum = xmax + 4 * BM;                                   // [half][row]
         const QtPlan q = t == 0 ? plan.qt[0] : plan.qt[1];
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         using TM = TmemMap<DH, TILES>;
@@ -725,20 +754,21 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             const int nchunks = (ncols + 31) / 32;
             // 32-column chunks in which no row of this warp sees a key (beyond the diagonal, or before the
             // window's left edge): not loaded, not exponentiated, P = 0
-            bool hid[4] = {false, false, false, false};
-            if (!full) {
+            // (cc counts this thread's chunks, c = c_first + cc is the chunk's place in the tile)
+            bool hid[NCH];
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    hid[c] = __all_sync(0xffffffffu, j_hi - c * 32 < 0 || j_lo - c * 32 > 31);
+            for (int cc = 0; cc < NCH; ++cc) {
+                const int c = c_first + cc;
+                hid[cc] = !full && __all_sync(0xffffffffu, j_hi - c * 32 < 0 || j_lo - c * 32 > 31);
             }
 
             mbar_wait(bar(BAR_S_FULL + t), item & 1, abort_flag, p.status);
             tc_fence_after();
 
-            uint32_t s[4][32];
+            uint32_t s[NCH][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (c < nchunks && !hid[c]) tmem_ld32(s_addr + c * 32, s[c]);
+            for (int cc = 0; cc < NCH; ++cc)
+                if (c_first + cc < nchunks && !hid[cc]) tmem_ld32(s_addr + (c_first + cc) * 32, s[cc]);
             tc_wait_ld();
             if (TM::kSplitP) {
                 // S is in registers now: let the issuing warp overwrite it with the next item's scores
@@ -751,30 +781,39 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             // over four independent chains of 3-input max
             if (!full) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    if (c < nchunks && !hid[c]) {
+                for (int cc = 0; cc < NCH; ++cc)
+                    if (c_first + cc < nchunks && !hid[cc]) {
+                        const int c = c_first + cc;
                         const int lo = j_lo - c * 32, hi = j_hi - c * 32;  // visible columns of the chunk: [lo, hi]
                         if (!__all_sync(0xffffffffu, lo <= 0 && hi >= 31)) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (j < lo || j > hi) s[c][j] = 0xff800000u;  // -inf
+                                if (j < lo || j > hi) s[cc][j] = 0xff800000u;  // -inf
                         }
                     }
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (c < nchunks && !hid[c]) {
+            for (int cc = 0; cc < NCH; ++cc)
+                if (c_first + cc < nchunks && !hid[cc]) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            mx[k] = max3(mx[k], __uint_as_float(s[c][j + 2 * k]), __uint_as_float(s[c][j + 2 * k + 1]));
+                            mx[k] = max3(mx[k], __uint_as_float(s[cc][j + 2 * k]), __uint_as_float(s[cc][j + 2 * k + 1]));
                         }
                     }
                 }
             float tile_max = max3(fmaxf(mx[0], mx[1]), mx[2], mx[3]);
             tile_max *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
+            if (RS == 2) {
+                // the row's other half: through shared memory, two buffers in turn (a buffer is written again two
+                // items later, behind the next item's barrier, when both threads of every row have read it)
+                float* xm = xmax + (item & 1) * 2 * BM;
+                xm[half * BM + row] = tile_max;
+                named_barrier_sync(3 + (warp & 3), 64);  // the two warps that share these 32 rows
+                tile_max = fmaxf(tile_max, xm[(half ^ 1) * BM + row]);
+            }
 
             if (TM::kSplitP && item > 0) {
                 // the previous P V must have finished before O is rescaled or P is overwritten.  (Keeping the
@@ -792,14 +831,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 const float alpha = (m_new == -INFINITY) ? 1.f : fast_exp2(m_used - m_new);
                 m_used = m_new;
                 l_sum *= alpha;
+                if (RS == 2) {
+                    // this thread's half of the output columns, 16 at a time: the scores stay live in registers
 #pragma unroll
-                for (int c = 0; c < DH / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_ld32(o_addr + c * 32, o);
-                    tc_wait_ld();
+                    for (int cc = 0; cc < DH / 32; ++cc) {
+                        uint32_t o[16];
+                        tmem_ld16(o_addr + half * (DH / 2) + cc * 16, o);
+                        tc_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-                    tmem_st32(o_addr + c * 32, o);
+                        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                        tmem_st16(o_addr + half * (DH / 2) + cc * 16, o);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < DH / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(o_addr + c * 32, o);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                        tmem_st32(o_addr + c * 32, o);
+                    }
                 }
             }
 
@@ -810,33 +862,41 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             uint64_t lacc[2] = {0ull, 0ull};  // four partial row sums
             if (kAlternate) mbar_wait(my_turn, (uint32_t)(item & 1) ^ (t == 0 ? 1u : 0u), abort_flag, p.status);
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                if (c < nchunks) {
-                    uint32_t packed[16];
-                    if (hid[c]) {
+            for (int cc = 0; cc < NCH; ++cc)
+                if (c_first + cc < nchunks) {
+                    const int c = c_first + cc;
+                    // 32 score columns -> 16 packed columns per store (two threads per row: 16 -> 8, fewer
+                    // registers in flight)
+                    constexpr int PART = RS == 2 ? 8 : 16;  // column pairs per store
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) packed[i] = 0u;
-                        tmem_st16(p_addr + c * 16, packed);
-                        continue;
-                    }
+                    for (int part = 0; part < 16 / PART; ++part) {
+                        uint32_t packed[PART];
+                        if (hid[cc]) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const uint64_t x = fma2(pack2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
-                                                scale2, negm2);
-                        float x0, x1;
-                        unpack2(x, x0, x1);
-                        const float e0 = fast_exp2(x0);
-                        const float e1 = fast_exp2(x1);
-                        lacc[i & 1] = add2(lacc[i & 1], pack2(e0, e1));
-                        if (BF16) {
-                            const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-                            packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                            for (int i = 0; i < PART; ++i) packed[i] = 0u;
                         } else {
-                            const __half2 h = __floats2half2_rn(e0, e1);
-                            packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+#pragma unroll
+                            for (int i = 0; i < PART; ++i) {
+                                const int j = (part * PART + i) * 2;
+                                const uint64_t x = fma2(pack2(__uint_as_float(s[cc][j]), __uint_as_float(s[cc][j + 1])),
+                                                        scale2, negm2);
+                                float x0, x1;
+                                unpack2(x, x0, x1);
+                                const float e0 = fast_exp2(x0);
+                                const float e1 = fast_exp2(x1);
+                                lacc[i & 1] = add2(lacc[i & 1], pack2(e0, e1));
+                                if (BF16) {
+                                    const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+                                    packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                                } else {
+                                    const __half2 h = __floats2half2_rn(e0, e1);
+                                    packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                                }
+                            }
                         }
+                        if constexpr (RS == 2) tmem_st8(p_addr + c * 16 + part * 8, packed);
+                        else tmem_st16(p_addr + c * 16, packed);
                     }
-                    tmem_st16(p_addr + c * 16, packed);
                 }
             {
                 float a0, a1, a2, a3;
@@ -864,13 +924,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
             // ---------------- epilogue: O / l -> shared memory (swizzled) -> TMA store ----------------
             mbar_wait(bar(BAR_O_DONE + t), 0, abort_flag, p.status);
             tc_fence_after();
+            if (RS == 2) {  // the row's sum: both halves
+                xsum[half * BM + row] = l_sum;
+                named_barrier_sync(1, RS * BM);
+                l_sum += xsum[(half ^ 1) * BM + row];
+            }
             const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
-            if (p.lse != nullptr && row < q.rows)
+            if (p.lse != nullptr && row < q.rows && half == 0)
                 p.lse[((long long)batch * gridDim.y + head) * p.q_rows + (blockIdx.x * TILES + t) * BM + row] =
                     m_used + log2f(l_sum);
             uint8_t* stage = smem + L::kQ + t * L::kTileBytes;  // the Q tile is no longer needed
 #pragma unroll
-            for (int c = 0; c < DH / 32; ++c) {
+            for (int cc = 0; cc < DH / 32 / RS; ++cc) {  // this thread's share of the output columns
+                const int c = half * (DH / 32 / RS) + cc;
                 uint32_t o[32];
                 tmem_ld32(o_addr + c * 32, o);
                 tc_wait_ld();
@@ -897,8 +963,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
                 }
             }
             fence_proxy_async_smem();
-            named_barrier_sync(1 + t, BM);
-            if (row == 0) {
+            named_barrier_sync(1 + t, RS * BM);
+            if (row == 0 && half == 0) {
                 int c1, c2;
                 coords(3, (blockIdx.x * TILES + t) * BM, c1, c2);
                 for (int u = 0; u < NSUB; ++u)
@@ -1035,7 +1101,7 @@ bool make_map(CUtensorMap* map, const void* base, int dtype, int batch, int head
 
 int np_pad_of(int np) { return np > 0 ? ((np + 15) / 16) * 16 : 0; }
 
-template <int DH, int KS, int VS, int TILES>
+template <int DH, int KS, int VS, int TILES, int RS>
 int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, void* o, cudaStream_t stream,
               int window_block, bool all_keys, float* lse, const tmw_halo_wait* wait) {
     using L = TcSmem<DH, KS, VS, TILES>;
@@ -1075,7 +1141,7 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     if (p.status == nullptr) return TMW_ERR_CUDA;
     const int smem_bytes = L::total_bytes(np_pad);
     dim3 grid((d.q_rows + TILES * BM - 1) / (TILES * BM), d.heads, d.batch);
-    constexpr int kThreadsTc = Budget<TILES>::kThreads;
+    constexpr int kThreadsTc = Budget<TILES, RS>::kThreads;
     const bool general = window_block > 0 || all_keys;
     auto run = [&](auto kern) -> int {
         const int rc = allow_shared_memory(reinterpret_cast<const void*>(kern), smem_bytes);
@@ -1085,9 +1151,9 @@ int launch_tc(const tmw_prefill_desc& d, const void* q, const void* k, const voi
     };
     int st;
     if (d.dtype == TMW_BF16)
-        st = general ? run(prefill_tc_kernel<DH, KS, VS, true, TILES, true>) : run(prefill_tc_kernel<DH, KS, VS, true, TILES, false>);
+        st = general ? run(prefill_tc_kernel<DH, KS, VS, true, TILES, true, RS>) : run(prefill_tc_kernel<DH, KS, VS, true, TILES, false, RS>);
     else
-        st = general ? run(prefill_tc_kernel<DH, KS, VS, false, TILES, true>) : run(prefill_tc_kernel<DH, KS, VS, false, TILES, false>);
+        st = general ? run(prefill_tc_kernel<DH, KS, VS, false, TILES, true, RS>) : run(prefill_tc_kernel<DH, KS, VS, false, TILES, false, RS>);
     if (st != TMW_OK) return st;
     TMW_CUDA_TRY(cudaGetLastError());
     return TMW_OK;
@@ -1123,11 +1189,17 @@ int launch_prefill_tc(const tmw_prefill_desc& d, const void* q, const void* k, c
         // One query tile per CTA and two CTAs per SM when two such CTAs fit into shared memory (they do
         // unless there are many persistent keys): independent CTAs drift apart, so one CTA's exponentials,
         // start-up and output phase overlap the other's matrix products.
-        if (TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem)
-            return launch_tc<64, 3, 2, 1>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
-        return launch_tc<64, 3, 3, 2>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
+        if (TcSmem<64, 3, 2, 1>::total_bytes(np_pad_of(d.n_persistent)) <= kTwoCtaSmem) {
+            // Two threads per score row (twice the softmax warps, half the dependent chain per key tile each) once a
+            // query tile has enough key tiles for that to outweigh the exchange between the two threads: measured
+            // on 8 x 10 heads x 4112 rows, window 128 | 512 | 2048: 91.0 | 141.5 | 293.9 us against 87.2 | 152.6 | 300.9.
+            if (d.window >= 192)
+                return launch_tc<64, 3, 2, 1, 2>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
+            return launch_tc<64, 3, 2, 1, 1>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
+        }
+        return launch_tc<64, 3, 3, 2, 1>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
     }
-    return launch_tc<128, 2, 2, 2>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
+    return launch_tc<128, 2, 2, 2, 1>(d, q, k, v, o, stream, window_block, all_keys, lse, wait);
 }
 
 }  // namespace tmw
