@@ -928,8 +928,8 @@ def run_train(args, wl_name: str, wl: dict) -> None:
             "config": dict(workload=wl_name, **wl, global_batch=B * world, parallelism=f"batch-sharded x{world}",
                            l2="inputs rotate over 4 sets; activations + gradients per step > 126 MB L2",
                            flops_per_step_per_gpu=flops),
-            "roofline": {"bound": "tensor", "kernel": "attention-core backward (tmw_prefill_backward: dK/dV and dQ "
-                         "launches of the tcgen05 kernel; the block-sparse class: warp-level tensor cores)", "achieved": achieved, "peak": peaks["bf16_tflops"],
+            "roofline": {"bound": "tensor", "kernel": "attention-core backward (tmw_prefill_backward / "
+                         "tmw_prefill_block_sparse_backward: dQ and dK/dV launches of the tcgen05 kernel)", "achieved": achieved, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                          "peak_source": f"{peaks['source']} bf16 burst", "avg_launch_ms": core_ms, "traffic": NCU_TRAFFIC_BYTES.get(wl_name),
                          "algorithmic_flops_per_launch": flops["core_bwd"]},

@@ -134,7 +134,8 @@ TMW_API int tmw_prefill_block_sparse(const tmw_prefill_desc* desc, int32_t block
  * lse holds batch x heads x L floats in two planes: [batch, heads, L - n_persistent] for the sequence rows,
  * followed by [batch, heads, n_persistent] for the persistent rows.  The backward writes dq, dk, dv (addressed
  * like q, k, v) from d_o (addressed like o): what autograd does through the reference's per-block matmul /
- * softmax / matmul (block_sparse_attention.py:163-199, 258-343).
+ * softmax / matmul (block_sparse_attention.py:163-199, 258-343).  Kernels and desc->algo as for
+ * tmw_prefill_backward (tcgen05 for bf16 / f16 with head_dim 64 or 128 unless another path is pinned).
  */
 TMW_API int tmw_prefill_block_sparse_lse(const tmw_prefill_desc* desc, int32_t block_size, const void* q, const void* k,
                                          const void* v, void* o, float* lse, void* stream);

@@ -151,7 +151,10 @@ def test_block_sparse_module_gradients_match_reference_fp32():
 
 
 @pytest.mark.parametrize("dh,H,B,T,w,bs,Np", [(64, 2, 1, 700, 128, 64, 16), (128, 1, 1, 400, 100, 32, 5),
-                                               (64, 1, 2, 300, 0, 16, 0)])
+                                               (64, 1, 2, 300, 0, 16, 0),
+                                               (64, 1, 1, 1500, 512, 64, 16),    # windows over several tiles, ragged tail
+                                               (64, 1, 1, 600, 100, 48, 130),    # persistent rows over two tiles, odd block
+                                               (128, 1, 1, 900, 256, 64, 16)])
 def test_block_sparse_core_gradients_bf16_both_backward_kernels(dh, H, B, T, w, bs, Np):
     from oracle import block_sparse_oracle as bo
 
@@ -165,7 +168,8 @@ def test_block_sparse_core_gradients_bf16_both_backward_kernels(dh, H, B, T, w, 
     o = _native.prefill(qd, kd, vd, w, Np, window_block=bs, lse=lse)
     d_o = torch.empty_like(o)
     d_o.copy_(g.to(DEV))
-    for bwd_algo in (_native.ALGO_SIMT, _native.ALGO_AUTO):
+    # CUDA cores, warp-level tensor cores, tcgen05, and what the library picks by itself (tcgen05)
+    for bwd_algo in (_native.ALGO_SIMT, _native.ALGO_MMA, _native.ALGO_TCGEN05, _native.ALGO_AUTO):
         dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
         _native.prefill_backward(qd, kd, vd, o, d_o, lse, dq, dk, dv, w, Np, algo=bwd_algo, window_block=bs)
         for got, want, nm in ((dq, qr.grad, "dq"), (dk, kr.grad, "dk"), (dv, vr.grad, "dv")):

@@ -268,6 +268,10 @@ int tmw_prefill_block_sparse_backward(const tmw_prefill_desc* desc, int32_t bloc
     if (!tmw::aligned16(d_o) || !tmw::aligned16(dq) || !tmw::aligned16(dk) || !tmw::aligned16(dv))
         return TMW_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool tc_ok = tmw::prefill_backward_tc_supports(*desc);
+    if (desc->algo == TMW_ALGO_TCGEN05 && !tc_ok) return TMW_ERR_UNSUPPORTED;
+    if ((desc->algo == TMW_ALGO_AUTO || desc->algo == TMW_ALGO_TCGEN05) && tc_ok)
+        return tmw::launch_prefill_backward_tc(*desc, q, k, v, o, d_o, lse, dq, dk, dv, s, block_size);
     if (desc->algo != TMW_ALGO_SIMT && tmw::prefill_backward_mma_supports(*desc))
         return tmw::launch_prefill_backward_mma(*desc, q, k, v, o, d_o, lse, dq, dk, dv, s, block_size, true);
     return tmw::launch_prefill_backward(*desc, q, k, v, o, d_o, lse, dq, dk, dv, s, block_size, true);

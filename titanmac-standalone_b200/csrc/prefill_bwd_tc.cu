@@ -1,7 +1,7 @@
 // Backward of the windowed attention core on tcgen05: dQ, dK, dV over the visible pairs only, every matrix
 // product on the 5th-generation tensor cores with accumulators AND the 16-bit intermediates (P, dS) in tensor
 // memory, tiles staged by TMA.  Whole sequences (q_pos0 = 0, k_pos0 = n_persistent), 16-bit types, head_dim 64
-// or 128, the plain windowed mask.
+// or 128; the plain windowed mask, or (kernels instantiated with GENERAL) the mask of the block-sparse class.
 //
 // Same mathematics as the other backward paths of this library (c = scale * log2 e, lse from the forward):
 //   S = Q Kᵀ,  P = exp2(S c - lse) o mask,  dP = dO Vᵀ,  D_i = dO_i · O_i,  dS = P o (dP - D)
@@ -60,6 +60,12 @@ struct BwdParams {
     float* stats;
     int rows_pad;
     int n_bx, heads, batch;      // row tiles per (batch, head); grid = n_bx * heads * batch
+    // The mask of the block-sparse class (kernels instantiated with GENERAL): block > 0 moves the left edge of a
+    // query's window in steps of `block` rows (first_visible_pos), and the persistent QUERY rows see every key;
+    // lse then comes in two planes, [batch, heads, rows - np] for the sequence rows and, at lse_pers,
+    // [batch, heads, np] for the persistent rows.
+    int block;
+    const float* lse_pers;
     int* status;
 };
 
@@ -109,31 +115,42 @@ struct ColPlan {
     int a1, n1;  // second segment
 };
 
+// last query that sees sequence key k through its window (block > 0: the window's left edge is block-aligned)
+__device__ __forceinline__ int last_query_of_key(int k, int np, int w, int block) {
+    return block > 0 ? np + ((k - np + w) / block) * block + block - 1 : k + w;
+}
+
+// `block` > 0 selects the block-sparse class's mask (then the persistent query rows see every key as well)
 template <bool ROWS_ARE_KEYS, int CW>
-__device__ __forceinline__ ColPlan col_plan(int r0, int L, int w, int np) {
+__device__ __forceinline__ ColPlan col_plan(int r0, int L, int w, int np, int block) {
     ColPlan c = {0, 0, 0, 0};
     const int r1 = min(L, r0 + BT);
     const int n_tiles = (L + CW - 1) / CW;
+    const int np_tiles = (np + CW - 1) / CW;
     if (ROWS_ARE_KEYS) {
         if (r0 < np) {  // the tile holds persistent keys: every query sees them
             c.n0 = n_tiles;
             return c;
         }
-        c.a1 = r0 / CW;
-        c.n1 = min(L - 1, r1 - 1 + w) / CW - c.a1 + 1;
+        if (block > 0) c.n0 = np_tiles;  // the persistent queries see every key
+        c.a1 = max(r0 / CW, c.n0);
+        c.n1 = max(0, min(L - 1, last_query_of_key(r1 - 1, np, w, block)) / CW - c.a1 + 1);
         return c;
     }
-    const int np_tiles = (np + CW - 1) / CW;
+    if (block > 0 && r0 < np) {  // the tile holds persistent queries: they see every key
+        c.n0 = n_tiles;
+        return c;
+    }
     c.n0 = np_tiles;  // persistent keys
     if (r1 > np) {
-        const int lo = max(np, max(r0, np) - w);
+        const int lo = first_visible_pos(max(r0, np), np, w, block);
         c.a1 = max(lo / CW, np_tiles);
         c.n1 = max(0, (r1 - 1) / CW - c.a1 + 1);
     }
     return c;
 }
 
-template <int DH, bool BF16, bool ROWS_ARE_KEYS>
+template <int DH, bool BF16, bool ROWS_ARE_KEYS, bool GENERAL>
 __global__ void __launch_bounds__(kBwdThreads, Geo<DH>::kCtasPerSm)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant__ CUtensorMap map_r2,
               const __grid_constant__ CUtensorMap map_c1, const __grid_constant__ CUtensorMap map_c2,
@@ -163,7 +180,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
     {
         const int n_bh = p.heads * p.batch;
         int id = (int)blockIdx.x, bh;
-        if (ROWS_ARE_KEYS && p.np > 0 && p.n_bx > 1) {
+        if ((ROWS_ARE_KEYS || GENERAL) && p.np > 0 && p.n_bx > 1) {
             if (id < n_bh) { tile_x = 0; bh = id; }
             else { id -= n_bh; tile_x = 1 + id % (p.n_bx - 1); bh = id / (p.n_bx - 1); }
         } else {
@@ -174,7 +191,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
         batch = bh / p.heads;
     }
     const int r0 = tile_x * BT;
-    const ColPlan plan = col_plan<ROWS_ARE_KEYS, CW>(r0, p.rows, p.window, p.np);
+    const int wblock = GENERAL ? p.block : 0;
+    const ColPlan plan = col_plan<ROWS_ARE_KEYS, CW>(r0, p.rows, p.window, p.np, wblock);
     const int n_cols = plan.n0 + plan.n1;
     auto col_tile = [&](int n) -> int { return n < plan.n0 ? plan.a0 + n : plan.a1 + (n - plan.n0); };
     // coordinate order of a tensor map: (dh, rows, heads, batch) or (dh, heads, rows, batch)
@@ -252,7 +270,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
                 } else {
                     for (int i = lane; i < CW; i += 32) {
                         const int qrow = col_tile(n) * CW + i;
-                        v_lse[i] = qrow < p.rows ? p.lse[bh * p.rows + qrow] : 0.f;
+                        v_lse[i] = qrow >= p.rows ? 0.f
+                                   : !GENERAL ? p.lse[bh * p.rows + qrow]
+                                   : qrow >= p.np ? p.lse[bh * (p.rows - p.np) + (qrow - p.np)] : p.lse_pers[bh * p.np + qrow];
                         v_lse[CW + i] = delta_of<DH, BF16>(p, batch, head, qrow);
                     }
                 }
@@ -328,14 +348,19 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
         const int pos_row = r0 + row;              // position of this thread's key (ROWS_ARE_KEYS) or query
         const uint32_t t_row = tmem_base + ((uint32_t)(g * 32) << 16);
         const long long bh = (long long)batch * p.heads + head;
-        const float* lse_bh = p.lse + bh * p.rows;
+        // log-sum-exp of a query row (GENERAL: the persistent rows have a plane of their own)
+        auto lse_of = [&](int q) -> float {
+            if (q >= p.rows) return 0.f;
+            if (GENERAL) return q >= p.np ? p.lse[bh * (p.rows - p.np) + (q - p.np)] : p.lse_pers[bh * p.np + q];
+            return p.lse[bh * p.rows + q];
+        };
         constexpr int HC = CW / 2;                 // columns per thread and tile
         const int cbase = half * HC;
 
         // rows are queries: this thread's own statistics, once
         float lse_own = 0.f, d_own = 0.f;
         if (!ROWS_ARE_KEYS) {
-            lse_own = pos_row < p.rows ? lse_bh[pos_row] : 0.f;
+            lse_own = lse_of(pos_row);
             d_own = delta_of<DH, BF16>(p, batch, head, pos_row);
             if (p.stats != nullptr && half == 0) {  // rows beyond the sequence get (0, 0), like the bounds-checked path
                 p.stats[bh * 2 * p.rows_pad + pos_row] = lse_own;
@@ -353,21 +378,26 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
             bool full;
             if (ROWS_ARE_KEYS)  // rows = keys [rlo, rhi], columns = queries [clo, chi]
                 full = r0 + BT <= p.rows && c0 + CW <= p.rows &&
-                       (rhi < p.np || (rlo >= p.np && clo >= p.np && rhi <= clo && chi - rlo <= p.window));
+                       (rhi < p.np || (GENERAL && chi < p.np) ||
+                        (rlo >= p.np && clo >= p.np && rhi <= clo && chi <= last_query_of_key(rlo, p.np, p.window, wblock)));
             else               // rows = queries, columns = keys
                 full = r0 + BT <= p.rows && c0 + CW <= p.rows &&
-                       (chi < p.np || (clo >= p.np && rlo >= p.np && chi <= rlo && rhi - clo <= p.window));
+                       (chi < p.np || (GENERAL && rhi < p.np) ||
+                        (clo >= p.np && rlo >= p.np && chi <= rlo && clo >= first_visible_pos(rhi, p.np, p.window, wblock)));
 
-            // Columns of this tile that this thread's row sees: [vlo, vhi] (relative to the tile) and, when the rows
-            // are queries, the persistent keys below column npc.  Same set as visible(), at two instructions per element.
+            // Columns of this tile that this thread's row sees: [vlo, vhi] (relative to the tile) and the columns
+            // below npc - the persistent keys when the rows are queries, the persistent queries (block-sparse
+            // class: they see every key) when the rows are keys.  Two instructions per element.
             int vlo = 1, vhi = 0, npc = 0;
             if (pos_row < p.rows) {
                 if (ROWS_ARE_KEYS) {
+                    if (GENERAL) npc = p.np - c0;
                     if (pos_row < p.np) { vlo = 0; vhi = p.rows - 1 - c0; }
-                    else { vlo = pos_row - c0; vhi = min(pos_row + p.window, p.rows - 1) - c0; }
+                    else { vlo = pos_row - c0; vhi = min(last_query_of_key(pos_row, p.np, p.window, wblock), p.rows - 1) - c0; }
                 } else {
                     npc = p.np - c0;
-                    if (pos_row >= p.np) { vlo = max(p.np, pos_row - p.window) - c0; vhi = pos_row - c0; }
+                    if (pos_row >= p.np) { vlo = first_visible_pos(pos_row, p.np, p.window, wblock) - c0; vhi = pos_row - c0; }
+                    else if (GENERAL) { vlo = 0; vhi = p.rows - 1 - c0; }
                 }
             }
             const int vbase = cbase - vlo;                 // column - vlo = vbase + (column - cbase)
@@ -410,7 +440,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
                             if (MASKED) {
                                 const int rel = j * 16 + e4 + e;  // column - cbase, a compile-time constant
                                 bool vis = ((unsigned)(vbase + rel) <= vspan) & !vnone;
-                                if (!ROWS_ARE_KEYS) vis |= rel < pbase;
+                                if (!ROWS_ARE_KEYS || GENERAL) vis |= rel < pbase;
                                 pv[e] = vis ? pr : 0.f;
                                 dv[e] = vis ? dsv : 0.f;
                             } else {
@@ -440,7 +470,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap map_r1, const __grid_constant_
             // a warp none of whose rows sees any of its columns (rows beyond the diagonal or the window's edge, or the
             // sequence keys of a tile that far queries only reach through the persistent keys) writes zeros unread
             const bool mine_empty = vnone || vhi < cbase || vlo >= cbase + HC;
-            const bool nothing = !full && __all_sync(0xffffffffu, mine_empty && (ROWS_ARE_KEYS || pbase <= 0 || pos_row >= p.rows));
+            const bool nothing = !full && __all_sync(0xffffffffu, mine_empty && ((ROWS_ARE_KEYS && !GENERAL) || pbase <= 0 || pos_row >= p.rows));
             if (nothing) {
                 const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 #pragma unroll
@@ -628,7 +658,7 @@ cudaMemPool_t scratch_pool() {
 
 template <int DH>
 int launch_bwd_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                  const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream) {
+                  const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream, int window_block) {
     using L = BwdSmem<DH>;
     const int B = d.batch, H = d.heads, R = d.q_rows;
     const Strides4 sq = strides_of(B, H, R, DH, d.q_stride), sk = strides_of(B, H, R, DH, d.k_stride);
@@ -652,6 +682,8 @@ int launch_bwd_tc(const tmw_prefill_desc& d, const void* q, const void* k, const
     p.o = o; p.d_o = d_o;
     for (int i = 0; i < 3; ++i) p.os[i] = d.o_stride[i];
     p.lse = lse;
+    p.block = window_block;
+    p.lse_pers = window_block > 0 ? lse + (size_t)B * H * (R - d.n_persistent) : nullptr;
     p.status = device_status_word();
     if (p.status == nullptr) return TMW_ERR_CUDA;
     // scratch memory for the rows' (lse, D), ordered on the caller's stream; without it the launch whose rows are
@@ -677,12 +709,17 @@ int launch_bwd_tc(const tmw_prefill_desc& d, const void* q, const void* k, const
         return TMW_OK;
     };
     // dQ first: rows are queries (Q, dO), columns are keys (K, V); it also leaves the rows' statistics
-    int st = d.dtype == TMW_BF16 ? run(bwd_tc_kernel<DH, true, false>, mq, mdo, ck, cv, mdq, mdq)
-                                 : run(bwd_tc_kernel<DH, false, false>, mq, mdo, ck, cv, mdq, mdq);
+    const bool bf16 = d.dtype == TMW_BF16, general = window_block > 0;
+    int st = general ? (bf16 ? run(bwd_tc_kernel<DH, true, false, true>, mq, mdo, ck, cv, mdq, mdq)
+                             : run(bwd_tc_kernel<DH, false, false, true>, mq, mdo, ck, cv, mdq, mdq))
+                     : (bf16 ? run(bwd_tc_kernel<DH, true, false, false>, mq, mdo, ck, cv, mdq, mdq)
+                             : run(bwd_tc_kernel<DH, false, false, false>, mq, mdo, ck, cv, mdq, mdq));
     // dK, dV: rows are keys (K, V), columns are queries (Q, dO)
     if (st == TMW_OK)
-        st = d.dtype == TMW_BF16 ? run(bwd_tc_kernel<DH, true, true>, mk, mv, cq, cdo, mdv, mdk)
-                                 : run(bwd_tc_kernel<DH, false, true>, mk, mv, cq, cdo, mdv, mdk);
+        st = general ? (bf16 ? run(bwd_tc_kernel<DH, true, true, true>, mk, mv, cq, cdo, mdv, mdk)
+                             : run(bwd_tc_kernel<DH, false, true, true>, mk, mv, cq, cdo, mdv, mdk))
+                     : (bf16 ? run(bwd_tc_kernel<DH, true, true, false>, mk, mv, cq, cdo, mdv, mdk)
+                             : run(bwd_tc_kernel<DH, false, true, false>, mk, mv, cq, cdo, mdv, mdk));
     const cudaError_t launched = cudaGetLastError();
     if (p.stats != nullptr) (void)cudaFreeAsync(p.stats, stream);
     if (st != TMW_OK) return st;
@@ -697,7 +734,7 @@ bool prefill_backward_tc_supports(const tmw_prefill_desc& d) {
     if (d.dtype != TMW_BF16 && d.dtype != TMW_F16) return false;
     if (d.head_dim != 64 && d.head_dim != 128) return false;
     if (d.batch > 65535 || d.heads > 65535) return false;
-    if ((int64_t)d.q_rows + d.window + 2 * BT >= (int64_t)1 << 30) return false;
+    if ((int64_t)d.q_rows + d.window + 2 * BT >= (int64_t)1 << 29) return false;  // (+ a block size of up to 2^20)
     return strides_of(d.batch, d.heads, d.q_rows, d.head_dim, d.q_stride).ok &&
            strides_of(d.batch, d.heads, d.q_rows, d.head_dim, d.k_stride).ok &&
            strides_of(d.batch, d.heads, d.q_rows, d.head_dim, d.v_stride).ok &&
@@ -705,9 +742,10 @@ bool prefill_backward_tc_supports(const tmw_prefill_desc& d) {
 }
 
 int launch_prefill_backward_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
-                               const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream) {
-    return d.head_dim == 64 ? launch_bwd_tc<64>(d, q, k, v, o, d_o, lse, dq, dk, dv, stream)
-                            : launch_bwd_tc<128>(d, q, k, v, o, d_o, lse, dq, dk, dv, stream);
+                               const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream,
+                               int window_block) {
+    return d.head_dim == 64 ? launch_bwd_tc<64>(d, q, k, v, o, d_o, lse, dq, dk, dv, stream, window_block)
+                            : launch_bwd_tc<128>(d, q, k, v, o, d_o, lse, dq, dk, dv, stream, window_block);
 }
 
 }  // namespace tmw

@@ -152,10 +152,12 @@ bool prefill_backward_mma_supports(const tmw_prefill_desc& d);
 int launch_prefill_backward_mma(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
                                 const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream,
                                 int window_block = 0, bool pers_global = false);
-// the same on tcgen05 (plain windowed mask, 16-bit types, head_dim 64 / 128)
+// the same on tcgen05 (16-bit types, head_dim 64 / 128); window_block > 0: the block-sparse class's mask with its
+// persistent query rows seeing every key and lse in two planes
 bool prefill_backward_tc_supports(const tmw_prefill_desc& d);
 int launch_prefill_backward_tc(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o,
-                               const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream);
+                               const void* d_o, const float* lse, void* dq, void* dk, void* dv, cudaStream_t stream,
+                               int window_block = 0);
 bool prefill_tc_supports(const tmw_prefill_desc& d, const void* q, const void* k, const void* v, const void* o);
 int launch_decode(const tmw_cache_desc& c, const void* q, const void* k_new, const void* v_new, void* o,
                   const int64_t qs[2], const int64_t ns[2], const int64_t os[2], const int32_t* pos,
