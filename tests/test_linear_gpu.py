@@ -42,7 +42,8 @@ def test_layer_shapes(m, n, k, bias, gelu):
     run_case(m, n, k, bias, gelu)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (127, 136, 72), (129, 264, 200), (300, 50000, 640), (515, 128, 64)])
+@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (127, 136, 72), (129, 264, 200), (300, 50000, 640), (515, 128, 64),
+                                   (700, 40, 64), (1000, 1944, 128), (513, 24, 640)])  # narrow last tiles of the pair kernel
 def test_ragged_sizes(m, n, k):
     run_case(m, n, k, True, False, seed=m)
     run_case(m, n, k, False, True, seed=m + 1)
